@@ -1,0 +1,1038 @@
+// Host side of the B200 decode engine: device memory layout, weight repacking, the per-token
+// CUDA graph and the C ABI declared in include/lpp_b200.h.
+//
+// Stands in for the device halves of malloc_run_state / free_run_state (src/model.cpp:18-118),
+// attention / transformer_block / forward (src/model.cpp:121-384, USE_CUDA branches) and the upload
+// code of the loaders (src/loader.cpp:73-131, 543-637) of the reference tree.
+//
+// Device layout (per tensor-parallel rank; Dq = local query rows, KVd = local kv rows, Fl = local
+// FFN columns):
+//   wqkv [L][Dq + 2*KVd][D]   rows q | k | v of one layer back to back  -> one fused GEMV
+//   wo   [L][D][Dq]           column slice of the reference wo, repacked contiguous
+//   w13  [L][2*Fl][D]         gate row i and up row i interleaved         -> SwiGLU in the epilogue
+//   w2   [L][D][Fl]           column slice of the reference w2
+//   emb / wcls [V][D]         weight dtype; wcls aliases emb when the classifier is tied
+//   K, V cache [L][KVHl][S][hs]   FP16 (or FP32), the reference's index order
+//   rope [S][hs/2] (cos, sin)     built on the host with libm so rotations match the CPU path bit
+//                                 for bit
+#include <cuda_runtime.h>
+#include <cuda_fp16.h>
+#include <dlfcn.h>
+#include <math.h>
+#include <stdarg.h>
+#include <stdio.h>
+#include <stdlib.h>
+#include <string.h>
+
+#include <algorithm>
+#include <string>
+#include <vector>
+
+#include "../../include/lpp_b200.h"
+#include "attention.cuh"
+#include "common.cuh"
+#include "gemv.cuh"
+#include "ops.cuh"
+#include "sampler.cuh"
+
+using namespace lpp;
+
+// ------------------------------------------------------------------ error plumbing
+
+static thread_local std::string g_err;
+static lpp_status fail(lpp_status s, const char* fmt, ...) {
+    char buf[512];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof buf, fmt, ap);
+    va_end(ap);
+    g_err = buf;
+    return s;
+}
+#define CU(call)                                                                                   \
+    do {                                                                                           \
+        cudaError_t e_ = (call);                                                                   \
+        if (e_ != cudaSuccess)                                                                     \
+            return fail(LPP_ERR_CUDA, "%s failed: %s (%s:%d)", #call, cudaGetErrorString(e_), __FILE__, __LINE__); \
+    } while (0)
+#define TRY(call)                      \
+    do {                               \
+        lpp_status s_ = (call);        \
+        if (s_ != LPP_OK) return s_;   \
+    } while (0)
+
+// LPP_TRACE=1 in the environment prints one line per host-side phase and synchronises after every
+// launch of an un-graphed step, to localise a failing kernel.
+static bool tracing() {
+    static int t = -1;
+    if (t < 0) t = getenv("LPP_TRACE") ? 1 : 0;
+    return t == 1;
+}
+#define TRACE(...)                        \
+    do {                                  \
+        if (tracing()) {                  \
+            fprintf(stderr, "[lpp] " __VA_ARGS__); \
+            fprintf(stderr, "\n");        \
+            fflush(stderr);               \
+        }                                 \
+    } while (0)
+
+// ------------------------------------------------------------------ NCCL through dlopen
+// Only tensor-parallel engines need NCCL, so it is bound at run time; a single-GPU process never
+// loads it.  The handful of prototypes below follow nccl.h.
+
+namespace nccl {
+typedef struct ncclComm* comm_t;
+typedef struct { char internal[128]; } unique_id;
+typedef int result_t;
+static void* lib = nullptr;
+static result_t (*GetUniqueId)(unique_id*);
+static result_t (*CommInitRank)(comm_t*, int, unique_id, int);
+static result_t (*CommDestroy)(comm_t);
+static result_t (*AllReduce)(const void*, void*, size_t, int /*dtype*/, int /*op*/, comm_t, cudaStream_t);
+static const char* (*GetErrorString)(result_t);
+constexpr int kFloat32 = 7, kSum = 0;
+static bool load() {
+    if (lib) return true;
+    const char* names[] = {"libnccl.so.2", "libnccl.so"};
+    for (const char* n : names) {
+        lib = dlopen(n, RTLD_NOW | RTLD_GLOBAL);
+        if (lib) break;
+    }
+    if (!lib) return false;
+    GetUniqueId = (decltype(GetUniqueId))dlsym(lib, "ncclGetUniqueId");
+    CommInitRank = (decltype(CommInitRank))dlsym(lib, "ncclCommInitRank");
+    CommDestroy = (decltype(CommDestroy))dlsym(lib, "ncclCommDestroy");
+    AllReduce = (decltype(AllReduce))dlsym(lib, "ncclAllReduce");
+    GetErrorString = (decltype(GetErrorString))dlsym(lib, "ncclGetErrorString");
+    return GetUniqueId && CommInitRank && CommDestroy && AllReduce && GetErrorString;
+}
+}  // namespace nccl
+
+// ------------------------------------------------------------------ engine
+
+enum Kind { kQkv = 0, kAttn = 1, kOproj = 2, kGateUp = 3, kDown = 4, kLmHead = 5, kSampler = 6, kAllReduce = 7, kKinds = 8 };
+
+struct lpp_engine {
+    lpp_config c;
+    int hs, Hl, KVHl, Dq, KVd, Fl, gqa;
+    int esz, kvesz;
+    int num_sms;
+    int attn_splits, attn_gb, attn_z;
+    int sample_blocks;
+    size_t smem_optin;
+    cudaStream_t stream = nullptr;
+    // weights
+    void *wqkv = nullptr, *wo = nullptr, *w13 = nullptr, *w2 = nullptr, *emb = nullptr, *wcls = nullptr;
+    float *rms_att = nullptr, *rms_ffn = nullptr, *rms_final = nullptr;
+    bool wcls_owned = false;
+    std::vector<unsigned char> got;  // upload bookkeeping: [tensor][layer]
+    // state
+    void *kcache = nullptr, *vcache = nullptr;
+    float *xa = nullptr, *xb = nullptr, *q = nullptr, *att_out = nullptr, *hb = nullptr, *logits = nullptr;
+    float *attn_part = nullptr, *samp_max = nullptr, *samp_sum = nullptr, *r_values = nullptr;
+    int *samp_idx = nullptr, *out_tokens = nullptr;
+    unsigned int *attn_counters = nullptr, *samp_counter = nullptr;
+    float2* rope = nullptr;
+    StepState* st = nullptr;
+    int run_cap = 0;  // capacity of r_values / out_tokens
+    // host staging (pinned)
+    StepState* h_st = nullptr;
+    int* h_out = nullptr;  // out_token, status
+    // upload staging
+    void* stage = nullptr;
+    size_t stage_bytes = 0;
+    // graphs
+    cudaGraphExec_t g_full = nullptr, g_logits = nullptr;
+    bool finalized = false;
+    int kernels_full = 0;
+    cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+    // NCCL
+    nccl::comm_t comm = nullptr;
+    // profiling hooks
+    bool profiling = false;
+    std::vector<cudaEvent_t> prof_events;
+    std::vector<int> prof_kinds;
+};
+
+static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+template <typename... KArgs, typename... Args>
+static cudaError_t launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s,
+                                 bool pdl, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, args...);
+}
+
+// ---- GEMV dispatch
+
+struct GemvPlan {
+    dim3 grid;
+    int threads;
+    size_t smem;
+};
+
+template <typename WT, int EPI>
+static cudaError_t launch_gemv_t(lpp_engine* e, GemvArgs& a, bool pdl, cudaStream_t s) {
+    const int esz = sizeof(WT);
+    const int groups = a.n_rows / kRowsPerGroup;
+    const size_t xbytes = align_up((size_t)a.K * 4, 128);
+    if (e->c.flags & LPP_FLAG_GEMV_LDG) {
+        const size_t smem = 128 + xbytes;
+        static bool attr_done[64] = {};
+        if (!attr_done[e->c.device & 63]) {
+            cudaError_t r = cudaFuncSetAttribute(gemv_ldg_kernel<WT, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                 (int)e->smem_optin);
+            if (r != cudaSuccess) return r;
+            attr_done[e->c.device & 63] = true;
+        }
+        const int grid = std::max(1, std::min(groups, e->num_sms * 4));
+        return launch_kernel(gemv_ldg_kernel<WT, EPI>, dim3(grid), dim3(kGemvLdgThreads), smem, s, pdl, a);
+    }
+    int kc = std::min(a.K, 8192 / esz);
+    kc = kc / 8 * 8;
+    a.kc = kc;
+    a.stage_bytes = kRowsPerGroup * kc * esz;
+    const size_t fixed = kGemvBarrierBytes + 128 + xbytes;
+    size_t ring = (size_t)(e->c.ring_kb > 0 ? e->c.ring_kb : 88) * 1024;
+    if (fixed + ring > e->smem_optin) ring = e->smem_optin - fixed;
+    int ns = (int)(ring / a.stage_bytes);
+    ns = std::max(2, std::min(ns, kGemvMaxStages));
+    a.n_stages = ns;
+    const size_t smem = fixed + (size_t)ns * a.stage_bytes;
+    if (smem > e->smem_optin) return cudaErrorInvalidValue;
+    static bool attr_done[64] = {};
+    if (!attr_done[e->c.device & 63]) {
+        cudaError_t r = cudaFuncSetAttribute(gemv_ring_kernel<WT, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             (int)e->smem_optin);
+        if (r != cudaSuccess) return r;
+        attr_done[e->c.device & 63] = true;
+    }
+    const int grid = std::max(1, std::min(groups, e->num_sms));
+    return launch_kernel(gemv_ring_kernel<WT, EPI>, dim3(grid), dim3(kGemvRingThreads), smem, s, pdl, a);
+}
+
+static cudaError_t launch_gemv(lpp_engine* e, int epi, int w_dtype, GemvArgs& a, bool pdl, cudaStream_t s) {
+#define LPP_GEMV_CASE(E)                                                          \
+    case E:                                                                       \
+        return w_dtype == LPP_F16 ? launch_gemv_t<__half, E>(e, a, pdl, s)        \
+                                  : launch_gemv_t<float, E>(e, a, pdl, s);
+    switch (epi) {
+        LPP_GEMV_CASE(kEpiStore)
+        LPP_GEMV_CASE(kEpiResid)
+        LPP_GEMV_CASE(kEpiSwiglu)
+        LPP_GEMV_CASE(kEpiQkv)
+    }
+#undef LPP_GEMV_CASE
+    return cudaErrorInvalidValue;
+}
+
+// ---- attention dispatch
+
+template <typename KT, int DPL>
+static cudaError_t launch_attn_d(lpp_engine* e, const AttnArgs& a, dim3 grid, bool pdl, cudaStream_t s) {
+    switch (e->attn_gb) {
+        case 4:
+            return launch_kernel(attn_decode_kernel<KT, DPL, 4>, grid, dim3(kAttnThreads), 0, s, pdl, a);
+        case 2:
+            return launch_kernel(attn_decode_kernel<KT, DPL, 2>, grid, dim3(kAttnThreads), 0, s, pdl, a);
+        default:
+            return launch_kernel(attn_decode_kernel<KT, DPL, 1>, grid, dim3(kAttnThreads), 0, s, pdl, a);
+    }
+}
+template <typename KT>
+static cudaError_t launch_attn_t(lpp_engine* e, const AttnArgs& a, dim3 grid, bool pdl, cudaStream_t s) {
+    switch (e->hs / 8) {
+        case 2: return launch_attn_d<KT, 2>(e, a, grid, pdl, s);
+        case 4: return launch_attn_d<KT, 4>(e, a, grid, pdl, s);
+        case 6: return launch_attn_d<KT, 6>(e, a, grid, pdl, s);
+        case 8: return launch_attn_d<KT, 8>(e, a, grid, pdl, s);
+        case 12: return launch_attn_d<KT, 12>(e, a, grid, pdl, s);
+        case 16: return launch_attn_d<KT, 16>(e, a, grid, pdl, s);
+    }
+    return cudaErrorInvalidValue;
+}
+
+// ---- one decode step as a sequence of launches (captured into the graph, or run directly)
+
+struct Recorder {
+    lpp_engine* e;
+    cudaStream_t s;
+    bool prev_kernel = false;  // previous stream item was one of our kernels -> PDL edge allowed
+    int kernels = 0;
+    cudaError_t err = cudaSuccess;
+    std::string where;
+
+    bool pdl() const { return prev_kernel && !(e->c.flags & LPP_FLAG_NO_PDL) && !e->profiling; }
+    void mark(int kind) {
+        if (!e->profiling) return;
+        cudaEvent_t ev;
+        cudaEventCreate(&ev);
+        cudaEventRecord(ev, s);
+        e->prof_events.push_back(ev);
+        e->prof_kinds.push_back(kind);
+    }
+    void check(cudaError_t r, const char* what) {
+        if (r != cudaSuccess && err == cudaSuccess) {
+            err = r;
+            where = what;
+        }
+        if (tracing() && (e->c.flags & LPP_FLAG_NO_GRAPH)) {
+            TRACE("launched %s #%d -> %s; syncing", what, kernels, cudaGetErrorString(r));
+            cudaError_t se = cudaStreamSynchronize(s);
+            TRACE("  sync -> %s", cudaGetErrorString(se));
+        }
+    }
+};
+
+// LPP_DEBUG_SKIP=<bitmask of Kind> leaves those kernels out of the step (results become
+// meaningless): a timing aid that shows what each kernel kind costs inside the replayed graph.
+static unsigned skip_mask() {
+    const char* v = getenv("LPP_DEBUG_SKIP");
+    return v ? (unsigned)strtol(v, nullptr, 0) : 0u;
+}
+
+static void record_gemv(Recorder& R, int kind, int epi, GemvArgs a) {
+    lpp_engine* e = R.e;
+    if (skip_mask() & (1u << kind)) return;
+    a.st = e->st;
+    a.vocab = e->c.vocab_size;
+    a.seq_len = e->c.seq_len;
+    R.mark(kind);
+    R.check(launch_gemv(e, epi, e->c.weight_dtype, a, R.pdl(), R.s), "gemv launch");
+    R.mark(-1);
+    R.prev_kernel = true;
+    R.kernels++;
+}
+
+static void record_allreduce(Recorder& R, float* buf, int n) {
+    lpp_engine* e = R.e;
+    R.mark(kAllReduce);
+    nccl::result_t r = nccl::AllReduce(buf, buf, (size_t)n, nccl::kFloat32, nccl::kSum, e->comm, R.s);
+    if (r != 0 && R.err == cudaSuccess) {
+        R.err = cudaErrorUnknown;
+        R.where = std::string("ncclAllReduce: ") + nccl::GetErrorString(r);
+    }
+    R.mark(-1);
+    R.prev_kernel = false;
+}
+
+static void record_step(Recorder& R, bool with_sampler) {
+    lpp_engine* e = R.e;
+    const lpp_config& c = e->c;
+    const int D = c.dim, L = c.n_layers;
+    const size_t esz = e->esz;
+    const int qkv_rows = e->Dq + 2 * e->KVd;
+    const bool tp = c.tp_size > 1;
+    float* cur = e->xa;
+    float* oth = e->xb;
+    for (int l = 0; l < L; ++l) {
+        {  // fused RMSNorm + QKV GEMV + RoPE + KV scatter
+            GemvArgs a = {};
+            a.W = (const char*)e->wqkv + (size_t)l * qkv_rows * D * esz;
+            a.n_rows = qkv_rows;
+            a.K = D;
+            a.norm_w = e->rms_att + (size_t)l * D;
+            if (l == 0) {
+                a.emb = e->emb;
+                a.x_store = cur;
+            } else {
+                a.x = cur;
+            }
+            a.out = e->q;
+            a.q_rows = e->Dq;
+            a.kv_rows = e->KVd;
+            a.head_size = e->hs;
+            a.rope = e->rope;
+            const size_t lofs = (size_t)l * e->KVHl * c.seq_len * e->hs * e->kvesz;
+            a.k_cache = (char*)e->kcache + lofs;
+            a.v_cache = (char*)e->vcache + lofs;
+            a.kv_is_f32 = c.kv_dtype == LPP_F32;
+            record_gemv(R, kQkv, kEpiQkv, a);
+        }
+        {  // split-KV flash decode
+            AttnArgs a = {};
+            a.q = e->q;
+            const size_t lofs = (size_t)l * e->KVHl * c.seq_len * e->hs * e->kvesz;
+            a.k_cache = (char*)e->kcache + lofs;
+            a.v_cache = (char*)e->vcache + lofs;
+            a.out = e->att_out;
+            a.part = e->attn_part;
+            a.counters = e->attn_counters;
+            a.st = e->st;
+            a.seq_len = c.seq_len;
+            a.head_size = e->hs;
+            a.gqa = e->gqa;
+            a.n_splits = e->attn_splits;
+            dim3 grid(e->attn_splits, e->KVHl, e->attn_z);
+            if (!(skip_mask() & (1u << kAttn))) {
+            R.mark(kAttn);
+            R.check(c.kv_dtype == LPP_F32 ? launch_attn_t<float>(e, a, grid, R.pdl(), R.s)
+                                          : launch_attn_t<__half>(e, a, grid, R.pdl(), R.s),
+                    "attention launch");
+            R.mark(-1);
+            R.prev_kernel = true;
+            R.kernels++;
+            }
+        }
+        {  // o_proj + residual
+            GemvArgs a = {};
+            a.W = (const char*)e->wo + (size_t)l * D * e->Dq * esz;
+            a.n_rows = D;
+            a.K = e->Dq;
+            a.x = e->att_out;
+            a.resid = (!tp || c.tp_rank == 0) ? cur : nullptr;
+            a.out = tp ? oth : cur;
+            record_gemv(R, kOproj, kEpiResid, a);
+            if (tp) {
+                record_allreduce(R, oth, D);
+                std::swap(cur, oth);
+            }
+        }
+        {  // fused RMSNorm + gate|up GEMV + SwiGLU
+            GemvArgs a = {};
+            a.W = (const char*)e->w13 + (size_t)l * 2 * e->Fl * D * esz;
+            a.n_rows = 2 * e->Fl;
+            a.K = D;
+            a.x = cur;
+            a.norm_w = e->rms_ffn + (size_t)l * D;
+            a.out = e->hb;
+            record_gemv(R, kGateUp, kEpiSwiglu, a);
+        }
+        {  // down + residual
+            GemvArgs a = {};
+            a.W = (const char*)e->w2 + (size_t)l * D * e->Fl * esz;
+            a.n_rows = D;
+            a.K = e->Fl;
+            a.x = e->hb;
+            a.resid = (!tp || c.tp_rank == 0) ? cur : nullptr;
+            a.out = tp ? oth : cur;
+            record_gemv(R, kDown, kEpiResid, a);
+            if (tp) {
+                record_allreduce(R, oth, D);
+                std::swap(cur, oth);
+            }
+        }
+    }
+    {  // final RMSNorm + classifier
+        GemvArgs a = {};
+        a.W = e->wcls;
+        a.n_rows = c.vocab_size;
+        a.K = D;
+        a.x = cur;
+        a.norm_w = e->rms_final;
+        a.out = e->logits;
+        record_gemv(R, kLmHead, kEpiStore, a);
+    }
+    if (with_sampler && !(skip_mask() & (1u << kSampler))) {
+        SampleArgs a = {};
+        a.logits = e->logits;
+        a.vocab = c.vocab_size;
+        a.st = e->st;
+        a.part_max = e->samp_max;
+        a.part_idx = e->samp_idx;
+        a.part_sum = e->samp_sum;
+        a.counter = e->samp_counter;
+        a.r_values = e->r_values;
+        a.out_tokens = e->out_tokens;
+        R.mark(kSampler);
+        R.check(launch_kernel(sample_kernel, dim3(e->sample_blocks), dim3(kSampleThreads), 0, R.s, R.pdl(), a),
+                "sampler launch");
+        R.mark(-1);
+        R.prev_kernel = true;
+        R.kernels++;
+    }
+}
+
+static lpp_status capture(lpp_engine* e, bool with_sampler, cudaGraphExec_t* out, int* kernels) {
+    cudaGraph_t g = nullptr;
+    CU(cudaStreamBeginCapture(e->stream, cudaStreamCaptureModeThreadLocal));
+    Recorder R{e, e->stream};
+    record_step(R, with_sampler);
+    cudaError_t ce = cudaStreamEndCapture(e->stream, &g);
+    if (R.err != cudaSuccess) {
+        if (g) cudaGraphDestroy(g);
+        (void)cudaGetLastError();
+        return fail(LPP_ERR_CUDA, "%s: %s", R.where.c_str(), cudaGetErrorString(R.err));
+    }
+    if (ce != cudaSuccess) return fail(LPP_ERR_CUDA, "cudaStreamEndCapture: %s", cudaGetErrorString(ce));
+    cudaError_t ie = cudaGraphInstantiate(out, g, 0);
+    cudaGraphDestroy(g);
+    if (ie != cudaSuccess) return fail(LPP_ERR_CUDA, "cudaGraphInstantiate: %s", cudaGetErrorString(ie));
+    if (kernels) *kernels = R.kernels;
+    return LPP_OK;
+}
+
+static lpp_status run_step(lpp_engine* e, bool with_sampler) {
+    if (e->c.flags & LPP_FLAG_NO_GRAPH) {
+        Recorder R{e, e->stream};
+        record_step(R, with_sampler);
+        if (R.err != cudaSuccess) return fail(LPP_ERR_CUDA, "%s: %s", R.where.c_str(), cudaGetErrorString(R.err));
+        return LPP_OK;
+    }
+    CU(cudaGraphLaunch(with_sampler ? e->g_full : e->g_logits, e->stream));
+    return LPP_OK;
+}
+
+// ------------------------------------------------------------------ create / destroy
+
+static bool dpl_supported(int hs) {
+    const int d = hs / 8;
+    return hs % 8 == 0 && (d == 2 || d == 4 || d == 6 || d == 8 || d == 12 || d == 16);
+}
+
+extern "C" lpp_status lpp_engine_create(const lpp_config* cfg, const void* nccl_id, lpp_engine** out) {
+    if (!cfg || !out) return fail(LPP_ERR_INVALID_ARG, "null argument");
+    *out = nullptr;
+    const lpp_config& c = *cfg;
+    if (c.dim <= 0 || c.hidden_dim <= 0 || c.n_layers <= 0 || c.n_heads <= 0 || c.n_kv_heads <= 0 ||
+        c.vocab_size <= 0 || c.seq_len <= 0)
+        return fail(LPP_ERR_INVALID_ARG, "non-positive model dimension");
+    if (c.dim % c.n_heads || c.n_heads % c.n_kv_heads)
+        return fail(LPP_ERR_INVALID_ARG, "dim %% n_heads or n_heads %% n_kv_heads != 0");
+    if (c.weight_dtype != LPP_F16 && c.weight_dtype != LPP_F32) return fail(LPP_ERR_INVALID_ARG, "bad weight_dtype");
+    if (c.kv_dtype != LPP_F16 && c.kv_dtype != LPP_F32) return fail(LPP_ERR_INVALID_ARG, "bad kv_dtype");
+    if (c.tp_size < 1 || c.tp_rank < 0 || c.tp_rank >= c.tp_size) return fail(LPP_ERR_INVALID_ARG, "bad tp rank/size");
+    if (c.n_kv_heads % c.tp_size || c.hidden_dim % c.tp_size)
+        return fail(LPP_ERR_INVALID_ARG, "tp_size %d must divide n_kv_heads %d and hidden_dim %d", c.tp_size,
+                    c.n_kv_heads, c.hidden_dim);
+    const int hs = c.dim / c.n_heads;
+    if (!dpl_supported(hs)) return fail(LPP_ERR_INVALID_ARG, "head_size %d unsupported (16,32,48,64,96,128)", hs);
+    const int vec = c.weight_dtype == LPP_F16 ? 8 : 4;
+    const int Fl = c.hidden_dim / c.tp_size;
+    const int Dq = c.dim / c.tp_size;
+    if (c.dim % vec || Fl % vec || Dq % vec || (c.vocab_size & 1) || (Fl & 1))
+        return fail(LPP_ERR_INVALID_ARG, "dim/hidden/vocab not multiples of the vector width");
+    if (c.tp_size > 1 && !nccl_id) return fail(LPP_ERR_INVALID_ARG, "tp_size > 1 needs an nccl id");
+
+    int ndev = 0;
+    if (cudaGetDeviceCount(&ndev) != cudaSuccess || ndev == 0) {
+        (void)cudaGetLastError();
+        return fail(LPP_ERR_NO_DEVICE, "no CUDA device");
+    }
+    if (c.device < 0 || c.device >= ndev) return fail(LPP_ERR_INVALID_ARG, "device %d out of range", c.device);
+    CU(cudaSetDevice(c.device));
+    cudaDeviceProp prop;
+    CU(cudaGetDeviceProperties(&prop, c.device));
+    if (prop.major < 10) return fail(LPP_ERR_NO_DEVICE, "device is sm_%d%d; this library is built for sm_100a only", prop.major, prop.minor);
+
+    TRACE("create: device %d ok (%s, %d SMs)", c.device, prop.name, prop.multiProcessorCount);
+    lpp_engine* e = new lpp_engine();
+    e->c = c;
+    e->hs = hs;
+    e->Hl = c.n_heads / c.tp_size;
+    e->KVHl = c.n_kv_heads / c.tp_size;
+    e->Dq = Dq;
+    e->KVd = e->KVHl * hs;
+    e->Fl = Fl;
+    e->gqa = c.n_heads / c.n_kv_heads;
+    e->esz = c.weight_dtype == LPP_F16 ? 2 : 4;
+    e->kvesz = c.kv_dtype == LPP_F16 ? 2 : 4;
+    e->num_sms = prop.multiProcessorCount;
+    e->smem_optin = prop.sharedMemPerBlockOptin;
+    e->attn_gb = (e->gqa % 4 == 0) ? 4 : (e->gqa % 2 == 0 ? 2 : 1);  // query heads per attention CTA
+    e->attn_z = e->gqa / e->attn_gb;
+    int splits = c.attn_splits > 0 ? c.attn_splits : (2 * e->num_sms + e->KVHl * e->attn_z - 1) / (e->KVHl * e->attn_z);
+    e->attn_splits = std::max(1, std::min(splits, 64));
+    e->sample_blocks = (c.vocab_size + kSampleChunk - 1) / kSampleChunk;
+    if (e->sample_blocks > kSampleMaxBlocks) {
+        delete e;
+        return fail(LPP_ERR_TOO_LARGE, "vocab_size %d exceeds the sampler's %d", c.vocab_size, kSampleMaxBlocks * kSampleChunk);
+    }
+    e->got.assign((size_t)LPP_T_COUNT * c.n_layers, 0);
+
+    auto bail = [&](lpp_status s) {
+        lpp_engine_destroy(e);
+        return s;
+    };
+#define CUB(call)                                                                                              \
+    do {                                                                                                       \
+        cudaError_t e_ = (call);                                                                               \
+        if (e_ != cudaSuccess)                                                                                 \
+            return bail(fail(LPP_ERR_CUDA, "%s failed: %s (%s:%d)", #call, cudaGetErrorString(e_), __FILE__, __LINE__)); \
+    } while (0)
+    CUB(cudaStreamCreateWithFlags(&e->stream, cudaStreamNonBlocking));
+    CUB(cudaEventCreate(&e->ev0));
+    CUB(cudaEventCreate(&e->ev1));
+    const size_t D = c.dim, L = c.n_layers, V = c.vocab_size, S = c.seq_len;
+    const size_t esz = e->esz;
+    CUB(cudaMalloc(&e->wqkv, L * (e->Dq + 2 * (size_t)e->KVd) * D * esz));
+    CUB(cudaMalloc(&e->wo, L * D * e->Dq * esz));
+    CUB(cudaMalloc(&e->w13, L * 2 * e->Fl * D * esz));
+    CUB(cudaMalloc(&e->w2, L * D * e->Fl * esz));
+    CUB(cudaMalloc(&e->emb, V * D * esz));
+    CUB(cudaMalloc(&e->rms_att, L * D * 4));
+    CUB(cudaMalloc(&e->rms_ffn, L * D * 4));
+    CUB(cudaMalloc(&e->rms_final, D * 4));
+    const size_t kvbytes = L * e->KVHl * S * hs * e->kvesz;
+    CUB(cudaMalloc(&e->kcache, kvbytes));
+    CUB(cudaMalloc(&e->vcache, kvbytes));
+    CUB(cudaMemsetAsync(e->kcache, 0, kvbytes, e->stream));
+    CUB(cudaMemsetAsync(e->vcache, 0, kvbytes, e->stream));
+    CUB(cudaMalloc(&e->xa, D * 4));
+    CUB(cudaMalloc(&e->xb, D * 4));
+    CUB(cudaMalloc(&e->q, (size_t)e->Dq * 4));
+    CUB(cudaMalloc(&e->att_out, (size_t)e->Dq * 4));
+    CUB(cudaMalloc(&e->hb, (size_t)e->Fl * 4));
+    CUB(cudaMalloc(&e->logits, V * 4));
+    CUB(cudaMalloc(&e->attn_part, (size_t)e->Hl * e->attn_splits * (hs + 2) * 4));
+    CUB(cudaMalloc(&e->attn_counters, (size_t)e->KVHl * e->attn_z * 4));
+    CUB(cudaMemsetAsync(e->attn_counters, 0, (size_t)e->KVHl * e->attn_z * 4, e->stream));
+    CUB(cudaMalloc(&e->samp_max, e->sample_blocks * 4));
+    CUB(cudaMalloc(&e->samp_sum, e->sample_blocks * 4));
+    CUB(cudaMalloc(&e->samp_idx, e->sample_blocks * 4));
+    CUB(cudaMalloc(&e->samp_counter, 4));
+    CUB(cudaMemsetAsync(e->samp_counter, 0, 4, e->stream));
+    e->run_cap = std::max<int>(4096, c.seq_len);
+    CUB(cudaMalloc(&e->r_values, (size_t)e->run_cap * 4));
+    CUB(cudaMalloc(&e->out_tokens, (size_t)e->run_cap * 4));
+    CUB(cudaMalloc(&e->st, sizeof(StepState)));
+    CUB(cudaMemsetAsync(e->st, 0, sizeof(StepState), e->stream));
+    CUB(cudaMallocHost(&e->h_st, sizeof(StepState)));
+    memset(e->h_st, 0, sizeof(StepState));
+    CUB(cudaMallocHost(&e->h_out, 16));
+
+    TRACE("create: buffers allocated");
+    // rope table with libm, evaluated exactly like the reference loop (src/ops.cpp:36-40)
+    {
+        const int half = hs / 2;
+        std::vector<float> freq(half);
+        for (int j = 0; j < half; ++j) {
+            const int head_dim = 2 * j;
+            freq[j] = 1.0f / powf(c.rope_base, head_dim / (float)hs);
+        }
+        std::vector<float2> tab((size_t)S * half);
+        for (size_t p = 0; p < S; ++p)
+            for (int j = 0; j < half; ++j) {
+                const float val = (int)p * freq[j];
+                tab[p * half + j] = make_float2(cosf(val), sinf(val));
+            }
+        CUB(cudaMalloc(&e->rope, tab.size() * sizeof(float2)));
+        CUB(cudaMemcpy(e->rope, tab.data(), tab.size() * sizeof(float2), cudaMemcpyHostToDevice));
+    }
+
+    if (c.tp_size > 1) {
+        if (!nccl::load()) return bail(fail(LPP_ERR_NCCL, "cannot load libnccl.so.2: %s", dlerror()));
+        nccl::unique_id id;
+        memcpy(&id, nccl_id, sizeof id);
+        nccl::result_t r = nccl::CommInitRank(&e->comm, c.tp_size, id, c.tp_rank);
+        if (r != 0) return bail(fail(LPP_ERR_NCCL, "ncclCommInitRank: %s", nccl::GetErrorString(r)));
+    }
+    CUB(cudaStreamSynchronize(e->stream));
+#undef CUB
+    TRACE("create: done");
+    *out = e;
+    return LPP_OK;
+}
+
+extern "C" lpp_status lpp_engine_destroy(lpp_engine* e) {
+    if (!e) return LPP_OK;
+    cudaSetDevice(e->c.device);
+    if (e->stream) cudaStreamSynchronize(e->stream);
+    if (e->g_full) cudaGraphExecDestroy(e->g_full);
+    if (e->g_logits) cudaGraphExecDestroy(e->g_logits);
+    if (e->comm) nccl::CommDestroy(e->comm);
+    void* bufs[] = {e->wqkv, e->wo, e->w13, e->w2, e->emb, e->wcls_owned ? e->wcls : nullptr, e->rms_att, e->rms_ffn,
+                    e->rms_final, e->kcache, e->vcache, e->xa, e->xb, e->q, e->att_out, e->hb, e->logits,
+                    e->attn_part, e->attn_counters, e->samp_max, e->samp_sum, e->samp_idx, e->samp_counter,
+                    e->r_values, e->out_tokens, e->st, e->rope, e->stage};
+    for (void* p : bufs)
+        if (p) cudaFree(p);
+    if (e->h_st) cudaFreeHost(e->h_st);
+    if (e->h_out) cudaFreeHost(e->h_out);
+    if (e->ev0) cudaEventDestroy(e->ev0);
+    if (e->ev1) cudaEventDestroy(e->ev1);
+    if (e->stream) cudaStreamDestroy(e->stream);
+    delete e;
+    return LPP_OK;
+}
+
+extern "C" lpp_status lpp_nccl_unique_id(void* out128) {
+    if (!out128) return fail(LPP_ERR_INVALID_ARG, "null argument");
+    if (!nccl::load()) return fail(LPP_ERR_NCCL, "cannot load libnccl.so.2: %s", dlerror());
+    nccl::unique_id id;
+    nccl::result_t r = nccl::GetUniqueId(&id);
+    if (r != 0) return fail(LPP_ERR_NCCL, "ncclGetUniqueId: %s", nccl::GetErrorString(r));
+    memcpy(out128, &id, sizeof id);
+    return LPP_OK;
+}
+
+// ------------------------------------------------------------------ weight upload
+
+static lpp_status ensure_stage(lpp_engine* e, size_t bytes) {
+    if (bytes <= e->stage_bytes) return LPP_OK;
+    if (e->stage) CU(cudaFree(e->stage));
+    e->stage = nullptr;
+    e->stage_bytes = 0;
+    CU(cudaMalloc(&e->stage, bytes));
+    e->stage_bytes = bytes;
+    return LPP_OK;
+}
+
+// dst[r*dst_pitch + c] (dst_dtype) = src[(r0 + r)*src_pitch + c0 + c] (src_dtype), r < rows, c < cols
+static lpp_status put_block(lpp_engine* e, void* dst, size_t dst_pitch, int dst_dtype, const void* src,
+                            size_t src_pitch, size_t r0, size_t c0, int rows, int cols, int src_dtype, int memkind) {
+    const size_t sesz = src_dtype == LPP_F16 ? 2 : 4;
+    const char* s = (const char*)src + (r0 * src_pitch + c0) * sesz;
+    size_t spitch = src_pitch;
+    if (memkind == LPP_MEM_HOST) {
+        TRY(ensure_stage(e, (size_t)rows * cols * sesz));
+        CU(cudaMemcpy2DAsync(e->stage, (size_t)cols * sesz, s, src_pitch * sesz, (size_t)cols * sesz, rows,
+                             cudaMemcpyHostToDevice, e->stream));
+        s = (const char*)e->stage;
+        spitch = cols;
+    }
+    const long long total = (long long)rows * cols;
+    const int grid = (int)std::min<long long>((total + 255) / 256, 148 * 16);
+    if (dst_dtype == LPP_F16 && src_dtype == LPP_F16)
+        repack_kernel<__half, __half><<<grid, 256, 0, e->stream>>>((__half*)dst, dst_pitch, (const __half*)s, spitch, rows, cols);
+    else if (dst_dtype == LPP_F16 && src_dtype == LPP_F32)
+        repack_kernel<__half, float><<<grid, 256, 0, e->stream>>>((__half*)dst, dst_pitch, (const float*)s, spitch, rows, cols);
+    else if (dst_dtype == LPP_F32 && src_dtype == LPP_F16)
+        repack_kernel<float, __half><<<grid, 256, 0, e->stream>>>((float*)dst, dst_pitch, (const __half*)s, spitch, rows, cols);
+    else
+        repack_kernel<float, float><<<grid, 256, 0, e->stream>>>((float*)dst, dst_pitch, (const float*)s, spitch, rows, cols);
+    CU(cudaGetLastError());
+    // the staging buffer is reused by the next call and host memory may be freed by the caller
+    CU(cudaStreamSynchronize(e->stream));
+    return LPP_OK;
+}
+
+extern "C" lpp_status lpp_upload_tensor(lpp_engine* e, int which, int layer, const void* src, int src_dtype,
+                                        int memkind) {
+    if (!e || !src) return fail(LPP_ERR_INVALID_ARG, "null argument");
+    if (which < 0 || which >= LPP_T_COUNT) return fail(LPP_ERR_INVALID_ARG, "unknown tensor id %d", which);
+    if (src_dtype != LPP_F16 && src_dtype != LPP_F32) return fail(LPP_ERR_INVALID_ARG, "bad src_dtype");
+    if (memkind != LPP_MEM_HOST && memkind != LPP_MEM_DEVICE) return fail(LPP_ERR_INVALID_ARG, "bad memkind");
+    const lpp_config& c = e->c;
+    const bool stacked = !(which == LPP_T_TOK_EMB || which == LPP_T_RMS_FINAL || which == LPP_T_W_CLS);
+    if (stacked && (layer < 0 || layer >= c.n_layers)) return fail(LPP_ERR_INVALID_ARG, "layer %d out of range", layer);
+    if (!stacked) layer = 0;
+    CU(cudaSetDevice(c.device));
+    TRACE("upload tensor %d layer %d", which, layer);
+    const size_t D = c.dim, F = c.hidden_dim, V = c.vocab_size, esz = e->esz;
+    const size_t l = layer, r = c.tp_rank;
+    const size_t qkv_rows = e->Dq + 2 * (size_t)e->KVd;
+    const int wd = c.weight_dtype;
+    char* wqkv_l = (char*)e->wqkv + l * qkv_rows * D * esz;
+    char* w13_l = (char*)e->w13 + l * 2 * e->Fl * D * esz;
+    lpp_status s = LPP_OK;
+    switch (which) {
+        case LPP_T_TOK_EMB:
+            s = put_block(e, e->emb, D, wd, src, D, 0, 0, (int)V, (int)D, src_dtype, memkind);
+            break;
+        case LPP_T_W_CLS:
+            if (!e->wcls_owned) {
+                CU(cudaMalloc(&e->wcls, V * D * esz));
+                e->wcls_owned = true;
+            }
+            s = put_block(e, e->wcls, D, wd, src, D, 0, 0, (int)V, (int)D, src_dtype, memkind);
+            break;
+        case LPP_T_RMS_ATT:
+            s = put_block(e, e->rms_att + l * D, D, LPP_F32, src, D, 0, 0, 1, (int)D, src_dtype, memkind);
+            break;
+        case LPP_T_RMS_FFN:
+            s = put_block(e, e->rms_ffn + l * D, D, LPP_F32, src, D, 0, 0, 1, (int)D, src_dtype, memkind);
+            break;
+        case LPP_T_RMS_FINAL:
+            s = put_block(e, e->rms_final, D, LPP_F32, src, D, 0, 0, 1, (int)D, src_dtype, memkind);
+            break;
+        case LPP_T_WQ:  // row slice of [D][D]
+            s = put_block(e, wqkv_l, D, wd, src, D, r * e->Dq, 0, e->Dq, (int)D, src_dtype, memkind);
+            break;
+        case LPP_T_WK:  // row slice of [KV][D]
+            s = put_block(e, wqkv_l + (size_t)e->Dq * D * esz, D, wd, src, D, r * e->KVd, 0, e->KVd, (int)D, src_dtype, memkind);
+            break;
+        case LPP_T_WV:
+            s = put_block(e, wqkv_l + ((size_t)e->Dq + e->KVd) * D * esz, D, wd, src, D, r * e->KVd, 0, e->KVd, (int)D, src_dtype, memkind);
+            break;
+        case LPP_T_WO:  // column slice of [D][D] (columns = this rank's heads), repacked contiguous
+            s = put_block(e, (char*)e->wo + l * D * e->Dq * esz, e->Dq, wd, src, D, 0, r * e->Dq, (int)D, e->Dq, src_dtype, memkind);
+            break;
+        case LPP_T_W1:  // gate rows -> even rows of w13
+            s = put_block(e, w13_l, 2 * D, wd, src, D, r * e->Fl, 0, e->Fl, (int)D, src_dtype, memkind);
+            break;
+        case LPP_T_W3:  // up rows -> odd rows of w13
+            s = put_block(e, w13_l + D * esz, 2 * D, wd, src, D, r * e->Fl, 0, e->Fl, (int)D, src_dtype, memkind);
+            break;
+        case LPP_T_W2:  // column slice of [D][F]
+            s = put_block(e, (char*)e->w2 + l * D * e->Fl * esz, e->Fl, wd, src, F, 0, r * e->Fl, (int)D, e->Fl, src_dtype, memkind);
+            break;
+    }
+    TRY(s);
+    e->got[(size_t)which * c.n_layers + layer] = 1;
+    e->finalized = false;
+    return LPP_OK;
+}
+
+extern "C" lpp_status lpp_finalize(lpp_engine* e) {
+    if (!e) return fail(LPP_ERR_INVALID_ARG, "null argument");
+    const lpp_config& c = e->c;
+    CU(cudaSetDevice(c.device));
+    static const char* names[LPP_T_COUNT] = {"tok_emb", "rms_att", "wq", "wk", "wv", "wo", "rms_ffn", "w1", "w2", "w3", "rms_final", "w_cls"};
+    for (int t = 0; t < LPP_T_COUNT; ++t) {
+        if (t == LPP_T_W_CLS) continue;
+        const bool stacked = !(t == LPP_T_TOK_EMB || t == LPP_T_RMS_FINAL);
+        const int n = stacked ? c.n_layers : 1;
+        for (int l = 0; l < n; ++l)
+            if (!e->got[(size_t)t * c.n_layers + l])
+                return fail(LPP_ERR_NOT_READY, "tensor %s (layer %d) was never uploaded", names[t], l);
+    }
+    if (!e->wcls_owned) e->wcls = e->emb;  // tied classifier (src/loader.cpp:66, 471)
+    if (e->stage) {
+        cudaFree(e->stage);
+        e->stage = nullptr;
+        e->stage_bytes = 0;
+    }
+    if (e->g_full) cudaGraphExecDestroy(e->g_full), e->g_full = nullptr;
+    if (e->g_logits) cudaGraphExecDestroy(e->g_logits), e->g_logits = nullptr;
+    TRACE("finalize: weights complete");
+    if (!(c.flags & LPP_FLAG_NO_GRAPH)) {
+        TRY(capture(e, true, &e->g_full, &e->kernels_full));
+        TRACE("finalize: full graph captured (%d kernels)", e->kernels_full);
+        TRY(capture(e, false, &e->g_logits, nullptr));
+        TRACE("finalize: logits graph captured");
+    } else {
+        e->kernels_full = 5 * c.n_layers + 2;
+    }
+    e->finalized = true;
+    return LPP_OK;
+}
+
+// ------------------------------------------------------------------ stepping
+
+static lpp_status push_state(lpp_engine* e, int token, int pos, const lpp_sample_params* sp, const int* hist,
+                             int hist_len, float r, int advance, int window) {
+    const lpp_config& c = e->c;
+    if (token < 0 || token >= c.vocab_size) return fail(LPP_ERR_INVALID_ARG, "token %d outside [0, %d)", token, c.vocab_size);
+    if (pos < 0 || pos >= c.seq_len) return fail(LPP_ERR_INVALID_ARG, "pos %d outside [0, %d)", pos, c.seq_len);
+    if (hist_len < 0 || hist_len > kHistoryMax) return fail(LPP_ERR_TOO_LARGE, "history_len %d > %d", hist_len, kHistoryMax);
+    StepState* h = e->h_st;
+    h->token = token;
+    h->pos = pos;
+    const bool use_hist = sp && sp->penalty > 1.0f && hist && hist_len > 0;
+    h->history_len = use_hist || advance ? (hist ? hist_len : 0) : 0;
+    h->history_window = window;
+    h->history_count = h->history_len;
+    h->step_idx = 0;
+    h->advance = advance;
+    h->temperature = sp ? sp->temperature : 0.f;
+    h->penalty = sp ? sp->penalty : 1.f;
+    h->r = r;
+    h->out_token = -1;
+    h->status = 0;
+    if (h->history_len > 0) memcpy(h->history, hist, (size_t)h->history_len * sizeof(int));
+    const size_t bytes = offsetof(StepState, history) + (size_t)h->history_len * sizeof(int);
+    CU(cudaMemcpyAsync(e->st, h, bytes, cudaMemcpyHostToDevice, e->stream));
+    return LPP_OK;
+}
+
+static lpp_status pull_result(lpp_engine* e, int* token) {
+    TRACE("pull_result: waiting for the stream");
+    CU(cudaMemcpyAsync(e->h_out, &e->st->out_token, 2 * sizeof(int), cudaMemcpyDeviceToHost, e->stream));
+    CU(cudaStreamSynchronize(e->stream));
+    if (e->h_out[1] != 0) return fail(LPP_ERR_DEVICE_STATUS, "device status 0x%x (1=barrier timeout, 2=bad token, 4=bad pos)", e->h_out[1]);
+    if (token) *token = e->h_out[0];
+    return LPP_OK;
+}
+
+#define NEED_READY(e)                                                              \
+    do {                                                                           \
+        if (!(e)) return fail(LPP_ERR_INVALID_ARG, "null engine");                 \
+        if (!(e)->finalized) return fail(LPP_ERR_NOT_READY, "lpp_finalize not called"); \
+        CU(cudaSetDevice((e)->c.device));                                          \
+    } while (0)
+
+extern "C" lpp_status lpp_step(lpp_engine* e, int token, int pos, const lpp_sample_params* sp, const int* h_history,
+                               int history_len, float r, int* next_token) {
+    NEED_READY(e);
+    if (!sp || !next_token) return fail(LPP_ERR_INVALID_ARG, "null argument");
+    TRY(push_state(e, token, pos, sp, h_history, history_len, r, 0, 0));
+    TRY(run_step(e, true));
+    return pull_result(e, next_token);
+}
+
+extern "C" lpp_status lpp_step_logits(lpp_engine* e, int token, int pos, float* h_logits) {
+    NEED_READY(e);
+    if (!h_logits) return fail(LPP_ERR_INVALID_ARG, "null argument");
+    TRY(push_state(e, token, pos, nullptr, nullptr, 0, 0.f, 0, 0));
+    TRY(run_step(e, false));
+    CU(cudaMemcpyAsync(h_logits, e->logits, (size_t)e->c.vocab_size * 4, cudaMemcpyDeviceToHost, e->stream));
+    return pull_result(e, nullptr);
+}
+
+extern "C" lpp_status lpp_decode(lpp_engine* e, int first_token, int start_pos, int n, const lpp_sample_params* sp,
+                                 const int* h_history, int history_len, int history_window, const float* h_r,
+                                 int* h_out_tokens, float* device_ms) {
+    NEED_READY(e);
+    if (!sp || !h_out_tokens || n <= 0) return fail(LPP_ERR_INVALID_ARG, "bad argument");
+    if (n > e->run_cap) return fail(LPP_ERR_TOO_LARGE, "n %d > capacity %d", n, e->run_cap);
+    if (start_pos + n > e->c.seq_len) return fail(LPP_ERR_INVALID_ARG, "start_pos + n exceeds seq_len %d", e->c.seq_len);
+    if (history_window < 0 || history_window > kHistoryMax || history_len > std::max(history_window, 0))
+        return fail(LPP_ERR_INVALID_ARG, "history_len %d / window %d invalid", history_len, history_window);
+    if (sp->temperature != 0.0f && !h_r) return fail(LPP_ERR_INVALID_ARG, "temperature > 0 needs h_r");
+    TRY(push_state(e, first_token, start_pos, sp, h_history, history_len, 0.f, 1, history_window));
+    if (h_r) CU(cudaMemcpyAsync(e->r_values, h_r, (size_t)n * 4, cudaMemcpyHostToDevice, e->stream));
+    CU(cudaEventRecord(e->ev0, e->stream));
+    for (int i = 0; i < n; ++i) TRY(run_step(e, true));
+    CU(cudaEventRecord(e->ev1, e->stream));
+    CU(cudaMemcpyAsync(h_out_tokens, e->out_tokens, (size_t)n * 4, cudaMemcpyDeviceToHost, e->stream));
+    TRY(pull_result(e, nullptr));
+    if (device_ms) CU(cudaEventElapsedTime(device_ms, e->ev0, e->ev1));
+    return LPP_OK;
+}
+
+extern "C" lpp_status lpp_sample_logits(lpp_engine* e, const float* h_logits, const lpp_sample_params* sp,
+                                        const int* h_history, int history_len, float r, int* token) {
+    NEED_READY(e);
+    if (!h_logits || !sp || !token) return fail(LPP_ERR_INVALID_ARG, "null argument");
+    TRY(push_state(e, 0, 0, sp, h_history, history_len, r, 0, 0));
+    CU(cudaMemcpyAsync(e->logits, h_logits, (size_t)e->c.vocab_size * 4, cudaMemcpyHostToDevice, e->stream));
+    SampleArgs a = {};
+    a.logits = e->logits;
+    a.vocab = e->c.vocab_size;
+    a.st = e->st;
+    a.part_max = e->samp_max;
+    a.part_idx = e->samp_idx;
+    a.part_sum = e->samp_sum;
+    a.counter = e->samp_counter;
+    a.r_values = e->r_values;
+    a.out_tokens = e->out_tokens;
+    CU(launch_kernel(sample_kernel, dim3(e->sample_blocks), dim3(kSampleThreads), 0, e->stream, false, a));
+    return pull_result(e, token);
+}
+
+// ------------------------------------------------------------------ KV cache access
+
+extern "C" int64_t lpp_kv_index(const lpp_engine* e, int layer, int kv_head, int pos, int off) {
+    if (!e) return -1;
+    const int64_t kvd = (int64_t)e->KVHl * e->hs, S = e->c.seq_len;
+    return (int64_t)layer * (kvd * S) + (int64_t)kv_head * (S * e->hs) + (int64_t)pos * e->hs + off;
+}
+
+extern "C" lpp_status lpp_kv_prefill(lpp_engine* e, int layer, const void* k, const void* v, int n_pos, int src_dtype,
+                                     int memkind) {
+    if (!e || !k || !v) return fail(LPP_ERR_INVALID_ARG, "null argument");
+    const lpp_config& c = e->c;
+    if (layer < 0 || layer >= c.n_layers || n_pos < 0 || n_pos > c.seq_len) return fail(LPP_ERR_INVALID_ARG, "layer/n_pos out of range");
+    if (src_dtype != LPP_F16 && src_dtype != LPP_F32) return fail(LPP_ERR_INVALID_ARG, "bad src_dtype");
+    CU(cudaSetDevice(c.device));
+    const int hs = e->hs;
+    for (int h = 0; h < e->KVHl; ++h) {
+        const size_t gh = (size_t)c.tp_rank * e->KVHl + h;  // global kv head
+        const size_t dst = (size_t)lpp_kv_index(e, layer, h, 0, 0) * e->kvesz;
+        // source rows [gh][0..n_pos) are contiguous: one block of n_pos rows x hs columns
+        TRY(put_block(e, (char*)e->kcache + dst, hs, c.kv_dtype, k, hs, gh * n_pos, 0, n_pos, hs, src_dtype, memkind));
+        TRY(put_block(e, (char*)e->vcache + dst, hs, c.kv_dtype, v, hs, gh * n_pos, 0, n_pos, hs, src_dtype, memkind));
+    }
+    if (e->stage && e->finalized) {
+        cudaFree(e->stage);
+        e->stage = nullptr;
+        e->stage_bytes = 0;
+    }
+    return LPP_OK;
+}
+
+extern "C" lpp_status lpp_kv_read(lpp_engine* e, int layer, int kv_head, int pos, float* h_k, float* h_v) {
+    if (!e || !h_k || !h_v) return fail(LPP_ERR_INVALID_ARG, "null argument");
+    const lpp_config& c = e->c;
+    if (layer < 0 || layer >= c.n_layers || kv_head < 0 || kv_head >= e->KVHl || pos < 0 || pos >= c.seq_len)
+        return fail(LPP_ERR_INVALID_ARG, "index out of range");
+    CU(cudaSetDevice(c.device));
+    const size_t off = (size_t)lpp_kv_index(e, layer, kv_head, pos, 0) * e->kvesz;
+    const int hs = e->hs;
+    CU(cudaStreamSynchronize(e->stream));
+    if (c.kv_dtype == LPP_F32) {
+        CU(cudaMemcpy(h_k, (char*)e->kcache + off, hs * 4, cudaMemcpyDeviceToHost));
+        CU(cudaMemcpy(h_v, (char*)e->vcache + off, hs * 4, cudaMemcpyDeviceToHost));
+    } else {
+        std::vector<__half> tk(hs), tv(hs);
+        CU(cudaMemcpy(tk.data(), (char*)e->kcache + off, hs * 2, cudaMemcpyDeviceToHost));
+        CU(cudaMemcpy(tv.data(), (char*)e->vcache + off, hs * 2, cudaMemcpyDeviceToHost));
+        for (int i = 0; i < hs; ++i) {
+            h_k[i] = __half2float(tk[i]);
+            h_v[i] = __half2float(tv[i]);
+        }
+    }
+    return LPP_OK;
+}
+
+// ------------------------------------------------------------------ introspection
+
+extern "C" const char* lpp_strerror(int s) {
+    switch (s) {
+        case LPP_OK: return "ok";
+        case LPP_ERR_INVALID_ARG: return "invalid argument";
+        case LPP_ERR_CUDA: return "CUDA error";
+        case LPP_ERR_NOT_READY: return "engine not ready";
+        case LPP_ERR_NCCL: return "NCCL error";
+        case LPP_ERR_DEVICE_STATUS: return "device reported an error status";
+        case LPP_ERR_TOO_LARGE: return "request exceeds capacity";
+        case LPP_ERR_NO_DEVICE: return "no usable CUDA device";
+    }
+    return "unknown status";
+}
+extern "C" const char* lpp_last_error(void) { return g_err.c_str(); }
+extern "C" void* lpp_engine_stream(lpp_engine* e) { return e ? (void*)e->stream : nullptr; }
+extern "C" int lpp_kernels_per_step(const lpp_engine* e) { return e ? e->kernels_full : 0; }
+
+static void kind_bytes(const lpp_engine* e, int pos, int64_t* b) {
+    const lpp_config& c = e->c;
+    const int64_t D = c.dim, L = c.n_layers, V = c.vocab_size, esz = e->esz;
+    for (int k = 0; k < kKinds; ++k) b[k] = 0;
+    b[kQkv] = L * ((int64_t)(e->Dq + 2 * e->KVd) * D * esz + 4 * D) + 4 * D;  // + att norms + embedding row
+    b[kAttn] = L * (int64_t)e->kvesz * 2 * e->KVd * ((int64_t)pos + 1) + L * (int64_t)e->kvesz * 2 * e->KVd;
+    b[kOproj] = L * D * e->Dq * esz;
+    b[kGateUp] = L * ((int64_t)2 * e->Fl * D * esz + 4 * D);
+    b[kDown] = L * D * e->Fl * esz;
+    b[kLmHead] = V * D * esz + 4 * D;
+}
+extern "C" int64_t lpp_step_bytes(const lpp_engine* e, int pos) {
+    if (!e) return 0;
+    int64_t b[kKinds], t = 0;
+    kind_bytes(e, pos, b);
+    for (int k = 0; k < kKinds; ++k) t += b[k];
+    return t;
+}
+
+extern "C" lpp_status lpp_profile_step(lpp_engine* e, int pos, int iters, float* ms, int* launches, int64_t* bytes) {
+    NEED_READY(e);
+    if (!ms || !launches || !bytes || iters <= 0) return fail(LPP_ERR_INVALID_ARG, "bad argument");
+    if (pos < 0 || pos >= e->c.seq_len) return fail(LPP_ERR_INVALID_ARG, "pos out of range");
+    for (int k = 0; k < kKinds; ++k) ms[k] = 0.f, launches[k] = 0;
+    kind_bytes(e, pos, bytes);
+    lpp_sample_params sp = {0.f, 1.f};
+    lpp_status rs = LPP_OK;
+    for (int it = 0; it < iters + 1 && rs == LPP_OK; ++it) {  // iteration 0 is a warm-up
+        rs = push_state(e, 0, pos, &sp, nullptr, 0, 0.f, 0, 0);
+        if (rs != LPP_OK) break;
+        e->profiling = true;
+        Recorder R{e, e->stream};
+        record_step(R, true);
+        e->profiling = false;
+        cudaError_t se = cudaStreamSynchronize(e->stream);
+        if (R.err != cudaSuccess || se != cudaSuccess)
+            rs = fail(LPP_ERR_CUDA, "profile step: %s", cudaGetErrorString(R.err != cudaSuccess ? R.err : se));
+        for (size_t i = 0; i + 1 < e->prof_events.size() && rs == LPP_OK; i += 2) {
+            float t = 0.f;
+            cudaEventElapsedTime(&t, e->prof_events[i], e->prof_events[i + 1]);
+            if (it > 0) {
+                ms[e->prof_kinds[i]] += t / iters;
+                if (it == 1) launches[e->prof_kinds[i]]++;
+            }
+        }
+        for (cudaEvent_t ev : e->prof_events) cudaEventDestroy(ev);
+        e->prof_events.clear();
+        e->prof_kinds.clear();
+    }
+    return rs;
+}

@@ -1,0 +1,432 @@
+// Batch-1 streaming GEMV family: out[n] = W[n,K] . x[K] with FP16 or FP32 weights, FP32 activations
+// and FP32 accumulation.  One kernel template serves every matrix of the decode step; what differs
+// is the prologue (plain vector, RMSNorm'd vector, embedding row) and the epilogue (store,
+// residual add, SwiGLU, RoPE + KV-cache scatter).
+//
+// Replaces, from the reference tree: gemv_kernel / gemv_f16_kernel / convert_f32_to_f16_kernel
+// (src/matmul.cu:9-161), rmsnorm (src/RMSNorm.cu:11-71, fused as prologue), swiglu_kernel
+// (src/swiglu.cu:6-33) and residual_add_kernel (src/residual.cu:5-31) as epilogues, rope_kernel +
+// scatter_kv_kernel (src/rope.cu:7-38, src/scatter_kv.cu:6-26) as the QKV epilogue.  Numerics
+// follow the reference CPU path (src/ops.cpp): activations stay FP32 (the reference GPU kernel
+// rounds x to FP16 and accumulates in half2, src/matmul.cu:85-99 -- deliberately not copied).
+//
+// Data movement, ring variant: each CTA owns a contiguous range of row pairs.  A producer warp
+// streams that range through a shared-memory ring with 1-D bulk async copies (one elected lane,
+// completion counted in bytes on an mbarrier); eight consumer warps each take whole stages, so the
+// main loop has no CTA-wide barrier.  Ring slots are shared by all warps, but the "data ready"
+// barriers are private to a consumer warp: warps drift apart by up to a ring's worth of stages, and
+// a parity wait is only unambiguous if the waiter visits every phase of its barrier in order.  The producer starts before the programmatic
+// dependency wait -- weights do not depend on the previous kernel -- so the ring is already full
+// when the activations arrive.  HBM traffic = the matrix once; x is re-read from L2 per CTA.
+#pragma once
+#include "common.cuh"
+
+namespace lpp {
+
+enum GemvEpi : int { kEpiStore = 0, kEpiResid = 1, kEpiSwiglu = 2, kEpiQkv = 3 };
+
+constexpr int kGemvConsumerWarps = 8;
+constexpr int kGemvRingThreads = (kGemvConsumerWarps + 1) * 32;  // + producer warp
+constexpr int kGemvLdgThreads = 256;
+constexpr int kGemvMaxStages = 64;
+// one "full" barrier array per consumer warp plus one "empty" barrier per ring slot
+constexpr int kGemvBarrierBytes = (kGemvConsumerWarps + 1) * kGemvMaxStages * 8;
+constexpr int kRowsPerGroup = 2;                           // rows handled together by one warp
+
+struct GemvArgs {
+    const void* W;  // [n_rows][K] row-major, element type WT
+    int n_rows, K;
+    // ---- prologue
+    const float* x;       // input vector [K] (ignored when emb != nullptr)
+    const float* norm_w;  // RMSNorm weight [K], nullptr = no normalisation
+    const void* emb;      // embedding table [vocab][K] in the weight dtype, nullptr = use x
+    float* x_store;       // CTA 0 stores the un-normalised input vector here (nullptr = don't)
+    StepState* st;        // token / pos / status
+    int vocab, seq_len;
+    // ---- epilogue
+    float* out;          // Store/Resid: [n_rows]; Swiglu: [n_rows/2]; Qkv: q vector [q_rows]
+    const float* resid;  // Resid: added to the result when non-null
+    int q_rows, kv_rows, head_size;  // Qkv: rows are q | k | v
+    const float2* rope;              // Qkv: [seq_len][head_size/2] (cos, sin)
+    void* k_cache;                   // Qkv: this layer's K cache [kv_heads][seq_len][head_size]
+    void* v_cache;
+    int kv_is_f32;
+    // ---- ring geometry (host-computed)
+    int kc;           // K elements per stage row (multiple of 8)
+    int n_stages;     // ring slots
+    int stage_bytes;  // bytes per slot = kRowsPerGroup * kc * sizeof(WT)
+};
+
+// ------------------------------------------------------------------ x staging layouts
+//
+// FP16 weights: a lane multiplies 8 consecutive weights (one 16-byte vector) with 8 consecutive x.
+// To keep both 16-byte x reads bank-conflict free the low and high halves of every 8-group live in
+// two separate planes.  FP32 weights: one 16-byte vector = 4 weights, x is stored naturally.
+template <typename WT>
+__device__ __forceinline__ int xs_index(int k, int K);
+template <>
+__device__ __forceinline__ int xs_index<__half>(int k, int K) {
+    return ((k >> 3) << 2) + (k & 3) + ((k & 4) ? (K >> 1) : 0);
+}
+template <>
+__device__ __forceinline__ int xs_index<float>(int k, int /*K*/) {
+    return k;
+}
+
+__device__ __forceinline__ void consumer_barrier(int nthreads) {
+    asm volatile("bar.sync 1, %0;" ::"r"(nthreads) : "memory");
+}
+
+// Stores four consecutive inputs x[k..k+3] (k % 4 == 0) into the staging layout.
+template <typename WT>
+__device__ __forceinline__ void xs_store4(float* xs, int k, int K, float4 v) {
+    if constexpr (sizeof(WT) == 2)
+        *reinterpret_cast<float4*>(xs + ((k >> 3) << 2) + ((k & 4) ? (K >> 1) : 0)) = v;
+    else
+        *reinterpret_cast<float4*>(xs + k) = v;
+}
+
+// Waits for the producing kernel, loads the input vector (embedding row or x), optionally
+// RMS-normalises it (ss = 1/sqrt(mean(x^2) + 1e-5); out = x*ss*w, src/ops.cpp:20-32) and leaves it
+// in shared memory in the layout xs_index<WT> describes.  Executed by `NT` threads (tid 0..NT-1).
+// The norm weights are constants, so their loads are issued before the dependency wait.
+template <typename WT, int NT>
+__device__ __forceinline__ void stage_input(const GemvArgs& a, float* xs, float* red, int tid) {
+    const int K = a.K;
+    const int nv4 = K >> 2;
+    constexpr int kPer = 4;  // float4 per thread and pass: one pass covers 4*4*NT inputs
+    const bool one_pass = nv4 <= kPer * NT;
+    float4 wr[kPer];
+    if (a.norm_w && one_pass) {
+#pragma unroll
+        for (int j = 0; j < kPer; ++j) {
+            const int i = tid + j * NT;
+            if (i < nv4) wr[j] = __ldg(reinterpret_cast<const float4*>(a.norm_w) + i);
+        }
+    }
+    pdl_wait();  // activations / KV / step state come from the previous kernel
+
+    if (a.emb) {
+        // first layer: the input is the embedding row of the device-resident token, widened exactly
+        int tok = a.st->token;
+        if (tok < 0 || tok >= a.vocab) {
+            if (tid == 0) atomicOr(&a.st->status, kStatusBadToken);
+            tok = 0;
+        }
+        const WT* erow = reinterpret_cast<const WT*>(a.emb) + (size_t)tok * K;
+        const bool store = a.x_store && blockIdx.x == 0;
+        float ss = 0.f;
+        for (int k = tid; k < K; k += NT) {
+            float v;
+            if constexpr (sizeof(WT) == 2)
+                v = __half2float(erow[k]);
+            else
+                v = erow[k];
+            ss = fmaf(v, v, ss);
+            if (store) a.x_store[k] = v;
+            xs[xs_index<WT>(k, K)] = v;
+        }
+        if (a.norm_w) {
+            ss = warp_sum(ss);
+            if ((tid & 31) == 0) red[tid >> 5] = ss;
+            consumer_barrier(NT);
+            float tot = 0.f;
+#pragma unroll
+            for (int w = 0; w < NT / 32; ++w) tot += red[w];
+            const float scale = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(tot, (float)K), 1e-5f)));
+            for (int k = tid; k < K; k += NT) {
+                const int i = xs_index<WT>(k, K);
+                xs[i] = __fmul_rn(__fmul_rn(xs[i], scale), a.norm_w[k]);
+            }
+        }
+        consumer_barrier(NT);
+        return;
+    }
+
+    const float4* x4 = reinterpret_cast<const float4*>(a.x);
+    if (!a.norm_w) {
+        for (int i = tid; i < nv4; i += NT) xs_store4<WT>(xs, i << 2, K, __ldcg(x4 + i));
+        consumer_barrier(NT);
+        return;
+    }
+    float ss = 0.f;
+    float4 xr[kPer];
+    if (one_pass) {
+#pragma unroll
+        for (int j = 0; j < kPer; ++j) {
+            const int i = tid + j * NT;
+            if (i < nv4) xr[j] = __ldcg(x4 + i);
+        }
+#pragma unroll
+        for (int j = 0; j < kPer; ++j) {
+            const int i = tid + j * NT;
+            if (i < nv4) ss = fmaf(xr[j].x, xr[j].x, fmaf(xr[j].y, xr[j].y, fmaf(xr[j].z, xr[j].z, fmaf(xr[j].w, xr[j].w, ss))));
+        }
+    } else {
+        for (int i = tid; i < nv4; i += NT) {
+            const float4 v = __ldcg(x4 + i);
+            ss = fmaf(v.x, v.x, fmaf(v.y, v.y, fmaf(v.z, v.z, fmaf(v.w, v.w, ss))));
+        }
+    }
+    ss = warp_sum(ss);
+    if ((tid & 31) == 0) red[tid >> 5] = ss;
+    consumer_barrier(NT);
+    float tot = 0.f;
+#pragma unroll
+    for (int w = 0; w < NT / 32; ++w) tot += red[w];
+    const float scale = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(tot, (float)K), 1e-5f)));
+    auto normed = [&](float4 v, float4 w) {
+        return make_float4(__fmul_rn(__fmul_rn(v.x, scale), w.x), __fmul_rn(__fmul_rn(v.y, scale), w.y),
+                           __fmul_rn(__fmul_rn(v.z, scale), w.z), __fmul_rn(__fmul_rn(v.w, scale), w.w));
+    };
+    if (one_pass) {
+#pragma unroll
+        for (int j = 0; j < kPer; ++j) {
+            const int i = tid + j * NT;
+            if (i < nv4) xs_store4<WT>(xs, i << 2, K, normed(xr[j], wr[j]));
+        }
+    } else {
+        for (int i = tid; i < nv4; i += NT)
+            xs_store4<WT>(xs, i << 2, K, normed(__ldcg(x4 + i), __ldg(reinterpret_cast<const float4*>(a.norm_w) + i)));
+    }
+    consumer_barrier(NT);
+}
+
+// Dot products of kRowsPerGroup weight rows (klen elements each, 16-byte aligned, anywhere
+// addressable: shared or global) with x[k0 .. k0+klen) from shared memory.  Lane-strided over
+// 16-byte vectors.
+template <typename WT, bool kFromGlobal>
+__device__ __forceinline__ void dot_rows(const unsigned char* row0, const unsigned char* row1, const float* xs,
+                                         int K, int k0, int klen, int lane, float& acc0, float& acc1) {
+    float a0 = 0.f, a1 = 0.f, b0 = 0.f, b1 = 0.f;
+    if constexpr (sizeof(WT) == 2) {
+        const int nvec = klen >> 3;
+        const float4* xlo = reinterpret_cast<const float4*>(xs) + (k0 >> 3);
+        const float4* xhi = reinterpret_cast<const float4*>(xs + (K >> 1)) + (k0 >> 3);
+        const uint4* r0 = reinterpret_cast<const uint4*>(row0);
+        const uint4* r1 = reinterpret_cast<const uint4*>(row1);
+#pragma unroll 4
+        for (int v = lane; v < nvec; v += 32) {
+            uint4 w0, w1;
+            if constexpr (kFromGlobal) {
+                w0 = ldg_stream_u4(r0 + v);
+                w1 = ldg_stream_u4(r1 + v);
+            } else {
+                w0 = r0[v];
+                w1 = r1[v];
+            }
+            const float4 xl = xlo[v], xh = xhi[v];
+            float2 p;
+            p = half2_bits_to_float2(w0.x); a0 = fmaf(p.x, xl.x, a0); b0 = fmaf(p.y, xl.y, b0);
+            p = half2_bits_to_float2(w0.y); a0 = fmaf(p.x, xl.z, a0); b0 = fmaf(p.y, xl.w, b0);
+            p = half2_bits_to_float2(w0.z); a0 = fmaf(p.x, xh.x, a0); b0 = fmaf(p.y, xh.y, b0);
+            p = half2_bits_to_float2(w0.w); a0 = fmaf(p.x, xh.z, a0); b0 = fmaf(p.y, xh.w, b0);
+            p = half2_bits_to_float2(w1.x); a1 = fmaf(p.x, xl.x, a1); b1 = fmaf(p.y, xl.y, b1);
+            p = half2_bits_to_float2(w1.y); a1 = fmaf(p.x, xl.z, a1); b1 = fmaf(p.y, xl.w, b1);
+            p = half2_bits_to_float2(w1.z); a1 = fmaf(p.x, xh.x, a1); b1 = fmaf(p.y, xh.y, b1);
+            p = half2_bits_to_float2(w1.w); a1 = fmaf(p.x, xh.z, a1); b1 = fmaf(p.y, xh.w, b1);
+        }
+    } else {
+        const int nvec = klen >> 2;
+        const float4* x4 = reinterpret_cast<const float4*>(xs) + (k0 >> 2);
+        const uint4* r0 = reinterpret_cast<const uint4*>(row0);
+        const uint4* r1 = reinterpret_cast<const uint4*>(row1);
+#pragma unroll 4
+        for (int v = lane; v < nvec; v += 32) {
+            uint4 w0, w1;
+            if constexpr (kFromGlobal) {
+                w0 = ldg_stream_u4(r0 + v);
+                w1 = ldg_stream_u4(r1 + v);
+            } else {
+                w0 = r0[v];
+                w1 = r1[v];
+            }
+            const float4 xv = x4[v];
+            a0 = fmaf(__uint_as_float(w0.x), xv.x, a0); b0 = fmaf(__uint_as_float(w0.y), xv.y, b0);
+            a0 = fmaf(__uint_as_float(w0.z), xv.z, a0); b0 = fmaf(__uint_as_float(w0.w), xv.w, b0);
+            a1 = fmaf(__uint_as_float(w1.x), xv.x, a1); b1 = fmaf(__uint_as_float(w1.y), xv.y, b1);
+            a1 = fmaf(__uint_as_float(w1.z), xv.z, a1); b1 = fmaf(__uint_as_float(w1.w), xv.w, b1);
+        }
+    }
+    acc0 += a0 + b0;
+    acc1 += a1 + b1;
+}
+
+// Writes the results of row pair `g` (rows 2g, 2g+1); called by one lane with the warp-reduced sums.
+template <int EPI>
+__device__ __forceinline__ void gemv_epilogue(const GemvArgs& a, int g, float v0, float v1) {
+    const int row = g * kRowsPerGroup;
+    if constexpr (EPI == kEpiStore) {
+        *reinterpret_cast<float2*>(a.out + row) = make_float2(v0, v1);
+    } else if constexpr (EPI == kEpiResid) {
+        // x += W.xb (src/model.cpp:232, 239); under tensor parallelism only rank 0 passes resid
+        if (a.resid) {
+            const float2 r = *reinterpret_cast<const float2*>(a.resid + row);
+            v0 += r.x;
+            v1 += r.y;
+        }
+        *reinterpret_cast<float2*>(a.out + row) = make_float2(v0, v1);
+    } else if constexpr (EPI == kEpiSwiglu) {
+        // rows are interleaved (gate_i, up_i); hb = (h1*sigmoid(h1))*h3 (src/ops.cpp:78-87)
+        const float sig = __fdiv_rn(1.0f, 1.0f + expf(-v0));
+        a.out[g] = __fmul_rn(__fmul_rn(v0, sig), v1);
+    } else {  // kEpiQkv
+        const int pos = a.st->pos;
+        if (pos < 0 || pos >= a.seq_len) {
+            atomicOr(&a.st->status, kStatusBadPos);
+            return;
+        }
+        const int hs = a.head_size;
+        if (row < a.q_rows + a.kv_rows) {
+            // adjacent-pair rotation with the table entry for (pos, (row % hs)/2) (src/ops.cpp:34-54);
+            // separate multiply and subtract/add, as the reference's scalar code rounds
+            const float2 cs = a.rope[(size_t)pos * (hs >> 1) + ((row % hs) >> 1)];
+            const float r0 = __fsub_rn(__fmul_rn(v0, cs.x), __fmul_rn(v1, cs.y));
+            const float r1 = __fadd_rn(__fmul_rn(v0, cs.y), __fmul_rn(v1, cs.x));
+            v0 = r0;
+            v1 = r1;
+        }
+        if (row < a.q_rows) {
+            *reinterpret_cast<float2*>(a.out + row) = make_float2(v0, v1);
+        } else {
+            const bool is_k = row < a.q_rows + a.kv_rows;
+            const int r = row - a.q_rows - (is_k ? 0 : a.kv_rows);
+            const int h = r / hs, off = r % hs;
+            // cache index within the layer: h*(seq_len*hs) + pos*hs + off (src/scatter_kv.cu:15-16)
+            const size_t idx = (size_t)h * ((size_t)a.seq_len * hs) + (size_t)pos * hs + off;
+            void* base = is_k ? a.k_cache : a.v_cache;
+            if (a.kv_is_f32)
+                *reinterpret_cast<float2*>(reinterpret_cast<float*>(base) + idx) = make_float2(v0, v1);
+            else
+                *reinterpret_cast<__half2*>(reinterpret_cast<__half*>(base) + idx) = __floats2half2_rn(v0, v1);
+        }
+    }
+}
+
+// ------------------------------------------------------------------ ring (bulk async copy) variant
+
+template <typename WT, int EPI>
+__global__ void __launch_bounds__(kGemvRingThreads) gemv_ring_kernel(const GemvArgs a) {
+    extern __shared__ __align__(128) unsigned char smem[];
+    uint64_t* fullw = reinterpret_cast<uint64_t*>(smem);                 // [consumer warp][kGemvMaxStages]
+    uint64_t* empty = fullw + kGemvConsumerWarps * kGemvMaxStages;       // [ring slot]
+    float* red = reinterpret_cast<float*>(smem + kGemvBarrierBytes);     // 8 floats
+    float* xs = reinterpret_cast<float*>(smem + kGemvBarrierBytes + 128);
+    unsigned char* ring = smem + kGemvBarrierBytes + 128 + (((size_t)a.K * 4 + 127) & ~(size_t)127);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int NS = a.n_stages;
+    const int groups = a.n_rows / kRowsPerGroup;
+    const int g0 = (int)(((long long)blockIdx.x * groups) / gridDim.x);
+    const int g1 = (int)(((long long)(blockIdx.x + 1) * groups) / gridDim.x);
+    const int ng = g1 - g0;
+    const int nch = (a.K + a.kc - 1) / a.kc;
+    const int total = ng * nch;
+
+    if (tid < NS) {
+#pragma unroll
+        for (int w = 0; w < kGemvConsumerWarps; ++w) mbar_init(&fullw[w * kGemvMaxStages + tid], 1);
+        mbar_init(&empty[tid], 1);
+        mbar_fence_init();
+    }
+    __syncthreads();
+
+    if (warp == kGemvConsumerWarps) {
+        // ---------------- producer: one lane streams this CTA's rows through the ring.
+        // Stage s = (row pair j = s / nch, K-chunk c = s % nch) lands in slot s % NS and is
+        // announced on the barrier of the warp that owns pair j (j % 8), at that warp's own
+        // stage counter.
+        if (lane == 0) {
+            const unsigned char* W = reinterpret_cast<const unsigned char*>(a.W);
+            int j = 0, c = 0;
+            for (int s = 0; s < total; ++s) {
+                const int slot = s % NS, use = s / NS;
+                if (use > 0 && !mbar_wait_bounded(&empty[slot], (use - 1) & 1, &a.st->status)) break;
+                const int w = j & (kGemvConsumerWarps - 1);
+                const int iw = (j >> 3) * nch + c;
+                uint64_t* bar = &fullw[w * kGemvMaxStages + iw % NS];
+                const int g = g0 + j;
+                const int k0 = c * a.kc;
+                const int klen = min(a.kc, a.K - k0);
+                const uint32_t row_bytes = (uint32_t)klen * sizeof(WT);
+                unsigned char* dst = ring + (size_t)slot * a.stage_bytes;
+                mbar_arrive_expect_tx(bar, kRowsPerGroup * row_bytes);
+                if (nch == 1) {
+                    // whole rows: the pair is one contiguous span of the matrix
+                    bulk_g2s(dst, W + (size_t)g * kRowsPerGroup * a.K * sizeof(WT), kRowsPerGroup * row_bytes, bar);
+                } else {
+#pragma unroll
+                    for (int r = 0; r < kRowsPerGroup; ++r)
+                        bulk_g2s(dst + (size_t)r * row_bytes,
+                                 W + ((size_t)(g * kRowsPerGroup + r) * a.K + k0) * sizeof(WT), row_bytes, bar);
+                }
+                if (++c == nch) {
+                    c = 0;
+                    ++j;
+                }
+            }
+            // all of this CTA's HBM requests are issued: let the next kernel start filling its ring
+            pdl_launch_dependents();
+        }
+        return;
+    }
+
+    // ---------------- consumers
+    stage_input<WT, kGemvConsumerWarps * 32>(a, xs, red, tid);
+
+    uint64_t* myfull = fullw + warp * kGemvMaxStages;
+    int iw = 0;  // this warp's stage counter
+    for (int j = warp; j < ng; j += kGemvConsumerWarps) {
+        float acc0 = 0.f, acc1 = 0.f;
+        bool ok = true;
+        for (int c = 0; c < nch; ++c, ++iw) {
+            // warp-uniform outcome: a lane that timed out must not leave the others in __syncwarp
+            if (!__all_sync(0xffffffffu, mbar_wait_bounded(&myfull[iw % NS], (iw / NS) & 1, &a.st->status))) {
+                ok = false;
+                break;
+            }
+            const int slot = (j * nch + c) % NS;
+            const int k0 = c * a.kc;
+            const int klen = min(a.kc, a.K - k0);
+            const unsigned char* st = ring + (size_t)slot * a.stage_bytes;
+            dot_rows<WT, false>(st, st + (size_t)klen * sizeof(WT), xs, a.K, k0, klen, lane, acc0, acc1);
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&empty[slot]);
+        }
+        if (!ok) break;
+        acc0 = warp_sum(acc0);
+        acc1 = warp_sum(acc1);
+        if (lane == 0) gemv_epilogue<EPI>(a, g0 + j, acc0, acc1);
+    }
+}
+
+// ------------------------------------------------------------------ direct-load variant
+//
+// Same partition and epilogues; weights go global -> registers with 128-bit streaming loads.  Kept
+// as the measured alternative to the ring (see profiles/).
+template <typename WT, int EPI>
+__global__ void __launch_bounds__(kGemvLdgThreads) gemv_ldg_kernel(const GemvArgs a) {
+    extern __shared__ __align__(128) unsigned char smem[];
+    float* red = reinterpret_cast<float*>(smem);
+    float* xs = reinterpret_cast<float*>(smem + 128);
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int groups = a.n_rows / kRowsPerGroup;
+    const int g0 = (int)(((long long)blockIdx.x * groups) / gridDim.x);
+    const int g1 = (int)(((long long)(blockIdx.x + 1) * groups) / gridDim.x);
+    constexpr int NW = kGemvLdgThreads / 32;
+
+    stage_input<WT, kGemvLdgThreads>(a, xs, red, tid);
+    const unsigned char* W = reinterpret_cast<const unsigned char*>(a.W);
+    const size_t row_bytes = (size_t)a.K * sizeof(WT);
+    for (int g = g0 + warp; g < g1; g += NW) {
+        float acc0 = 0.f, acc1 = 0.f;
+        const unsigned char* r0 = W + (size_t)g * kRowsPerGroup * row_bytes;
+        dot_rows<WT, true>(r0, r0 + row_bytes, xs, a.K, 0, a.K, lane, acc0, acc1);
+        acc0 = warp_sum(acc0);
+        acc1 = warp_sum(acc1);
+        if (lane == 0) gemv_epilogue<EPI>(a, g, acc0, acc1);
+    }
+    pdl_launch_dependents();
+}
+
+}  // namespace lpp

@@ -1,0 +1,213 @@
+// C-ABI entry points for the stand-alone operators: one per host wrapper of the reference's
+// src/kernels.cuh:24-36, same argument meaning, device pointers in and out, nothing synchronised
+// (like the reference wrappers, callers order work through the stream).
+#include <cuda_runtime.h>
+#include <cuda_fp16.h>
+#include <stddef.h>
+
+#include <algorithm>
+
+#include "../../include/lpp_b200.h"
+#include "common.cuh"
+#include "gemv.cuh"
+#include "ops.cuh"
+#include "sampler.cuh"
+
+using namespace lpp;
+
+namespace {
+
+inline lpp_status chk() { return cudaGetLastError() == cudaSuccess ? LPP_OK : LPP_ERR_CUDA; }
+inline cudaStream_t S(void* s) { return (cudaStream_t)s; }
+inline int blocks(long long n, int t) { return (int)std::max<long long>(1, (n + t - 1) / t); }
+
+// Any-shape fallback for the stand-alone GEMV: one warp per row, scalar loads.
+template <typename WT>
+__global__ void gemv_generic_kernel(float* out, const float* x, const WT* w, int n, int d) {
+    const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
+    if (row >= n) return;
+    const WT* r = w + (size_t)row * d;
+    float acc = 0.f;
+    for (int k = lane; k < d; k += 32) {
+        float wv;
+        if constexpr (sizeof(WT) == 2)
+            wv = __half2float(r[k]);
+        else
+            wv = r[k];
+        acc = fmaf(wv, x[k], acc);
+    }
+    acc = warp_sum(acc);
+    if (lane == 0) out[row] = acc;
+}
+
+// Status word for stand-alone GEMV launches (their bounded waits need somewhere to report).
+__device__ StepState g_op_state;
+
+template <typename WT>
+lpp_status op_gemv_t(float* out, const float* x, const void* w, int n, int d, cudaStream_t s) {
+    const int vec = 16 / (int)sizeof(WT);
+    const size_t smem = 128 + (((size_t)d * 4 + 127) & ~(size_t)127);
+    if ((n & 1) || (d % vec) || (((uintptr_t)w) & 15) || smem > 200 * 1024) {
+        gemv_generic_kernel<WT><<<blocks(n, 8), 256, 0, s>>>(out, x, (const WT*)w, n, d);
+        return chk();
+    }
+    StepState* st = nullptr;
+    if (cudaGetSymbolAddress((void**)&st, g_op_state) != cudaSuccess) return LPP_ERR_CUDA;
+    if (smem > 48 * 1024 &&
+        cudaFuncSetAttribute(gemv_ldg_kernel<WT, kEpiStore>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
+            cudaSuccess)
+        return LPP_ERR_CUDA;
+    GemvArgs a = {};
+    a.W = w;
+    a.n_rows = n;
+    a.K = d;
+    a.x = x;
+    a.out = out;
+    a.st = st;
+    int dev = 0, sms = 148;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    const int grid = std::max(1, std::min(n / kRowsPerGroup, sms * 4));
+    gemv_ldg_kernel<WT, kEpiStore><<<grid, kGemvLdgThreads, smem, s>>>(a);
+    return chk();
+}
+
+}  // namespace
+
+extern "C" {
+
+lpp_status lpp_op_convert_f32_to_f16(void* d_dst, const float* d_src, int64_t n, void* stream) {
+    if (!d_dst || !d_src || n < 0) return LPP_ERR_INVALID_ARG;
+    if (n == 0) return LPP_OK;
+    convert_f32_to_f16_kernel<<<(int)std::min<long long>(blocks(n, 256), 148 * 16), 256, 0, S(stream)>>>(
+        (__half*)d_dst, d_src, n);
+    return chk();
+}
+
+lpp_status lpp_op_gemv(float* d_out, const float* d_x, const void* d_w, int n, int d, int w_dtype, void* stream) {
+    if (!d_out || !d_x || !d_w || n <= 0 || d <= 0) return LPP_ERR_INVALID_ARG;
+    if (w_dtype == LPP_F16) return op_gemv_t<__half>(d_out, d_x, d_w, n, d, S(stream));
+    if (w_dtype == LPP_F32) return op_gemv_t<float>(d_out, d_x, d_w, n, d, S(stream));
+    return LPP_ERR_INVALID_ARG;
+}
+
+lpp_status lpp_op_rmsnorm(float* d_out, const float* d_x, const float* d_w, int n, void* stream) {
+    if (!d_out || !d_x || !d_w || n <= 0) return LPP_ERR_INVALID_ARG;
+    rmsnorm_kernel<<<1, 256, 0, S(stream)>>>(d_out, d_x, d_w, n);
+    return chk();
+}
+
+lpp_status lpp_op_rope(float* d_q, float* d_k, int pos, int dim, int kv_dim, int head_size, float rope_base,
+                       void* stream) {
+    if (!d_q || !d_k || dim <= 0 || (dim & 1) || head_size <= 0 || (head_size & 1)) return LPP_ERR_INVALID_ARG;
+    rope_kernel<<<blocks(dim / 2, 256), 256, 0, S(stream)>>>(d_q, d_k, pos, dim, kv_dim, head_size, rope_base);
+    return chk();
+}
+
+lpp_status lpp_op_swiglu(float* d_hb, const float* d_h1, const float* d_h3, int size, void* stream) {
+    if (!d_hb || !d_h1 || !d_h3 || size <= 0) return LPP_ERR_INVALID_ARG;
+    swiglu_kernel<<<blocks(size, 256), 256, 0, S(stream)>>>(d_hb, d_h1, d_h3, size);
+    return chk();
+}
+
+lpp_status lpp_op_softmax_multihead(float* d_out, const float* d_x, int n_heads, int seq_len, int att_stride,
+                                    void* stream) {
+    if (!d_out || !d_x || n_heads <= 0 || seq_len <= 0) return LPP_ERR_INVALID_ARG;
+    softmax_multihead_kernel<<<n_heads, 256, 0, S(stream)>>>(d_out, d_x, seq_len, att_stride);
+    return chk();
+}
+
+lpp_status lpp_op_scale_multihead(float* d_att, float scale, int n_heads, int seq_len, int att_stride, void* stream) {
+    if (!d_att || n_heads <= 0 || seq_len <= 0) return LPP_ERR_INVALID_ARG;
+    scale_multihead_kernel<<<dim3(blocks(seq_len, 256), n_heads), 256, 0, S(stream)>>>(d_att, scale, seq_len,
+                                                                                        att_stride);
+    return chk();
+}
+
+lpp_status lpp_op_aggregation_multihead(float* d_out, const void* d_v_f16, const float* d_att, int n_heads,
+                                        int seq_len, int head_size, int gqa_factor, int att_stride, void* stream) {
+    if (!d_out || !d_v_f16 || !d_att || n_heads <= 0 || seq_len <= 0 || head_size <= 0 || head_size > 128 ||
+        gqa_factor <= 0)
+        return LPP_ERR_INVALID_ARG;
+    aggregation_multihead_kernel<<<n_heads, 128, 0, S(stream)>>>(d_out, (const __half*)d_v_f16, d_att, seq_len,
+                                                                 head_size, gqa_factor, att_stride);
+    return chk();
+}
+
+lpp_status lpp_op_residual_add(float* d_out, const float* d_a, const float* d_b, int n, void* stream) {
+    if (!d_out || !d_a || !d_b || n <= 0) return LPP_ERR_INVALID_ARG;
+    residual_add_kernel<<<blocks(n, 256), 256, 0, S(stream)>>>(d_out, d_a, d_b, n);
+    return chk();
+}
+
+lpp_status lpp_op_scatter_kv(void* d_kc_f16, void* d_vc_f16, const float* d_k, const float* d_v, int layer, int pos,
+                             int n_kv_heads, int head_size, int seq_len, void* stream) {
+    if (!d_kc_f16 || !d_vc_f16 || !d_k || !d_v || layer < 0 || pos < 0 || pos >= seq_len || n_kv_heads <= 0 ||
+        head_size <= 0)
+        return LPP_ERR_INVALID_ARG;
+    scatter_kv_kernel<<<blocks(n_kv_heads * head_size, 256), 256, 0, S(stream)>>>(
+        (__half*)d_kc_f16, (__half*)d_vc_f16, d_k, d_v, layer, pos, n_kv_heads, head_size, seq_len);
+    return chk();
+}
+
+lpp_status lpp_op_multihead_gemv(float* d_out, const float* d_q, const void* d_k_cache_f16, int layer, int pos,
+                                 int n_heads, int n_kv_heads, int head_size, int seq_len, void* stream) {
+    if (!d_out || !d_q || !d_k_cache_f16 || layer < 0 || pos < 0 || pos >= seq_len || n_heads <= 0 ||
+        n_kv_heads <= 0 || n_heads % n_kv_heads)
+        return LPP_ERR_INVALID_ARG;
+    multihead_gemv_kernel<<<dim3(blocks(pos + 1, 4), n_heads), 128, 0, S(stream)>>>(
+        d_out, d_q, (const __half*)d_k_cache_f16, layer, pos, n_heads, n_kv_heads, head_size, seq_len);
+    return chk();
+}
+
+lpp_status lpp_op_rope_scatter(float* d_q, const float* d_k, const float* d_v, void* d_kc_f16, void* d_vc_f16,
+                               int layer, int pos, int dim, int n_kv_heads, int head_size, int seq_len,
+                               float rope_base, void* stream) {
+    if (!d_q || !d_k || !d_v || !d_kc_f16 || !d_vc_f16 || layer < 0 || pos < 0 || pos >= seq_len || dim <= 0 ||
+        (dim & 1) || (head_size & 1) || head_size <= 0)
+        return LPP_ERR_INVALID_ARG;
+    rope_scatter_kernel<<<blocks(dim / 2, 256), 256, 0, S(stream)>>>(d_q, d_k, d_v, (__half*)d_kc_f16,
+                                                                    (__half*)d_vc_f16, layer, pos, dim, n_kv_heads,
+                                                                    head_size, seq_len, rope_base);
+    return chk();
+}
+
+lpp_status lpp_op_sample(float* d_logits, int vocab_size, float temperature, float penalty, const int* d_history,
+                         int history_len, float r, int* d_sampled_token, void* stream) {
+    if (!d_logits || !d_sampled_token || vocab_size <= 0 || history_len < 0 || history_len > kHistoryMax)
+        return LPP_ERR_INVALID_ARG;
+    cudaStream_t s = S(stream);
+    const int nb = (vocab_size + kSampleChunk - 1) / kSampleChunk;
+    if (nb > kSampleMaxBlocks) return LPP_ERR_TOO_LARGE;
+    // stream-ordered scratch: step state + per-block partials + ticket counter
+    const size_t st_bytes = (sizeof(StepState) + 255) & ~(size_t)255;
+    const size_t bytes = st_bytes + (size_t)nb * 12 + 256;
+    char* scratch = nullptr;
+    if (cudaMallocAsync((void**)&scratch, bytes, s) != cudaSuccess) return LPP_ERR_CUDA;
+    StepState h = {};
+    h.temperature = temperature;
+    h.penalty = penalty;
+    h.r = r;
+    const bool use_hist = penalty > 1.0f && d_history && history_len > 0;
+    h.history_len = use_hist ? history_len : 0;
+    cudaMemcpyAsync(scratch, &h, offsetof(StepState, history), cudaMemcpyHostToDevice, s);
+    if (use_hist)
+        cudaMemcpyAsync(scratch + offsetof(StepState, history), d_history, (size_t)history_len * sizeof(int),
+                        cudaMemcpyDeviceToDevice, s);
+    SampleArgs a = {};
+    a.logits = d_logits;
+    a.vocab = vocab_size;
+    a.st = (StepState*)scratch;
+    a.part_max = (float*)(scratch + st_bytes);
+    a.part_idx = (int*)(scratch + st_bytes + (size_t)nb * 4);
+    a.part_sum = (float*)(scratch + st_bytes + (size_t)nb * 8);
+    a.counter = (unsigned int*)(scratch + st_bytes + (size_t)nb * 12);
+    cudaMemsetAsync(a.counter, 0, 4, s);
+    sample_kernel<<<nb, kSampleThreads, 0, s>>>(a);
+    cudaMemcpyAsync(d_sampled_token, scratch + offsetof(StepState, out_token), sizeof(int), cudaMemcpyDeviceToDevice, s);
+    cudaFreeAsync(scratch, s);
+    return chk();
+}
+
+}  // extern "C"
