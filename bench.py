@@ -1,0 +1,331 @@
+#!/usr/bin/env python
+"""Benchmark of the batch-1 decode step (tokens/s and fraction of the HBM roofline).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
+
+A "step" is one decoded token: forward(token, pos) + fused sampler.  At N=1 the workload is the
+Llama-3.2-1B shape (FP16 weights, 128K vocabulary, temperature 0.8, repetition penalty 1.1, 32-token
+prompt); for N>1 it is the Llama-3-8B shape tensor-parallel over the N GPUs (one rank per GPU,
+all-reduce after o_proj and down_proj).  Weights are seeded random-init tensors of those shapes.
+Rank 0 prints ONE JSON line.
+
+--impl reference times the reference's own CPU implementation of the same step (the compiled,
+unmodified reference under oracle/_ref when present, else the plain-C port) on the host cores.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+WORKLOADS = {
+    # name: (shape, prompt tokens, temperature, penalty)
+    "llama-3.2-1b": ("llama-3.2-1b", 32, 0.8, 1.1),
+    "tinyllama-1.1b": ("tinyllama-1.1b", 32, 0.8, 1.1),
+    "llama-3-8b": ("llama-3-8b", 64, 0.8, 1.1),
+    "stories15m": ("stories15m", 16, 1.0, 1.0),
+}
+
+
+def measured_peak():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi clocks / throttle reasons while the timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.rows, self.proc, self.index = [], None, index
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.Q}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.t = threading.Thread(target=self._read, daemon=True)
+            self.t.start()
+        except Exception:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([x.strip() for x in line.split(",")])
+
+    def __exit__(self, *a):
+        if self.proc:
+            time.sleep(0.15)
+            self.proc.terminate()
+            self.t.join(timeout=2)
+
+    def summary(self):
+        sm = [float(r[0]) for r in self.rows if len(r) >= 7 and r[0].replace(".", "").isdigit()]
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = sorted({n for r in self.rows if len(r) >= 7 for n, v in zip(names, r[3:7]) if v.lower().startswith("active")})
+        busy = [x for x in sm if x > 0.5 * max(sm)]
+        return {"sm_mhz": statistics.median(busy), "sm_max_mhz": float(self.rows[0][1]), "reasons": reasons,
+                "samples": len(sm), "power_w_max": max(float(r[2]) for r in self.rows if len(r) >= 7)}
+
+
+def gen_device_weights(cfg, dtype, tied, seed, layers=None):
+    """Seeded random-init tensors on the current CUDA device: N(0, 0.02) matrices, unit norms."""
+    import torch
+    from lighterpp_b200.formats import tensor_shapes
+    g = torch.Generator(device="cuda")
+    g.manual_seed(seed)
+    tdt = torch.float16 if dtype == "f16" else torch.float32
+    for name, shape in tensor_shapes(cfg, tied).items():
+        stacked = len(shape) == 3 or name in ("rms_att", "rms_ffn")
+        for l in (range(cfg.n_layers) if stacked else [-1]):
+            shp = shape[1:] if stacked else shape
+            if name.startswith("rms"):
+                t = torch.ones(shp, device="cuda")
+            else:
+                t = (torch.randn(shp, device="cuda", generator=g) * 0.02).to(tdt)
+            yield name, l, t
+
+
+def run_ours(args, rank, world):
+    import torch
+    import torch.distributed as dist
+    from lighterpp_b200 import engine as E, synth
+    local = int(os.environ.get("LOCAL_RANK", 0))
+    torch.cuda.set_device(local)
+    shape, n_prompt, temp, pen = WORKLOADS[args.workload]
+    cfg, dtype, tied, seed = synth.SHAPES[shape]
+    need = n_prompt + args.warmup + 2 * args.steps + 8
+    if need > cfg.seq_len:
+        cfg = type(cfg)(**{**cfg.asdict(), "seq_len": need})
+    nccl_id = None
+    if world > 1:
+        ids = [E.nccl_unique_id() if rank == 0 else None]
+        dist.broadcast_object_list(ids, src=0)
+        nccl_id = ids[0]
+    eng = E.Engine(cfg, dtype, "f16" if dtype == "f16" else "f32", device=local, tp_rank=rank, tp_size=world,
+                   nccl_id=nccl_id, flags=args.flags, ring_kb=args.ring_kb)
+    host_copy = {} if (rank == 0 and world == 1 and not args.no_cpu_baseline) else None
+    for name, l, t in gen_device_weights(cfg, dtype, tied, seed):
+        eng.upload(name, t, max(l, 0))
+        if host_copy is not None:
+            host_copy.setdefault(name, []).append(t.cpu().numpy())
+    eng.finalize()
+    torch.cuda.empty_cache()
+
+    prompt = synth.prompt_tokens(cfg.vocab_size, n_prompt, seed)
+    rs = np.random.default_rng(seed).random(args.warmup + 2 * args.steps + 8).astype(np.float32)
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    # prompt: token by token through the same step, as the reference does (src/main.cpp:163-179)
+    hist = []
+    for pos, t in enumerate(prompt[:-1]):
+        hist = (hist + [int(t)])[-64:]
+        eng.forward(int(t), pos, temp, 1.1, hist, 0.5)
+    tok, pos = int(prompt[-1]), n_prompt - 1
+    hist = (hist + [tok])[-64:]
+    # warm-up (untimed), device-resident loop
+    if args.warmup > 0:
+        out, _ = eng.decode(tok, pos, args.warmup, temp, pen, hist, 64, rs[:args.warmup])
+        hist = (hist + [int(x) for x in out])[-64:]
+        tok, pos = int(out[-1]), pos + args.warmup
+    # ---- timed region 1: K steps, inputs resident in HBM, CUDA events on the engine's stream
+    barrier()
+    with ClockSampler(local) as clk:
+        out, dev_ms = eng.decode(tok, pos, args.steps, temp, pen, hist, 64, rs[args.warmup:args.warmup + args.steps])
+        barrier()
+    t_dev = torch.tensor([dev_ms], dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t_dev, op=dist.ReduceOp.MAX)
+    dev_ms = float(t_dev.item())
+    mean_bytes = float(np.mean([eng.step_bytes(p) for p in range(pos, pos + args.steps)]))
+    hist = (hist + [int(x) for x in out])[-64:]
+    tok, pos = int(out[-1]), pos + args.steps
+    # ---- timed region 2 (e2e): the forward(token,pos) call with host buffers, one call per token
+    r2 = rs[args.warmup + args.steps:]
+    for i in range(min(3, args.warmup)):
+        eng.forward(tok, pos, temp, pen, hist, float(r2[-1 - i]))  # same position: warms the host path only
+    barrier()
+    t0 = time.perf_counter()
+    h2d = d2h = 0
+    for i in range(args.steps):
+        tok = eng.forward(tok, pos, temp, pen, hist, float(r2[i]))
+        h2d += 48 + 4 * len(hist)
+        d2h += 8
+        hist = (hist + [tok])[-64:]
+        pos += 1
+    barrier()
+    e2e_s = time.perf_counter() - t0
+    t_e2e = torch.tensor([e2e_s], dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t_e2e, op=dist.ReduceOp.MAX)
+    e2e_s = float(t_e2e.item())
+
+    # ---- per-kernel durations (CUDA events inside a replayed graph) for the roofline object
+    prof = eng.profile_step(pos - args.steps // 2, 10)
+    line = None
+    if rank == 0:
+        peak, peak_kind = measured_peak()
+        us = dev_ms * 1e3 / args.steps
+        gemv = {k: v for k, v in prof.items() if k.endswith("gemv") and v["launches"]}
+        dom = max(gemv, key=lambda k: gemv[k]["ms"])
+        d = gemv[dom]
+        per_launch_bytes = d["bytes"] / d["launches"]
+        per_launch_us = d["ms"] * 1e3 / d["launches"]
+        achieved = per_launch_bytes / per_launch_us / 1e3
+        step_gbs = mean_bytes / us / 1e3
+        traffic = None
+        try:
+            with open(os.path.join(ROOT, "profiles", "traffic.json")) as f:
+                traffic = json.load(f).get(f"{args.workload}:{dom}")
+        except Exception:
+            pass
+        line = {
+            "metric": "batch-1 decode tok/s and % of HBM roofline", "value": round(args.steps / (dev_ms / 1e3), 2),
+            "unit": "tok/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": round(dev_ms / args.steps, 5), "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "f16 weights, f32 accumulate" if dtype == "f16" else "f32",
+            "data": "synthetic",
+            "config": {"workload": args.workload, "shape": cfg.asdict(), "prompt_tokens": n_prompt, "temperature": temp,
+                       "penalty": pen, "parallelism": f"tp{world}", "positions": [pos - 2 * args.steps, pos - args.steps],
+                       "l2": "inputs larger than L2 (every step streams all weights, >> 126 MB)",
+                       "timed_with": "CUDA events on the engine stream around K graph launches, max over ranks"},
+            "clocks": clk.summary(),
+            "e2e": {"value": round(args.steps / e2e_s, 2), "unit": "tok/s", "h2d_bytes_per_step": h2d // args.steps,
+                    "d2h_bytes_per_step": d2h // args.steps,
+                    "what": "forward(token,pos) through the C ABI per token: host token/history in, sampled id out"},
+            "gpu_launches": eng.kernels_per_step * args.steps,
+            "step_roofline": {"bytes_per_step": int(mean_bytes), "achieved_gbs": round(step_gbs, 1),
+                              "frac_of_measured": round(step_gbs / peak, 4), "frac_of_8tbs": round(step_gbs / 8000.0, 4),
+                              "per_gpu": True},
+            "roofline": {"bound": "hbm", "kernel": dom, "achieved": round(achieved, 1), "peak": peak,
+                         "peak_source": f"{peak_kind} copy bandwidth", "unit": "GB/s", "frac": round(achieved / peak, 4),
+                         "traffic": traffic, "bytes_per_launch": int(per_launch_bytes),
+                         "us_per_launch": round(per_launch_us, 3)},
+            "kernels": {k: {"us_per_launch": round(v["ms"] * 1e3 / v["launches"], 3), "launches": v["launches"],
+                            "gbs": round(v["bytes"] / v["ms"] / 1e6, 1) if v["ms"] else None}
+                        for k, v in prof.items() if v["launches"]},
+        }
+        if world > 1 and not args.no_tp1:
+            line["tp1_baseline"] = "run `bench.py --gpus 1 --workload %s` for the single-GPU number of this shape" % args.workload
+    eng.close()
+    if rank == 0 and host_copy is not None:
+        W = {k: (np.stack(v) if len(v) > 1 or k in ("rms_att", "rms_ffn", "wq") else v[0]) for k, v in host_copy.items()}
+        line["cpu_baseline"] = cpu_baseline(cfg, W, prompt, temp, pen, budget_s=args.cpu_seconds)
+    return line
+
+
+def cpu_baseline(cfg, W, prompt, temp, pen, budget_s=20.0):
+    """Times the reference CPU path on a bounded sample of the same workload (first tokens of the prompt)."""
+    from oracle import oracle as O
+    Wf = {k: np.ascontiguousarray(v, dtype=np.float32) for k, v in W.items()}
+    cores = os.cpu_count()
+    if O.have_reference():
+        m = O.Reference().model(cfg, Wf)
+        kind, threads = "reference", 1
+        t1 = m.time_steps(prompt[:1], 0, temp, pen)
+        n = int(max(2, min(len(prompt) - 1, budget_s / max(t1, 1e-6))))
+        t = m.time_steps(prompt[1:1 + n], 1, temp, pen, prompt[:1])
+    else:
+        orc = O.Oracle()
+        m = orc.model(cfg, Wf)
+        kind, threads = "port", cores
+        t0 = time.perf_counter()
+        m.step_logits(int(prompt[0]), 0)
+        t1 = time.perf_counter() - t0
+        n = int(max(2, min(len(prompt) - 1, budget_s / max(t1, 1e-6))))
+        t0 = time.perf_counter()
+        for i in range(n):
+            lg = m.step_logits(int(prompt[1 + i]), 1 + i)
+            orc.sample(lg, temp, pen, prompt[:1], 0.5)
+        t = time.perf_counter() - t0
+    return {"value": round(n / t, 4), "unit": "tok/s", "cores": threads, "host_cores": cores, "kind": kind,
+            "sample": f"{n} teacher-forced steps at positions 1..{n} of the same model (FP32 copies of the same weights)"}
+
+
+def run_reference(args, rank, world):
+    """The reference's own CPU implementation of the step on the host cores (rank 0 only)."""
+    if rank != 0:
+        return None
+    from lighterpp_b200 import synth
+    shape, n_prompt, temp, pen = WORKLOADS[args.workload]
+    cfg, dtype, tied, seed = synth.SHAPES[shape]
+    small = type(cfg)(**{**cfg.asdict(), "seq_len": 256})
+    try:
+        import torch
+        if torch.cuda.is_available():
+            torch.cuda.set_device(0)
+            W = {}
+            for name, l, t in gen_device_weights(small, dtype, tied, seed):
+                W.setdefault(name, []).append(t.float().cpu().numpy())
+            W = {k: (np.stack(v) if len(v) > 1 or k in ("rms_att", "rms_ffn", "wq") else v[0]) for k, v in W.items()}
+        else:
+            raise RuntimeError
+    except Exception:
+        W = synth.as_f32(synth.gen_model(small, seed, dtype, tied))
+    prompt = synth.prompt_tokens(cfg.vocab_size, n_prompt, seed)
+    cb = cpu_baseline(small, W, prompt, temp, pen, budget_s=args.cpu_seconds)
+    n = int(cb["sample"].split()[0])
+    return {"impl": "reference", "metric": "batch-1 decode tok/s and % of HBM roofline", "value": cb["value"],
+            "unit": "tok/s", "n_gpus": world, "steps": n, "warmup": 1, "ms_per_step": round(1e3 / cb["value"], 3),
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": args.workload, "shape": cfg.asdict(), "parallelism": "cpu"},
+            "cpu_baseline": cb,
+            "e2e": {"value": cb["value"], "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=256)
+    ap.add_argument("--warmup", type=int, default=16)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default=None, choices=sorted(WORKLOADS))
+    ap.add_argument("--flags", type=int, default=0)
+    ap.add_argument("--ring-kb", type=int, default=0)
+    ap.add_argument("--cpu-seconds", type=float, default=15.0)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-tp1", action="store_true")
+    args = ap.parse_args()
+    rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
+    if world != args.gpus and world == 1 and args.gpus > 1:
+        print(json.dumps({"error": f"--gpus {args.gpus} needs torchrun with {args.gpus} ranks"}))
+        sys.exit(2)
+    if args.workload is None:
+        args.workload = "llama-3.2-1b" if world == 1 else "llama-3-8b"
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    if world > 1 and args.impl == "ours":
+        import torch.distributed as dist
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("gloo")
+    line = run_reference(args, rank, world) if args.impl == "reference" else run_ours(args, rank, world)
+    if rank == 0 and line is not None:
+        print(json.dumps(line), flush=True)
+    if world > 1 and args.impl == "ours":
+        import torch.distributed as dist
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -150,8 +150,9 @@ int lpp_kernels_per_step(const lpp_engine* e); /* own kernel launches in one ste
  * weights + one embedding row + K/V rows 0..pos + this token's K/V write. */
 int64_t lpp_step_bytes(const lpp_engine* e, int pos);
 
-/* Per-kernel-kind timing of one un-graphed step at `pos`, CUDA events around every launch, averaged
- * over iters steps.  kinds: 0 qkv gemv, 1 attention, 2 o_proj gemv, 3 gate|up gemv, 4 down gemv,
+/* Per-kernel-kind timing of one step at `pos`: the step is captured with a CUDA event-record node
+ * before and after every kernel and replayed iters times (isolated kernel durations, no programmatic
+ * overlap, no host launch latency).  kinds: 0 qkv gemv, 1 attention, 2 o_proj gemv, 3 gate|up gemv, 4 down gemv,
  * 5 lm-head gemv, 6 sampler, 7 all-reduce.  ms[8] total device ms per step per kind, launches[8]
  * launches per step, bytes[8] algorithmic bytes per step. */
 lpp_status lpp_profile_step(lpp_engine* e, int pos, int iters, float* ms, int* launches, int64_t* bytes);

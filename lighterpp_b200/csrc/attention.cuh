@@ -207,7 +207,7 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const AttnArg
     }
     __syncthreads();
 
-    // merge the warps, write this split's partial
+    // merge the warps; with a single split the result is final, otherwise it is this split's partial
     constexpr int NW = kAttnThreads / 32;
     float* part = a.part;
     const int PS = HS + 2;
@@ -224,13 +224,18 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const AttnArg
             av += s_state[w][h][d] * f;
             lv += s_state[w][h][HS + 1] * f;
         }
-        float* p = part + ((size_t)(hbase + h) * a.n_splits + split) * PS;
-        __stcg(p + d, av);
-        if (d == 0) {
-            __stcg(p + HS, mm);
-            __stcg(p + HS + 1, lv);
+        if (n_eff == 1) {
+            a.out[(size_t)(hbase + h) * HS + d] = (lv > 0.f) ? __fdiv_rn(av, lv) : 0.f;
+        } else {
+            float* p = part + ((size_t)(hbase + h) * a.n_splits + split) * PS;
+            __stcg(p + d, av);
+            if (d == 0) {
+                __stcg(p + HS, mm);
+                __stcg(p + HS + 1, lv);
+            }
         }
     }
+    if (n_eff == 1) return;  // short context: no partials, no ticket, no second pass
     __threadfence();
     __syncthreads();
     if (tid == 0) {

@@ -132,6 +132,12 @@ __device__ __forceinline__ void bulk_g2s(void* smem_dst, const void* gsrc, uint3
                  : "memory");
 }
 
+// Asks the copy engine to pull [gsrc, gsrc+bytes) into L2 (no shared-memory destination, no
+// completion to wait for).  gsrc 16-byte aligned, bytes a multiple of 16.
+__device__ __forceinline__ void bulk_prefetch_l2(const void* gsrc, uint32_t bytes) {
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(gsrc), "r"(bytes) : "memory");
+}
+
 // ------------------------------------------------------------------ reproducible expf
 
 // exp(x) for float x, evaluated in double with only IEEE add/mul/fma, so the host twin (same

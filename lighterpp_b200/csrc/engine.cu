@@ -151,6 +151,7 @@ struct lpp_engine {
     nccl::comm_t comm = nullptr;
     // profiling hooks
     bool profiling = false;
+    bool profiling_capture = false;
     std::vector<cudaEvent_t> prof_events;
     std::vector<int> prof_kinds;
 };
@@ -198,17 +199,27 @@ static cudaError_t launch_gemv_t(lpp_engine* e, GemvArgs& a, bool pdl, cudaStrea
         const int grid = std::max(1, std::min(groups, e->num_sms * 4));
         return launch_kernel(gemv_ldg_kernel<WT, EPI>, dim3(grid), dim3(kGemvLdgThreads), smem, s, pdl, a);
     }
-    int kc = std::min(a.K, 8192 / esz);
-    kc = kc / 8 * 8;
-    a.kc = kc;
-    a.stage_bytes = kRowsPerGroup * kc * esz;
+    // A stage is one bulk copy of about stage_target bytes: whole row pairs when they fit, else one
+    // K-chunk of one row.  LPP_STAGE_KB (timing experiments) overrides the 8 KiB default.
+    int stage_target = 8192;
+    if (const char* sk = getenv("LPP_STAGE_KB")) stage_target = std::max(1, atoi(sk)) * 1024;
+    const int pair_bytes = kRowsPerGroup * a.K * esz;
+    if (pair_bytes <= stage_target) {
+        a.pairs_per_stage = stage_target / pair_bytes;
+        a.kc = a.K;
+        a.stage_bytes = a.pairs_per_stage * pair_bytes;
+    } else {
+        a.pairs_per_stage = 0;
+        a.kc = std::max(8, std::min(a.K, stage_target / esz) / 8 * 8);
+        a.stage_bytes = a.kc * esz;
+    }
     const size_t fixed = kGemvBarrierBytes + 128 + xbytes;
-    size_t ring = (size_t)(e->c.ring_kb > 0 ? e->c.ring_kb : 88) * 1024;
+    size_t ring = (size_t)(e->c.ring_kb > 0 ? e->c.ring_kb : 128) * 1024;
     if (fixed + ring > e->smem_optin) ring = e->smem_optin - fixed;
-    int ns = (int)(ring / a.stage_bytes);
+    int ns = (int)(ring / ((size_t)kGemvConsumerWarps * a.stage_bytes));  // slots per consumer warp
     ns = std::max(2, std::min(ns, kGemvMaxStages));
     a.n_stages = ns;
-    const size_t smem = fixed + (size_t)ns * a.stage_bytes;
+    const size_t smem = fixed + (size_t)kGemvConsumerWarps * ns * a.stage_bytes;
     if (smem > e->smem_optin) return cudaErrorInvalidValue;
     static bool attr_done[64] = {};
     if (!attr_done[e->c.device & 63]) {
@@ -277,7 +288,10 @@ struct Recorder {
         if (!e->profiling) return;
         cudaEvent_t ev;
         cudaEventCreate(&ev);
-        cudaEventRecord(ev, s);
+        if (e->profiling_capture)
+            cudaEventRecordWithFlags(ev, s, cudaEventRecordExternal);  // becomes an event-record graph node
+        else
+            cudaEventRecord(ev, s);
         e->prof_events.push_back(ev);
         e->prof_kinds.push_back(kind);
     }
@@ -305,6 +319,7 @@ static void record_gemv(Recorder& R, int kind, int epi, GemvArgs a) {
     lpp_engine* e = R.e;
     if (skip_mask() & (1u << kind)) return;
     a.st = e->st;
+    if (const char* dbg = getenv("LPP_DEBUG_GEMV")) a.debug = (int)strtol(dbg, nullptr, 0);
     a.vocab = e->c.vocab_size;
     a.seq_len = e->c.seq_len;
     R.mark(kind);
@@ -324,6 +339,40 @@ static void record_allreduce(Recorder& R, float* buf, int n) {
     }
     R.mark(-1);
     R.prev_kernel = false;
+}
+
+// Start and size of the weight matrix a GEMV kind streams in layer l (this rank's share).
+static void matrix_span(const lpp_engine* e, int kind, int l, const void** ptr, size_t* bytes) {
+    const size_t D = e->c.dim, esz = e->esz;
+    const size_t qkv_rows = e->Dq + 2 * (size_t)e->KVd;
+    switch (kind) {
+        case kQkv: *bytes = qkv_rows * D * esz; *ptr = (const char*)e->wqkv + l * *bytes; break;
+        case kOproj: *bytes = D * e->Dq * esz; *ptr = (const char*)e->wo + l * *bytes; break;
+        case kGateUp: *bytes = 2 * (size_t)e->Fl * D * esz; *ptr = (const char*)e->w13 + l * *bytes; break;
+        case kDown: *bytes = D * e->Fl * esz; *ptr = (const char*)e->w2 + l * *bytes; break;
+        default: *bytes = (size_t)e->c.vocab_size * D * esz; *ptr = e->wcls; break;
+    }
+}
+// What the GEMV (kind, l) should pull towards L2 for its successor in the step: the next matrix, or
+// its first LPP_PF_MB MiB (default 32) when it is larger.  The classifier's successor is the first
+// layer's QKV matrix of the next token.
+static void set_prefetch(const lpp_engine* e, GemvArgs& a, int kind, int l) {
+    int nk, nl = l;
+    switch (kind) {
+        case kQkv: nk = kOproj; break;
+        case kOproj: nk = kGateUp; break;
+        case kGateUp: nk = kDown; break;
+        case kDown: nk = (l + 1 < e->c.n_layers) ? kQkv : kLmHead; nl = l + 1; break;
+        default: nk = kQkv; nl = 0; break;
+    }
+    size_t cap = 32;
+    if (const char* v = getenv("LPP_PF_MB")) cap = (size_t)std::max(0, atoi(v));
+    const void* p;
+    size_t bytes;
+    matrix_span(e, nk, nl, &p, &bytes);
+    bytes = std::min(bytes, cap << 20) & ~(size_t)15;
+    a.pf = bytes ? p : nullptr;
+    a.pf_bytes = (unsigned int)bytes;
 }
 
 static void record_step(Recorder& R, bool with_sampler) {
@@ -357,6 +406,7 @@ static void record_step(Recorder& R, bool with_sampler) {
             a.k_cache = (char*)e->kcache + lofs;
             a.v_cache = (char*)e->vcache + lofs;
             a.kv_is_f32 = c.kv_dtype == LPP_F32;
+            set_prefetch(e, a, kQkv, l);
             record_gemv(R, kQkv, kEpiQkv, a);
         }
         {  // split-KV flash decode
@@ -392,6 +442,7 @@ static void record_step(Recorder& R, bool with_sampler) {
             a.x = e->att_out;
             a.resid = (!tp || c.tp_rank == 0) ? cur : nullptr;
             a.out = tp ? oth : cur;
+            set_prefetch(e, a, kOproj, l);
             record_gemv(R, kOproj, kEpiResid, a);
             if (tp) {
                 record_allreduce(R, oth, D);
@@ -406,6 +457,7 @@ static void record_step(Recorder& R, bool with_sampler) {
             a.x = cur;
             a.norm_w = e->rms_ffn + (size_t)l * D;
             a.out = e->hb;
+            set_prefetch(e, a, kGateUp, l);
             record_gemv(R, kGateUp, kEpiSwiglu, a);
         }
         {  // down + residual
@@ -416,6 +468,7 @@ static void record_step(Recorder& R, bool with_sampler) {
             a.x = e->hb;
             a.resid = (!tp || c.tp_rank == 0) ? cur : nullptr;
             a.out = tp ? oth : cur;
+            set_prefetch(e, a, kDown, l);
             record_gemv(R, kDown, kEpiResid, a);
             if (tp) {
                 record_allreduce(R, oth, D);
@@ -431,6 +484,7 @@ static void record_step(Recorder& R, bool with_sampler) {
         a.x = cur;
         a.norm_w = e->rms_final;
         a.out = e->logits;
+        set_prefetch(e, a, kLmHead, 0);
         record_gemv(R, kLmHead, kEpiStore, a);
     }
     if (with_sampler && !(skip_mask() & (1u << kSampler))) {
@@ -1011,28 +1065,51 @@ extern "C" lpp_status lpp_profile_step(lpp_engine* e, int pos, int iters, float*
     for (int k = 0; k < kKinds; ++k) ms[k] = 0.f, launches[k] = 0;
     kind_bytes(e, pos, bytes);
     lpp_sample_params sp = {0.f, 1.f};
+    // The step is captured once more with an event-record node before and after every kernel and
+    // replayed as a graph, so the durations carry no host launch latency.  Event nodes sit between
+    // the kernels, hence no programmatic overlap: these are isolated per-kernel times.
+    cudaGraphExec_t gx = nullptr;
     lpp_status rs = LPP_OK;
+    {
+        cudaGraph_t g = nullptr;
+        CU(cudaStreamBeginCapture(e->stream, cudaStreamCaptureModeThreadLocal));
+        e->profiling = e->profiling_capture = true;
+        Recorder R{e, e->stream};
+        record_step(R, true);
+        e->profiling = e->profiling_capture = false;
+        cudaError_t ce = cudaStreamEndCapture(e->stream, &g);
+        if (R.err != cudaSuccess || ce != cudaSuccess) {
+            rs = fail(LPP_ERR_CUDA, "profile capture: %s", cudaGetErrorString(R.err != cudaSuccess ? R.err : ce));
+        } else if (cudaGraphInstantiate(&gx, g, 0) != cudaSuccess) {
+            rs = fail(LPP_ERR_CUDA, "profile graph instantiate failed");
+        }
+        if (g) cudaGraphDestroy(g);
+        (void)cudaGetLastError();
+    }
     for (int it = 0; it < iters + 1 && rs == LPP_OK; ++it) {  // iteration 0 is a warm-up
         rs = push_state(e, 0, pos, &sp, nullptr, 0, 0.f, 0, 0);
         if (rs != LPP_OK) break;
-        e->profiling = true;
-        Recorder R{e, e->stream};
-        record_step(R, true);
-        e->profiling = false;
+        cudaError_t le = cudaGraphLaunch(gx, e->stream);
         cudaError_t se = cudaStreamSynchronize(e->stream);
-        if (R.err != cudaSuccess || se != cudaSuccess)
-            rs = fail(LPP_ERR_CUDA, "profile step: %s", cudaGetErrorString(R.err != cudaSuccess ? R.err : se));
-        for (size_t i = 0; i + 1 < e->prof_events.size() && rs == LPP_OK; i += 2) {
-            float t = 0.f;
-            cudaEventElapsedTime(&t, e->prof_events[i], e->prof_events[i + 1]);
-            if (it > 0) {
-                ms[e->prof_kinds[i]] += t / iters;
-                if (it == 1) launches[e->prof_kinds[i]]++;
-            }
+        if (le != cudaSuccess || se != cudaSuccess) {
+            rs = fail(LPP_ERR_CUDA, "profile step: %s", cudaGetErrorString(le != cudaSuccess ? le : se));
+            break;
         }
-        for (cudaEvent_t ev : e->prof_events) cudaEventDestroy(ev);
-        e->prof_events.clear();
-        e->prof_kinds.clear();
+        if (it == 0) continue;
+        for (size_t i = 0; i + 1 < e->prof_events.size(); i += 2) {
+            float t = 0.f;
+            if (cudaEventElapsedTime(&t, e->prof_events[i], e->prof_events[i + 1]) != cudaSuccess) {
+                rs = fail(LPP_ERR_CUDA, "cudaEventElapsedTime on graph event nodes failed");
+                break;
+            }
+            ms[e->prof_kinds[i]] += t / iters;
+            if (it == 1) launches[e->prof_kinds[i]]++;
+        }
     }
+    if (gx) cudaGraphExecDestroy(gx);
+    for (cudaEvent_t ev : e->prof_events) cudaEventDestroy(ev);
+    e->prof_events.clear();
+    e->prof_kinds.clear();
+    (void)cudaGetLastError();
     return rs;
 }

@@ -10,12 +10,17 @@
 // follow the reference CPU path (src/ops.cpp): activations stay FP32 (the reference GPU kernel
 // rounds x to FP16 and accumulates in half2, src/matmul.cu:85-99 -- deliberately not copied).
 //
-// Data movement, ring variant: each CTA owns a contiguous range of row pairs.  A producer warp
-// streams that range through a shared-memory ring with 1-D bulk async copies (one elected lane,
-// completion counted in bytes on an mbarrier); eight consumer warps each take whole stages, so the
-// main loop has no CTA-wide barrier.  Ring slots are shared by all warps, but the "data ready"
-// barriers are private to a consumer warp: warps drift apart by up to a ring's worth of stages, and
-// a parity wait is only unambiguous if the waiter visits every phase of its barrier in order.  The producer starts before the programmatic
+// Data movement, ring variant: each CTA owns a contiguous range of row pairs, dealt round-robin to
+// eight consumer warps.  Every consumer warp has a private ring of shared-memory slots fed by its
+// own lane of the producer warp with 1-D bulk async copies (completion counted in bytes on an
+// mbarrier per slot): eight independent single-producer / single-consumer pipelines, so every
+// barrier is visited phase by phase in order by exactly one waiter on each side, the main loop has
+// no CTA-wide barrier, and the copy-issue work runs eight lanes wide instead of on one thread.
+// The copy engine retires roughly one bulk copy per ~100 SM cycles whatever its size, so a stage is
+// always ONE copy of ~8 KiB: several whole row pairs when rows are short, one K-chunk of one row
+// when they are long.  When a producer lane has issued its last copy it asks the copy engine to
+// prefetch its share of the next kernel's weights into L2, which keeps HBM busy across the kernel
+// boundary.  The producer starts before the programmatic
 // dependency wait -- weights do not depend on the previous kernel -- so the ring is already full
 // when the activations arrive.  HBM traffic = the matrix once; x is re-read from L2 per CTA.
 #pragma once
@@ -28,9 +33,9 @@ enum GemvEpi : int { kEpiStore = 0, kEpiResid = 1, kEpiSwiglu = 2, kEpiQkv = 3 }
 constexpr int kGemvConsumerWarps = 8;
 constexpr int kGemvRingThreads = (kGemvConsumerWarps + 1) * 32;  // + producer warp
 constexpr int kGemvLdgThreads = 256;
-constexpr int kGemvMaxStages = 64;
-// one "full" barrier array per consumer warp plus one "empty" barrier per ring slot
-constexpr int kGemvBarrierBytes = (kGemvConsumerWarps + 1) * kGemvMaxStages * 8;
+constexpr int kGemvMaxStages = 16;  // ring slots per consumer warp
+// per consumer warp: one "full" and one "empty" barrier per slot of its private ring
+constexpr int kGemvBarrierBytes = 2 * kGemvConsumerWarps * kGemvMaxStages * 8;
 constexpr int kRowsPerGroup = 2;                           // rows handled together by one warp
 
 struct GemvArgs {
@@ -52,9 +57,15 @@ struct GemvArgs {
     void* v_cache;
     int kv_is_f32;
     // ---- ring geometry (host-computed)
-    int kc;           // K elements per stage row (multiple of 8)
-    int n_stages;     // ring slots
-    int stage_bytes;  // bytes per slot = kRowsPerGroup * kc * sizeof(WT)
+    int pairs_per_stage;  // > 0: a stage holds this many whole row pairs (one contiguous copy);
+                          // 0: rows are long, a stage holds one K-chunk (kc elements) of one row
+    int kc;           // K elements per stage in long-row mode (multiple of 8)
+    int n_stages;     // ring slots per consumer warp
+    int stage_bytes;  // bytes per slot
+    // ---- L2 prefetch of the weights the NEXT kernel of the step will stream (nullptr = none)
+    const void* pf;
+    unsigned int pf_bytes;
+    int debug;        // timing experiments only: 1 = consumers skip the arithmetic, 2 = producer skips the copies
 };
 
 // ------------------------------------------------------------------ x staging layouts
@@ -192,64 +203,78 @@ __device__ __forceinline__ void stage_input(const GemvArgs& a, float* xs, float*
     consumer_barrier(NT);
 }
 
-// Dot products of kRowsPerGroup weight rows (klen elements each, 16-byte aligned, anywhere
-// addressable: shared or global) with x[k0 .. k0+klen) from shared memory.  Lane-strided over
-// 16-byte vectors.
-template <typename WT, bool kFromGlobal>
+__device__ __forceinline__ uint4 lds_u4(uint32_t addr) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ float4 lds_f4(uint32_t addr) {
+    float4 v;
+    asm volatile("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr));
+    return v;
+}
+
+// Dot products of NR (1 or 2) weight rows (klen elements each, 16-byte aligned; in shared memory, or
+// in global memory when kFromGlobal) with x[k0 .. k0+klen) from shared memory.  Lane-strided over
+// 16-byte vectors; the x vectors are loaded once and used for both rows.
+template <typename WT, int NR, bool kFromGlobal>
 __device__ __forceinline__ void dot_rows(const unsigned char* row0, const unsigned char* row1, const float* xs,
                                          int K, int k0, int klen, int lane, float& acc0, float& acc1) {
     float a0 = 0.f, a1 = 0.f, b0 = 0.f, b1 = 0.f;
+    const uint4* r0 = reinterpret_cast<const uint4*>(row0);
+    const uint4* r1 = reinterpret_cast<const uint4*>(row1);
+    const uint32_t s0 = kFromGlobal ? 0u : smem_u32(row0), s1 = (kFromGlobal || NR == 1) ? 0u : smem_u32(row1);
     if constexpr (sizeof(WT) == 2) {
         const int nvec = klen >> 3;
-        const float4* xlo = reinterpret_cast<const float4*>(xs) + (k0 >> 3);
-        const float4* xhi = reinterpret_cast<const float4*>(xs + (K >> 1)) + (k0 >> 3);
-        const uint4* r0 = reinterpret_cast<const uint4*>(row0);
-        const uint4* r1 = reinterpret_cast<const uint4*>(row1);
+        const uint32_t xlo = smem_u32(xs) + (uint32_t)(k0 >> 3) * 16u;
+        const uint32_t xhi = xlo + (uint32_t)K * 2u;  // second plane starts K/2 floats further on
 #pragma unroll 4
         for (int v = lane; v < nvec; v += 32) {
-            uint4 w0, w1;
+            uint4 w0, w1 = make_uint4(0, 0, 0, 0);
             if constexpr (kFromGlobal) {
                 w0 = ldg_stream_u4(r0 + v);
-                w1 = ldg_stream_u4(r1 + v);
+                if constexpr (NR == 2) w1 = ldg_stream_u4(r1 + v);
             } else {
-                w0 = r0[v];
-                w1 = r1[v];
+                w0 = lds_u4(s0 + (uint32_t)v * 16u);
+                if constexpr (NR == 2) w1 = lds_u4(s1 + (uint32_t)v * 16u);
             }
-            const float4 xl = xlo[v], xh = xhi[v];
+            const float4 xl = lds_f4(xlo + (uint32_t)v * 16u), xh = lds_f4(xhi + (uint32_t)v * 16u);
             float2 p;
             p = half2_bits_to_float2(w0.x); a0 = fmaf(p.x, xl.x, a0); b0 = fmaf(p.y, xl.y, b0);
             p = half2_bits_to_float2(w0.y); a0 = fmaf(p.x, xl.z, a0); b0 = fmaf(p.y, xl.w, b0);
             p = half2_bits_to_float2(w0.z); a0 = fmaf(p.x, xh.x, a0); b0 = fmaf(p.y, xh.y, b0);
             p = half2_bits_to_float2(w0.w); a0 = fmaf(p.x, xh.z, a0); b0 = fmaf(p.y, xh.w, b0);
-            p = half2_bits_to_float2(w1.x); a1 = fmaf(p.x, xl.x, a1); b1 = fmaf(p.y, xl.y, b1);
-            p = half2_bits_to_float2(w1.y); a1 = fmaf(p.x, xl.z, a1); b1 = fmaf(p.y, xl.w, b1);
-            p = half2_bits_to_float2(w1.z); a1 = fmaf(p.x, xh.x, a1); b1 = fmaf(p.y, xh.y, b1);
-            p = half2_bits_to_float2(w1.w); a1 = fmaf(p.x, xh.z, a1); b1 = fmaf(p.y, xh.w, b1);
+            if constexpr (NR == 2) {
+                p = half2_bits_to_float2(w1.x); a1 = fmaf(p.x, xl.x, a1); b1 = fmaf(p.y, xl.y, b1);
+                p = half2_bits_to_float2(w1.y); a1 = fmaf(p.x, xl.z, a1); b1 = fmaf(p.y, xl.w, b1);
+                p = half2_bits_to_float2(w1.z); a1 = fmaf(p.x, xh.x, a1); b1 = fmaf(p.y, xh.y, b1);
+                p = half2_bits_to_float2(w1.w); a1 = fmaf(p.x, xh.z, a1); b1 = fmaf(p.y, xh.w, b1);
+            }
         }
     } else {
         const int nvec = klen >> 2;
-        const float4* x4 = reinterpret_cast<const float4*>(xs) + (k0 >> 2);
-        const uint4* r0 = reinterpret_cast<const uint4*>(row0);
-        const uint4* r1 = reinterpret_cast<const uint4*>(row1);
+        const uint32_t x4 = smem_u32(xs) + (uint32_t)(k0 >> 2) * 16u;
 #pragma unroll 4
         for (int v = lane; v < nvec; v += 32) {
-            uint4 w0, w1;
+            uint4 w0, w1 = make_uint4(0, 0, 0, 0);
             if constexpr (kFromGlobal) {
                 w0 = ldg_stream_u4(r0 + v);
-                w1 = ldg_stream_u4(r1 + v);
+                if constexpr (NR == 2) w1 = ldg_stream_u4(r1 + v);
             } else {
-                w0 = r0[v];
-                w1 = r1[v];
+                w0 = lds_u4(s0 + (uint32_t)v * 16u);
+                if constexpr (NR == 2) w1 = lds_u4(s1 + (uint32_t)v * 16u);
             }
-            const float4 xv = x4[v];
+            const float4 xv = lds_f4(x4 + (uint32_t)v * 16u);
             a0 = fmaf(__uint_as_float(w0.x), xv.x, a0); b0 = fmaf(__uint_as_float(w0.y), xv.y, b0);
             a0 = fmaf(__uint_as_float(w0.z), xv.z, a0); b0 = fmaf(__uint_as_float(w0.w), xv.w, b0);
-            a1 = fmaf(__uint_as_float(w1.x), xv.x, a1); b1 = fmaf(__uint_as_float(w1.y), xv.y, b1);
-            a1 = fmaf(__uint_as_float(w1.z), xv.z, a1); b1 = fmaf(__uint_as_float(w1.w), xv.w, b1);
+            if constexpr (NR == 2) {
+                a1 = fmaf(__uint_as_float(w1.x), xv.x, a1); b1 = fmaf(__uint_as_float(w1.y), xv.y, b1);
+                a1 = fmaf(__uint_as_float(w1.z), xv.z, a1); b1 = fmaf(__uint_as_float(w1.w), xv.w, b1);
+            }
         }
     }
     acc0 += a0 + b0;
-    acc1 += a1 + b1;
+    if constexpr (NR == 2) acc1 += a1 + b1;
 }
 
 // Writes the results of row pair `g` (rows 2g, 2g+1); called by one lane with the warp-reduced sums.
@@ -308,95 +333,143 @@ __device__ __forceinline__ void gemv_epilogue(const GemvArgs& a, int g, float v0
 template <typename WT, int EPI>
 __global__ void __launch_bounds__(kGemvRingThreads) gemv_ring_kernel(const GemvArgs a) {
     extern __shared__ __align__(128) unsigned char smem[];
-    uint64_t* fullw = reinterpret_cast<uint64_t*>(smem);                 // [consumer warp][kGemvMaxStages]
-    uint64_t* empty = fullw + kGemvConsumerWarps * kGemvMaxStages;       // [ring slot]
-    float* red = reinterpret_cast<float*>(smem + kGemvBarrierBytes);     // 8 floats
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem);                // [consumer warp][kGemvMaxStages]
+    uint64_t* empty = full + kGemvConsumerWarps * kGemvMaxStages;      // [consumer warp][kGemvMaxStages]
+    float* red = reinterpret_cast<float*>(smem + kGemvBarrierBytes);   // 8 floats
     float* xs = reinterpret_cast<float*>(smem + kGemvBarrierBytes + 128);
     unsigned char* ring = smem + kGemvBarrierBytes + 128 + (((size_t)a.K * 4 + 127) & ~(size_t)127);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int NS = a.n_stages;
+    const int NS = a.n_stages;  // slots per consumer warp
     const int groups = a.n_rows / kRowsPerGroup;
+    // this CTA's row pairs, then this warp's (or producer lane's) contiguous share of them
     const int g0 = (int)(((long long)blockIdx.x * groups) / gridDim.x);
     const int g1 = (int)(((long long)(blockIdx.x + 1) * groups) / gridDim.x);
     const int ng = g1 - g0;
-    const int nch = (a.K + a.kc - 1) / a.kc;
-    const int total = ng * nch;
+    const int w = (warp == kGemvConsumerWarps) ? lane : warp;  // pipeline index
+    const int p0 = g0 + (w < kGemvConsumerWarps ? (ng * w) / kGemvConsumerWarps : 0);
+    const int p1 = g0 + (w < kGemvConsumerWarps ? (ng * (w + 1)) / kGemvConsumerWarps : 0);
+    const size_t row_bytes = (size_t)a.K * sizeof(WT);
+    const int m = a.pairs_per_stage;
+    const int nch = m > 0 ? 1 : (a.K + a.kc - 1) / a.kc;
 
-    if (tid < NS) {
-#pragma unroll
-        for (int w = 0; w < kGemvConsumerWarps; ++w) mbar_init(&fullw[w * kGemvMaxStages + tid], 1);
-        mbar_init(&empty[tid], 1);
+    if (tid < kGemvConsumerWarps * NS) {
+        const int bw = tid / NS, sl = tid - bw * NS;
+        mbar_init(&full[bw * kGemvMaxStages + sl], 1);
+        mbar_init(&empty[bw * kGemvMaxStages + sl], 1);
         mbar_fence_init();
     }
     __syncthreads();
 
     if (warp == kGemvConsumerWarps) {
-        // ---------------- producer: one lane streams this CTA's rows through the ring.
-        // Stage s = (row pair j = s / nch, K-chunk c = s % nch) lands in slot s % NS and is
-        // announced on the barrier of the warp that owns pair j (j % 8), at that warp's own
-        // stage counter.
-        if (lane == 0) {
+        // ---------------- producer warp: lane w feeds consumer warp w through w's private ring
+        if (lane < kGemvConsumerWarps) {
             const unsigned char* W = reinterpret_cast<const unsigned char*>(a.W);
-            int j = 0, c = 0;
-            for (int s = 0; s < total; ++s) {
-                const int slot = s % NS, use = s / NS;
-                if (use > 0 && !mbar_wait_bounded(&empty[slot], (use - 1) & 1, &a.st->status)) break;
-                const int w = j & (kGemvConsumerWarps - 1);
-                const int iw = (j >> 3) * nch + c;
-                uint64_t* bar = &fullw[w * kGemvMaxStages + iw % NS];
-                const int g = g0 + j;
-                const int k0 = c * a.kc;
-                const int klen = min(a.kc, a.K - k0);
-                const uint32_t row_bytes = (uint32_t)klen * sizeof(WT);
-                unsigned char* dst = ring + (size_t)slot * a.stage_bytes;
-                mbar_arrive_expect_tx(bar, kRowsPerGroup * row_bytes);
-                if (nch == 1) {
-                    // whole rows: the pair is one contiguous span of the matrix
-                    bulk_g2s(dst, W + (size_t)g * kRowsPerGroup * a.K * sizeof(WT), kRowsPerGroup * row_bytes, bar);
+            uint64_t* myfull = full + w * kGemvMaxStages;
+            uint64_t* myempty = empty + w * kGemvMaxStages;
+            unsigned char* myring = ring + (size_t)w * NS * a.stage_bytes;
+            int slot = 0, pass = 0;  // pass = completed trips around the ring
+            bool alive = true;
+            auto issue = [&](const unsigned char* src, uint32_t bytes) -> bool {
+                // trip p > 0 reuses a slot once its release number p-1 has happened
+                if (pass > 0 && !mbar_wait_bounded(&myempty[slot], (uint32_t)(pass - 1) & 1u, &a.st->status))
+                    return false;
+                if (a.debug & 2) {
+                    mbar_arrive(&myfull[slot]);
                 } else {
-#pragma unroll
-                    for (int r = 0; r < kRowsPerGroup; ++r)
-                        bulk_g2s(dst + (size_t)r * row_bytes,
-                                 W + ((size_t)(g * kRowsPerGroup + r) * a.K + k0) * sizeof(WT), row_bytes, bar);
+                    mbar_arrive_expect_tx(&myfull[slot], bytes);
+                    bulk_g2s(myring + (size_t)slot * a.stage_bytes, src, bytes, &myfull[slot]);
                 }
-                if (++c == nch) {
-                    c = 0;
-                    ++j;
+                if (++slot == NS) {
+                    slot = 0;
+                    ++pass;
+                }
+                return true;
+            };
+            if (m > 0) {
+                for (int p = p0; p < p1 && alive; p += m) {
+                    const int cnt = min(m, p1 - p);
+                    alive = issue(W + (size_t)p * kRowsPerGroup * row_bytes, (uint32_t)(cnt * kRowsPerGroup * row_bytes));
+                }
+            } else {
+                for (int p = p0; p < p1 && alive; ++p)
+                    for (int r = 0; r < kRowsPerGroup && alive; ++r)
+                        for (int c = 0; c < nch && alive; ++c) {
+                            const int k0 = c * a.kc;
+                            const int klen = min(a.kc, a.K - k0);
+                            alive = issue(W + ((size_t)(p * kRowsPerGroup + r) * a.K + k0) * sizeof(WT),
+                                          (uint32_t)(klen * sizeof(WT)));
+                        }
+            }
+            // this lane's HBM requests are all queued: pull its share of the next kernel's weights
+            // towards L2 so the memory system stays busy across the kernel boundary
+            if (a.pf && alive) {
+                const unsigned int lanes = gridDim.x * kGemvConsumerWarps;
+                unsigned int slice = (a.pf_bytes + lanes - 1) / lanes;
+                slice = (slice + 15u) & ~15u;
+                const unsigned long long off = (unsigned long long)(blockIdx.x * kGemvConsumerWarps + w) * slice;
+                if (off < a.pf_bytes) {
+                    const unsigned int n = (unsigned int)min((unsigned long long)slice, (unsigned long long)a.pf_bytes - off);
+                    bulk_prefetch_l2(reinterpret_cast<const unsigned char*>(a.pf) + off, n & ~15u);
                 }
             }
-            // all of this CTA's HBM requests are issued: let the next kernel start filling its ring
-            pdl_launch_dependents();
         }
+        __syncwarp();
+        // all of this CTA's copies are issued: the next kernel may start launching
+        if (lane == 0) pdl_launch_dependents();
         return;
     }
 
     // ---------------- consumers
     stage_input<WT, kGemvConsumerWarps * 32>(a, xs, red, tid);
 
-    uint64_t* myfull = fullw + warp * kGemvMaxStages;
-    int iw = 0;  // this warp's stage counter
-    for (int j = warp; j < ng; j += kGemvConsumerWarps) {
-        float acc0 = 0.f, acc1 = 0.f;
-        bool ok = true;
-        for (int c = 0; c < nch; ++c, ++iw) {
-            // warp-uniform outcome: a lane that timed out must not leave the others in __syncwarp
-            if (!__all_sync(0xffffffffu, mbar_wait_bounded(&myfull[iw % NS], (iw / NS) & 1, &a.st->status))) {
-                ok = false;
-                break;
-            }
-            const int slot = (j * nch + c) % NS;
-            const int k0 = c * a.kc;
-            const int klen = min(a.kc, a.K - k0);
-            const unsigned char* st = ring + (size_t)slot * a.stage_bytes;
-            dot_rows<WT, false>(st, st + (size_t)klen * sizeof(WT), xs, a.K, k0, klen, lane, acc0, acc1);
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&empty[slot]);
+    uint64_t* myfull = full + w * kGemvMaxStages;
+    uint64_t* myempty = empty + w * kGemvMaxStages;
+    const unsigned char* myring = ring + (size_t)w * NS * a.stage_bytes;
+    int slot = 0;
+    uint32_t par = 0;
+    // waits for this warp's next stage; warp-uniform outcome so a timed-out lane cannot strand the rest
+    auto acquire = [&]() -> bool { return __all_sync(0xffffffffu, mbar_wait_bounded(&myfull[slot], par, &a.st->status)); };
+    auto release = [&]() {
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&myempty[slot]);
+        if (++slot == NS) {
+            slot = 0;
+            par ^= 1u;
         }
-        if (!ok) break;
-        acc0 = warp_sum(acc0);
-        acc1 = warp_sum(acc1);
-        if (lane == 0) gemv_epilogue<EPI>(a, g0 + j, acc0, acc1);
+    };
+    if (m > 0) {
+        for (int p = p0; p < p1; p += m) {
+            const int cnt = min(m, p1 - p);
+            if (!acquire()) return;
+            const unsigned char* st = myring + (size_t)slot * a.stage_bytes;
+            for (int i = 0; i < cnt; ++i) {
+                float acc0 = 0.f, acc1 = 0.f;
+                const unsigned char* r0 = st + (size_t)i * kRowsPerGroup * row_bytes;
+                if (!(a.debug & 1)) dot_rows<WT, 2, false>(r0, r0 + row_bytes, xs, a.K, 0, a.K, lane, acc0, acc1);
+                acc0 = warp_sum(acc0);
+                acc1 = warp_sum(acc1);
+                if (lane == 0) gemv_epilogue<EPI>(a, p + i, acc0, acc1);
+            }
+            release();
+        }
+    } else {
+        for (int p = p0; p < p1; ++p) {
+            float acc[kRowsPerGroup] = {0.f, 0.f};
+#pragma unroll
+            for (int r = 0; r < kRowsPerGroup; ++r)
+                for (int c = 0; c < nch; ++c) {
+                    if (!acquire()) return;
+                    const int k0 = c * a.kc;
+                    const int klen = min(a.kc, a.K - k0);
+                    const unsigned char* st = myring + (size_t)slot * a.stage_bytes;
+                    float dummy = 0.f;
+                    if (!(a.debug & 1)) dot_rows<WT, 1, false>(st, st, xs, a.K, k0, klen, lane, acc[r], dummy);
+                    release();
+                }
+            const float v0 = warp_sum(acc[0]), v1 = warp_sum(acc[1]);
+            if (lane == 0) gemv_epilogue<EPI>(a, p, v0, v1);
+        }
     }
 }
 
@@ -421,7 +494,7 @@ __global__ void __launch_bounds__(kGemvLdgThreads) gemv_ldg_kernel(const GemvArg
     for (int g = g0 + warp; g < g1; g += NW) {
         float acc0 = 0.f, acc1 = 0.f;
         const unsigned char* r0 = W + (size_t)g * kRowsPerGroup * row_bytes;
-        dot_rows<WT, true>(r0, r0 + row_bytes, xs, a.K, 0, a.K, lane, acc0, acc1);
+        dot_rows<WT, 2, true>(r0, r0 + row_bytes, xs, a.K, 0, a.K, lane, acc0, acc1);
         acc0 = warp_sum(acc0);
         acc1 = warp_sum(acc1);
         if (lane == 0) gemv_epilogue<EPI>(a, g, acc0, acc1);

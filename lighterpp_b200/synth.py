@@ -2,7 +2,7 @@
 
 Every tensor is drawn independently from ``numpy.random.default_rng([seed, tensor_id, layer])`` so a
 single layer (or a tensor-parallel rank's share of it) can be generated without materialising the
-whole model, and the same bytes come out whichever side (engine, oracle, file writer) asks.
+whole model, and the same bytes come out whichever side (engine, CPU checker, file writer) asks.
 Matrices and the embedding are N(0, 0.02) rounded to the model's weight dtype; RMSNorm weights are
 1.0, as in the benchmark configurations.
 """
@@ -26,6 +26,10 @@ SHAPES: Dict[str, Tuple[ModelConfig, str, bool, int]] = {
     "tiny-f32": (ModelConfig(96, 256, 2, 2, 2, 320, 40, 10000.0), "f32", True, 11),
     "tiny-gqa-f16": (ModelConfig(256, 704, 3, 8, 2, 1000, 96, 500000.0), "f16", False, 12),
     "tiny-tp8-f16": (ModelConfig(512, 1024, 2, 16, 8, 2048, 64, 500000.0), "f16", True, 13),
+    # the 8B shape's attention geometry (head size 128, 4 query heads per KV head) at toy width
+    "mini-8b-f16": (ModelConfig(1024, 3584, 2, 8, 2, 4096, 128, 500000.0), "f16", False, 14),
+    # long-context attention: seq_len large enough to exercise every KV split
+    "mini-long-f16": (ModelConfig(512, 1024, 2, 8, 2, 512, 4608, 500000.0), "f16", True, 15),
 }
 
 _TENSOR_ID = {"tok_emb": 0, "rms_att": 1, "wq": 2, "wk": 3, "wv": 4, "wo": 5, "rms_ffn": 6, "w1": 7, "w2": 8,
