@@ -185,6 +185,27 @@ lpp_status lpp_op_rope_scatter(float* d_q, const float* d_k, const float* d_v, v
 lpp_status lpp_op_sample(float* d_logits, int vocab_size, float temperature, float penalty, const int* d_history,
                          int history_len, float r, int* d_sampled_token, void* stream);
 
+/* lpp_op_sample for callers that must not allocate.  No counterpart in the reference: its
+ * cuda_sample works in place with shared memory only, while this library's multi-block sampler needs
+ * a few KiB of global scratch (step state, per-block partials, a ticket counter) that lpp_op_sample
+ * takes from the stream-ordered allocator on every call.  Some hosts cannot do that: a serving
+ * loop whose device memory was handed out in full at start-up, code that runs while another stream
+ * is being captured into a CUDA graph in global capture mode (where allocation calls are refused),
+ * or a real-time path that cannot tolerate an allocator's occasional synchronisation.  Here the
+ * scratch is a fixed array inside the library image (about 18 KiB per GPU, held from load until
+ * the process exits), so this call makes no allocation of any kind.
+ *
+ * Limits and rules: vocab_size <= 262144 and history_len <= 4096, otherwise LPP_ERR_TOO_LARGE
+ * (lpp_last_error() says which).  The first call on each device looks up the array's device address
+ * and must therefore run with that device current and outside any stream capture; later calls
+ * only launch kernels.  All calls on a device share the one array: two calls whose kernels can
+ * overlap on the GPU (different streams without ordering) race and give undefined results, so order
+ * them.  Everything that has to start clean is rewritten at the start of every call.  Arguments and
+ * result are those of lpp_op_sample. */
+lpp_status lpp_op_sample_static(float* d_logits, int vocab_size, float temperature, float penalty,
+                                const int* d_history, int history_len, float r, int* d_sampled_token,
+                                void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -73,7 +73,42 @@ lpp_status op_gemv_t(float* out, const float* x, const void* w, int n, int d, cu
     return chk();
 }
 
+// ---- scratch for lpp_op_sample_static: lives in the library image, one copy per GPU that loads it
+constexpr int kStaticSampleMaxVocab = 262144;  // 128 blocks of kSampleChunk logits
+constexpr size_t kStaticStateBytes = (sizeof(StepState) + 255) & ~(size_t)255;
+constexpr size_t kStaticPartialBytes = (size_t)(kStaticSampleMaxVocab / kSampleChunk) * 12;
+constexpr size_t kStaticScratchBytes = kStaticStateBytes + kStaticPartialBytes + 256;
+static __device__ __align__(256) unsigned char g_sample_scratch[kStaticScratchBytes];
+// Device addresses of g_sample_scratch, one per CUDA device, filled in on first use.  In host code
+// the name g_sample_scratch is only a handle for cudaGetSymbolAddress, never a pointer to pass on.
+static unsigned char* g_sample_scratch_addr[64];
+
+// Writes the step-state header the sampler reads, copies the history device-to-device and zeroes
+// the ticket counter -- everything in the shared scratch that must not survive from the last call.
+static __global__ void sample_static_setup_kernel(StepState* st, unsigned int* counter, float temperature,
+                                                  float penalty, float r, const int* history, int history_len) {
+    if (threadIdx.x == 0) {
+        st->token = 0;
+        st->pos = 0;
+        st->history_len = history_len;
+        st->history_window = 0;
+        st->history_count = 0;
+        st->step_idx = 0;
+        st->advance = 0;
+        st->temperature = temperature;
+        st->penalty = penalty;
+        st->r = r;
+        st->out_token = -1;
+        st->status = 0;
+        *counter = 0u;
+    }
+    for (int i = threadIdx.x; i < history_len; i += blockDim.x) st->history[i] = history[i];
+}
+static __global__ void sample_static_publish_kernel(const StepState* st, int* dst) { *dst = st->out_token; }
+
 }  // namespace
+
+void lpp_internal_set_error(const char* msg);  // engine.cu: text behind lpp_last_error()
 
 extern "C" {
 
@@ -207,6 +242,51 @@ lpp_status lpp_op_sample(float* d_logits, int vocab_size, float temperature, flo
     sample_kernel<<<nb, kSampleThreads, 0, s>>>(a);
     cudaMemcpyAsync(d_sampled_token, scratch + offsetof(StepState, out_token), sizeof(int), cudaMemcpyDeviceToDevice, s);
     cudaFreeAsync(scratch, s);
+    return chk();
+}
+
+lpp_status lpp_op_sample_static(float* d_logits, int vocab_size, float temperature, float penalty,
+                                const int* d_history, int history_len, float r, int* d_sampled_token, void* stream) {
+    if (!d_logits || !d_sampled_token || vocab_size <= 0 || history_len < 0) {
+        lpp_internal_set_error("lpp_op_sample_static: null pointer or non-positive size");
+        return LPP_ERR_INVALID_ARG;
+    }
+    if (vocab_size > kStaticSampleMaxVocab || history_len > kHistoryMax) {
+        lpp_internal_set_error("lpp_op_sample_static: vocab_size > 262144 or history_len > 4096 exceeds the built-in "
+                               "scratch; use lpp_op_sample, which sizes its scratch per call");
+        return LPP_ERR_TOO_LARGE;
+    }
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {
+        lpp_internal_set_error("lpp_op_sample_static: no current CUDA device");
+        return LPP_ERR_CUDA;
+    }
+    if (!g_sample_scratch_addr[dev]) {
+        // one-time set-up for this device (it must be the current one): resolve where the symbol lives
+        unsigned char* p = nullptr;
+        const cudaError_t ge = cudaGetSymbolAddress((void**)&p, g_sample_scratch);
+        if (ge != cudaSuccess || !p) {
+            lpp_internal_set_error(cudaGetErrorString(ge));
+            return LPP_ERR_CUDA;
+        }
+        g_sample_scratch_addr[dev] = p;
+    }
+    unsigned char* scratch = g_sample_scratch_addr[dev];
+    cudaStream_t s = S(stream);
+    const int nb = (vocab_size + kSampleChunk - 1) / kSampleChunk;
+    const bool use_hist = penalty > 1.0f && d_history && history_len > 0;
+    SampleArgs a = {};
+    a.logits = d_logits;
+    a.vocab = vocab_size;
+    a.st = (StepState*)scratch;
+    a.part_max = (float*)(scratch + kStaticStateBytes);
+    a.part_idx = (int*)(scratch + kStaticStateBytes + (size_t)nb * 4);
+    a.part_sum = (float*)(scratch + kStaticStateBytes + (size_t)nb * 8);
+    a.counter = (unsigned int*)(scratch + kStaticStateBytes + kStaticPartialBytes);
+    sample_static_setup_kernel<<<1, 256, 0, s>>>(a.st, a.counter, temperature, penalty, r, use_hist ? d_history : nullptr,
+                                                 use_hist ? history_len : 0);
+    sample_kernel<<<nb, kSampleThreads, 0, s>>>(a);
+    sample_static_publish_kernel<<<1, 1, 0, s>>>(a.st, d_sampled_token);
     return chk();
 }
 

@@ -34,7 +34,7 @@ EXPORTS = [
     "lpp_step_bytes", "lpp_profile_step", "lpp_op_convert_f32_to_f16", "lpp_op_gemv", "lpp_op_rmsnorm",
     "lpp_op_rope", "lpp_op_swiglu", "lpp_op_softmax_multihead", "lpp_op_scale_multihead",
     "lpp_op_aggregation_multihead", "lpp_op_residual_add", "lpp_op_scatter_kv", "lpp_op_multihead_gemv",
-    "lpp_op_rope_scatter", "lpp_op_sample",
+    "lpp_op_rope_scatter", "lpp_op_sample", "lpp_op_sample_static",
 ]
 
 
