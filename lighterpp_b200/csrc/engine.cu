@@ -355,7 +355,7 @@ static void matrix_span(const lpp_engine* e, int kind, int l, const void** ptr, 
     }
 }
 // What the GEMV (kind, l) should pull towards L2 for its successor in the step: the next matrix, or
-// its first LPP_PF_MB MiB (default 32) when it is larger.  The classifier's successor is the first
+// its first LPP_PF_MB MiB (default 8) when it is larger.  The classifier's successor is the first
 // layer's QKV matrix of the next token.
 static void set_prefetch(const lpp_engine* e, GemvArgs& a, int kind, int l) {
     int nk, nl = l;
@@ -366,7 +366,7 @@ static void set_prefetch(const lpp_engine* e, GemvArgs& a, int kind, int l) {
         case kDown: nk = (l + 1 < e->c.n_layers) ? kQkv : kLmHead; nl = l + 1; break;
         default: nk = kQkv; nl = 0; break;
     }
-    size_t cap = 32;
+    size_t cap = 8;
     if (const char* v = getenv("LPP_PF_MB")) cap = (size_t)std::max(0, atoi(v));
     const void* p;
     size_t bytes;
