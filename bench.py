@@ -187,7 +187,7 @@ def run_ours(args, rank, world):
     if rank == 0:
         peak, peak_kind = measured_peak()
         us = dev_ms * 1e3 / args.steps
-        gemv = {k: v for k, v in prof.items() if k.endswith("gemv") and v["launches"]}
+        gemv = {k: v for k, v in prof.items() if (k.endswith("gemv") or k == "step_kernel") and v["launches"]}
         dom = max(gemv, key=lambda k: gemv[k]["ms"])
         d = gemv[dom]
         per_launch_bytes = d["bytes"] / d["launches"]

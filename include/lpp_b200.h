@@ -60,6 +60,8 @@ typedef enum {
 #define LPP_FLAG_GEMV_LDG 0x1u   /* stream weights with 128-bit global loads instead of the bulk-copy ring */
 #define LPP_FLAG_NO_PDL 0x2u     /* plain stream order between kernels (no programmatic dependent launch) */
 #define LPP_FLAG_NO_GRAPH 0x4u   /* launch the step kernel by kernel instead of replaying the CUDA graph */
+#define LPP_FLAG_PERSISTENT 0x8u /* one persistent kernel with grid barriers per run of phases instead of one
+                                    kernel per phase (measured slower on B200; kept for comparison) */
 
 /* Mirror of the reference Config (src/model.h:21-31) plus what a device engine needs. */
 typedef struct {
@@ -153,8 +155,9 @@ int64_t lpp_step_bytes(const lpp_engine* e, int pos);
 /* Per-kernel-kind timing of one step at `pos`: the step is captured with a CUDA event-record node
  * before and after every kernel and replayed iters times (isolated kernel durations, no programmatic
  * overlap, no host launch latency).  kinds: 0 qkv gemv, 1 attention, 2 o_proj gemv, 3 gate|up gemv, 4 down gemv,
- * 5 lm-head gemv, 6 sampler, 7 all-reduce.  ms[8] total device ms per step per kind, launches[8]
- * launches per step, bytes[8] algorithmic bytes per step. */
+ * 5 lm-head gemv, 6 sampler, 7 all-reduce, 8 persistent step kernel (all GEMV and attention phases of
+ * a run in one launch; kinds 0-5 then stay empty), 9 reserved.  ms[10] total device ms per step per
+ * kind, launches[10] launches per step, bytes[10] algorithmic bytes per step. */
 lpp_status lpp_profile_step(lpp_engine* e, int pos, int iters, float* ms, int* launches, int64_t* bytes);
 
 /* ---- standalone operators: the host wrappers of src/kernels.cuh:24-36, device pointers in/out,

@@ -41,6 +41,7 @@ struct AttnArgs {
     unsigned int* counters;  // [kv_heads * gqa/GB], zero between launches
     const StepState* st;
     int seq_len, head_size, gqa, n_splits;
+    int n_kv_heads;  // KV heads on this rank
 };
 
 template <typename KT, int DPL>
@@ -96,23 +97,22 @@ __device__ __forceinline__ void merge_state(float& m, float& l, float (&acc)[DPL
     m = mn;
 }
 
-// DPL = head_size / 8 (dims per lane), GB = query heads handled per CTA (divides gqa).
-template <typename KT, int DPL, int GB>
-__global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const AttnArgs a) {
+__device__ __forceinline__ void team_barrier(int id, int nthreads) {
+    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
+}
+
+// One work item = (split, kv head, batch hz of GB query heads) at sequence length T with n_eff
+// splits in use, executed by a team of 128 threads (tid 0..127) that synchronise on named barrier
+// `bar`.  `scratch` holds [NT/32 warps][GB][HS+2] floats of shared memory, `s_last` one int.
+// DPL = head_size / 8 (dims per lane), GB = query heads per item (divides gqa), n_z = gqa / GB,
+// NT = threads in the team (128 for the stand-alone kernel, 256 when a GEMV CTA's consumers run it).
+template <typename KT, int DPL, int GB, int NT = kAttnThreads>
+__device__ __forceinline__ void attn_item(const AttnArgs& a, int split, int kvh, int hz, int n_z, int T, int n_eff,
+                                          float* scratch, int* s_last, int tid, int bar) {
     constexpr int HS = DPL * 8;
-    __shared__ float s_state[kAttnThreads / 32][GB][HS + 2];
-    __shared__ int s_last;
-
-    pdl_launch_dependents();  // the next GEMV may start streaming its weights now
-    pdl_wait();
-
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    float (*s_state)[GB][HS + 2] = reinterpret_cast<float (*)[GB][HS + 2]>(scratch);
+    const int warp = tid >> 5, lane = tid & 31;
     const int sub = lane & 7, grp = warp * 4 + (lane >> 3);
-    const int split = blockIdx.x, kvh = blockIdx.y, hz = blockIdx.z;
-    const int pos = a.st->pos;
-    const int T = (pos < 0 || pos >= a.seq_len) ? 0 : pos + 1;
-    const int n_eff = attn_effective_splits(T, a.n_splits);
-    if (split >= n_eff) return;  // surplus CTA at this sequence length: no work, no ticket
     const int chunk = (T + n_eff - 1) / n_eff;
     const int t0 = split * chunk;
     const int t1 = min(T, t0 + chunk);
@@ -134,51 +134,64 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const AttnArg
     const KT* kbase = reinterpret_cast<const KT*>(a.k_cache) + (size_t)kvh * a.seq_len * HS + sub * DPL;
     const KT* vbase = reinterpret_cast<const KT*>(a.v_cache) + (size_t)kvh * a.seq_len * HS + sub * DPL;
 
-    // Two positions per 8-lane group and iteration, so four independent 16-byte loads are in flight
-    // per lane.  The trip count depends only on (t0, t1) and is therefore the same for every lane:
-    // the shuffles below need all 32 lanes, so lanes whose position is past the end run the
+    // U positions per 8-lane group and iteration: all their K and V loads (2*U independent 16-byte
+    // loads per lane) are issued before any is used, so a chunk of up to U*16 positions costs one
+    // memory round trip.  The trip count depends only on (t0, t1) and is therefore the same for every
+    // lane: the shuffles below need all 32 lanes, so lanes whose position is past the end run the
     // iteration with zeros and are masked out of the softmax update.
-    for (int base = t0; base < t1; base += 2 * kAttnGroups) {
-        const int ta = base + grp, tb = ta + kAttnGroups;
-        const bool has_a = ta < t1, has_b = tb < t1;
-        float ka[DPL], va[DPL], kb[DPL], vb[DPL];
-        if (has_a) {
-            load_row_slice<KT, DPL>(kbase + (size_t)ta * HS, ka);
-            load_row_slice<KT, DPL>(vbase + (size_t)ta * HS, va);
-        } else {
+    constexpr int U = (DPL <= 8) ? 4 : 2;
+    for (int base = t0; base < t1; base += U * (NT / 8)) {
+        float kk[U][DPL], vv[U][DPL];
+        bool has[U];
 #pragma unroll
-            for (int d = 0; d < DPL; ++d) ka[d] = va[d] = 0.f;
-        }
-        if (has_b) {
-            load_row_slice<KT, DPL>(kbase + (size_t)tb * HS, kb);
-            load_row_slice<KT, DPL>(vbase + (size_t)tb * HS, vb);
-        } else {
+        for (int u = 0; u < U; ++u) {
+            const int t = base + u * (NT / 8) + grp;
+            has[u] = t < t1;
+            if (has[u]) {
+                load_row_slice<KT, DPL>(kbase + (size_t)t * HS, kk[u]);
+                load_row_slice<KT, DPL>(vbase + (size_t)t * HS, vv[u]);
+            } else {
 #pragma unroll
-            for (int d = 0; d < DPL; ++d) kb[d] = vb[d] = 0.f;
+                for (int d = 0; d < DPL; ++d) kk[u][d] = vv[u][d] = 0.f;
+            }
         }
 #pragma unroll
         for (int h = 0; h < GB; ++h) {
-            float sa = 0.f, sb = 0.f;
+            float sc[U];
 #pragma unroll
-            for (int d = 0; d < DPL; ++d) {
-                sa = fmaf(q[h][d], ka[d], sa);
-                sb = fmaf(q[h][d], kb[d], sb);
+            for (int u = 0; u < U; ++u) {
+                float x = 0.f;
+#pragma unroll
+                for (int d = 0; d < DPL; ++d) x = fmaf(q[h][d], kk[u][d], x);
+                sc[u] = x;
             }
 #pragma unroll
             for (int o = 1; o < 8; o <<= 1) {
-                sa += __shfl_xor_sync(0xffffffffu, sa, o);
-                sb += __shfl_xor_sync(0xffffffffu, sb, o);
+#pragma unroll
+                for (int u = 0; u < U; ++u) sc[u] += __shfl_xor_sync(0xffffffffu, sc[u], o);
             }
-            sa = has_a ? sa * scale : -INFINITY;
-            sb = has_b ? sb * scale : -INFINITY;
-            const float mn = fmaxf(m[h], fmaxf(sa, sb));
+            float mn = m[h];
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                sc[u] = has[u] ? sc[u] * scale : -INFINITY;
+                mn = fmaxf(mn, sc[u]);
+            }
             if (mn != -INFINITY) {  // per-lane predicate; no warp-collective inside
                 const float alpha = (m[h] == -INFINITY) ? 0.f : __expf(m[h] - mn);
-                const float pa = has_a ? __expf(sa - mn) : 0.f;
-                const float pb = has_b ? __expf(sb - mn) : 0.f;
-                l[h] = l[h] * alpha + pa + pb;
+                float pu[U], ls = 0.f;
 #pragma unroll
-                for (int d = 0; d < DPL; ++d) acc[h][d] = fmaf(pb, vb[d], fmaf(pa, va[d], acc[h][d] * alpha));
+                for (int u = 0; u < U; ++u) {
+                    pu[u] = has[u] ? __expf(sc[u] - mn) : 0.f;
+                    ls += pu[u];
+                }
+                l[h] = l[h] * alpha + ls;
+#pragma unroll
+                for (int d = 0; d < DPL; ++d) {
+                    float x = acc[h][d] * alpha;
+#pragma unroll
+                    for (int u = 0; u < U; ++u) x = fmaf(pu[u], vv[u][d], x);
+                    acc[h][d] = x;
+                }
                 m[h] = mn;
             }
         }
@@ -205,13 +218,13 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const AttnArg
             }
         }
     }
-    __syncthreads();
+    team_barrier(bar, NT);
 
     // merge the warps; with a single split the result is final, otherwise it is this split's partial
-    constexpr int NW = kAttnThreads / 32;
+    constexpr int NW = NT / 32;
     float* part = a.part;
     const int PS = HS + 2;
-    for (int idx = tid; idx < GB * HS; idx += kAttnThreads) {
+    for (int idx = tid; idx < GB * HS; idx += NT) {
         const int h = idx / HS, d = idx % HS;
         float mm = -INFINITY;
 #pragma unroll
@@ -235,31 +248,26 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const AttnArg
             }
         }
     }
-    if (n_eff == 1) return;  // short context: no partials, no ticket, no second pass
-    __threadfence();
-    __syncthreads();
-    if (tid == 0) {
-        const unsigned int ticket = atomicAdd(&a.counters[kvh * gridDim.z + hz], 1u);
-        s_last = (ticket == (unsigned int)n_eff - 1);
+    if (n_eff == 1) {
+        team_barrier(bar, NT);  // scratch may be reused by the team's next item
+        return;  // short context: no partials, no ticket, no second pass
     }
-    __syncthreads();
-    if (!s_last) return;
+    __threadfence();
+    team_barrier(bar, NT);
+    if (tid == 0) {
+        const unsigned int ticket = atomicAdd(&a.counters[kvh * n_z + hz], 1u);
+        *s_last = (ticket == (unsigned int)n_eff - 1);
+    }
+    team_barrier(bar, NT);
+    if (!*s_last) return;
     __threadfence();
 
-    // last CTA of this (kv head, head batch): combine the splits in index order.  Loads are issued
-    // in batches of eight before they are consumed so the L2 latency is paid once per batch.
-    for (int idx = tid; idx < GB * HS; idx += kAttnThreads) {
+    // last team of this (kv head, head batch): combine the splits in index order.  Loads are issued
+    // in batches of eight before they are consumed; up to eight splits need a single round trip.
+    for (int idx = tid; idx < GB * HS; idx += NT) {
         const int h = idx / HS, d = idx % HS;
         const float* p = part + (size_t)(hbase + h) * a.n_splits * PS;
-        float mm = -INFINITY;
-        for (int s0 = 0; s0 < n_eff; s0 += 8) {
-            float ms[8];
-#pragma unroll
-            for (int i = 0; i < 8; ++i) ms[i] = (s0 + i < n_eff) ? __ldcg(p + (size_t)(s0 + i) * PS + HS) : -INFINITY;
-#pragma unroll
-            for (int i = 0; i < 8; ++i) mm = fmaxf(mm, ms[i]);
-        }
-        float av = 0.f, lv = 0.f;
+        float mm = -INFINITY, av = 0.f, lv = 0.f;
         for (int s0 = 0; s0 < n_eff; s0 += 8) {
             float ms[8], ls[8], as[8];
 #pragma unroll
@@ -270,16 +278,37 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const AttnArg
                 ls[i] = ok ? __ldcg(ps + HS + 1) : 0.f;
                 as[i] = ok ? __ldcg(ps + d) : 0.f;
             }
+            float mb = mm;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) mb = fmaxf(mb, ms[i]);
+            // rescale what has been accumulated so far to the new running maximum (fixed order)
+            const float fo = (mm == -INFINITY) ? 0.f : __expf(mm - mb);
+            av *= fo;
+            lv *= fo;
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
-                const float f = (ms[i] == -INFINITY) ? 0.f : __expf(ms[i] - mm);
+                const float f = (ms[i] == -INFINITY) ? 0.f : __expf(ms[i] - mb);
                 av = fmaf(as[i], f, av);
                 lv = fmaf(ls[i], f, lv);
             }
+            mm = mb;
         }
         a.out[(size_t)(hbase + h) * HS + d] = (lv > 0.f) ? __fdiv_rn(av, lv) : 0.f;
     }
-    if (tid == 0) a.counters[kvh * gridDim.z + hz] = 0u;
+    if (tid == 0) a.counters[kvh * n_z + hz] = 0u;
+}
+
+template <typename KT, int DPL, int GB>
+__global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const AttnArgs a) {
+    __shared__ float s_scratch[(kAttnThreads / 32) * GB * (DPL * 8 + 2)];
+    __shared__ int s_last;
+    pdl_launch_dependents();  // the next GEMV may start streaming its weights now
+    pdl_wait();
+    const int pos = a.st->pos;
+    const int T = (pos < 0 || pos >= a.seq_len) ? 0 : pos + 1;
+    const int n_eff = attn_effective_splits(T, a.n_splits);
+    if ((int)blockIdx.x >= n_eff) return;  // surplus CTA at this sequence length: no work, no ticket
+    attn_item<KT, DPL, GB>(a, blockIdx.x, blockIdx.y, blockIdx.z, gridDim.z, T, n_eff, s_scratch, &s_last, threadIdx.x, 0);
 }
 
 }  // namespace lpp

@@ -34,6 +34,7 @@
 #include "gemv.cuh"
 #include "ops.cuh"
 #include "sampler.cuh"
+#include "step.cuh"
 
 using namespace lpp;
 
@@ -112,7 +113,7 @@ static bool load() {
 
 // ------------------------------------------------------------------ engine
 
-enum Kind { kQkv = 0, kAttn = 1, kOproj = 2, kGateUp = 3, kDown = 4, kLmHead = 5, kSampler = 6, kAllReduce = 7, kKinds = 8 };
+enum Kind { kQkv = 0, kAttn = 1, kOproj = 2, kGateUp = 3, kDown = 4, kLmHead = 5, kSampler = 6, kAllReduce = 7, kStepKernel = 8, kKinds = 10 };
 
 struct lpp_engine {
     lpp_config c;
@@ -143,8 +144,19 @@ struct lpp_engine {
     // upload staging
     void* stage = nullptr;
     size_t stage_bytes = 0;
+    // persistent step kernel: phase table (host copy + device), per-launch grid-barrier counters
+    bool persistent = false;
+    std::vector<StepPhase> h_phases;
+    StepPhase* d_phases = nullptr;
+    unsigned int* gbar = nullptr;
+    int n_gbar = 0;
+    unsigned long long* trace = nullptr;  // LPP_STEP_TRACE: per-CTA per-phase time stamps
+    int step_slots = 2, step_xs_bytes = 0;
+    size_t step_smem = 0;
     // graphs
-    cudaGraphExec_t g_full = nullptr, g_logits = nullptr;
+    // graph variants by context length; only [0] is used at present
+    cudaGraphExec_t g_full[2] = {nullptr, nullptr}, g_logits[2] = {nullptr, nullptr};
+
     bool finalized = false;
     int kernels_full = 0;
     cudaEvent_t ev0 = nullptr, ev1 = nullptr;
@@ -183,6 +195,23 @@ struct GemvPlan {
     size_t smem;
 };
 
+constexpr int kStageTarget = 8192;  // bytes per bulk copy / ring slot (see gemv.cuh)
+
+// A stage is one bulk copy of about stage_target bytes: whole row pairs when they fit, else one
+// K-chunk of one row.
+static void gemv_geometry(GemvArgs& a, int esz, int stage_target) {
+    const int pair_bytes = kRowsPerGroup * a.K * esz;
+    if (pair_bytes <= stage_target) {
+        a.pairs_per_stage = stage_target / pair_bytes;
+        a.kc = a.K;
+        a.stage_bytes = a.pairs_per_stage * pair_bytes;
+    } else {
+        a.pairs_per_stage = 0;
+        a.kc = std::max(8, std::min(a.K, stage_target / esz) / 8 * 8);
+        a.stage_bytes = a.kc * esz;
+    }
+}
+
 template <typename WT, int EPI>
 static cudaError_t launch_gemv_t(lpp_engine* e, GemvArgs& a, bool pdl, cudaStream_t s) {
     const int esz = sizeof(WT);
@@ -200,20 +229,10 @@ static cudaError_t launch_gemv_t(lpp_engine* e, GemvArgs& a, bool pdl, cudaStrea
         const int grid = std::max(1, std::min(groups, e->num_sms * 4));
         return launch_kernel(gemv_ldg_kernel<WT, EPI>, dim3(grid), dim3(kGemvLdgThreads), smem, s, pdl, a);
     }
-    // A stage is one bulk copy of about stage_target bytes: whole row pairs when they fit, else one
-    // K-chunk of one row.  LPP_STAGE_KB (timing experiments) overrides the 8 KiB default.
-    int stage_target = 8192;
+    // LPP_STAGE_KB (timing experiments) overrides the 8 KiB stage size.
+    int stage_target = kStageTarget;
     if (const char* sk = getenv("LPP_STAGE_KB")) stage_target = std::max(1, atoi(sk)) * 1024;
-    const int pair_bytes = kRowsPerGroup * a.K * esz;
-    if (pair_bytes <= stage_target) {
-        a.pairs_per_stage = stage_target / pair_bytes;
-        a.kc = a.K;
-        a.stage_bytes = a.pairs_per_stage * pair_bytes;
-    } else {
-        a.pairs_per_stage = 0;
-        a.kc = std::max(8, std::min(a.K, stage_target / esz) / 8 * 8);
-        a.stage_bytes = a.kc * esz;
-    }
+    gemv_geometry(a, esz, stage_target);
     const size_t fixed = kGemvBarrierBytes + 128 + xbytes;
     size_t ring = (size_t)(e->c.ring_kb > 0 ? e->c.ring_kb : 128) * 1024;
     if (fixed + ring > e->smem_optin) ring = e->smem_optin - fixed;
@@ -281,6 +300,11 @@ struct Recorder {
     cudaStream_t s;
     bool prev_kernel = false;  // previous stream item was one of our kernels -> PDL edge allowed
     int kernels = 0;
+    // persistent mode: phases are either collected into the engine's table (collect) or, once the
+    // table exists, counted off and launched as runs of consecutive phases
+    bool collect = false;
+    int cursor = 0, pending = 0, launch_idx = 0;
+    bool short_ctx = false;  // record the short-context variant of the step
     cudaError_t err = cudaSuccess;
     std::string where;
 
@@ -309,6 +333,42 @@ struct Recorder {
     }
 };
 
+// ---- persistent step kernel dispatch
+
+template <typename WT, typename KT, int DPL>
+static cudaError_t launch_step_g(lpp_engine* e, const StepArgs& sa, bool pdl, cudaStream_t s) {
+    auto go = [&](auto kernel) -> cudaError_t {
+        static bool attr_done[64] = {};
+        if (!attr_done[e->c.device & 63]) {
+            cudaError_t r = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)e->smem_optin);
+            if (r != cudaSuccess) return r;
+            attr_done[e->c.device & 63] = true;
+        }
+        return launch_kernel(kernel, dim3(e->num_sms), dim3(kGemvRingThreads), e->step_smem, s, pdl, sa);
+    };
+    switch (e->attn_gb) {
+        case 4: return go(step_kernel<WT, KT, DPL, 4>);
+        case 2: return go(step_kernel<WT, KT, DPL, 2>);
+        default: return go(step_kernel<WT, KT, DPL, 1>);
+    }
+}
+template <typename WT, typename KT>
+static cudaError_t launch_step_t(lpp_engine* e, const StepArgs& sa, bool pdl, cudaStream_t s) {
+    switch (e->hs / 8) {
+        case 4: return launch_step_g<WT, KT, 4>(e, sa, pdl, s);
+        case 6: return launch_step_g<WT, KT, 6>(e, sa, pdl, s);
+        case 8: return launch_step_g<WT, KT, 8>(e, sa, pdl, s);
+        case 16: return launch_step_g<WT, KT, 16>(e, sa, pdl, s);
+    }
+    return cudaErrorInvalidValue;
+}
+// The persistent kernel is instantiated for FP16 weights + FP16 cache and FP32 weights + FP32 cache,
+// head sizes 32/48/64/128; other combinations use the kernel-per-phase path.
+static bool step_kernel_supported(const lpp_engine* e) {
+    const int d = e->hs / 8;
+    return e->c.weight_dtype == e->c.kv_dtype && (d == 4 || d == 6 || d == 8 || d == 16);
+}
+
 // LPP_DEBUG_SKIP=<bitmask of Kind> leaves those kernels out of the step (results become
 // meaningless): a timing aid that shows what each kernel kind costs inside the replayed graph.
 static unsigned skip_mask() {
@@ -316,8 +376,52 @@ static unsigned skip_mask() {
     return v ? (unsigned)strtol(v, nullptr, 0) : 0u;
 }
 
+// Persistent mode: launches the phases counted since the last flush as one step-kernel run.
+static void flush_phases(Recorder& R) {
+    lpp_engine* e = R.e;
+    if (!e->persistent || R.collect || R.pending == 0) return;
+    StepArgs sa = {};
+    sa.phases = e->d_phases;
+    sa.first = R.cursor - R.pending;
+    sa.count = R.pending;
+    sa.gbar = e->gbar + R.launch_idx++;
+    sa.st = e->st;
+    sa.n_slots = e->step_slots;
+    sa.slot_bytes = kStageTarget;
+    sa.xs_bytes = e->step_xs_bytes;
+    sa.trace = e->trace;
+    R.mark(kStepKernel);
+    R.check(e->c.weight_dtype == LPP_F16 ? launch_step_t<__half, __half>(e, sa, R.pdl(), R.s)
+                                         : launch_step_t<float, float>(e, sa, R.pdl(), R.s),
+            "step kernel launch");
+    R.mark(-1);
+    R.prev_kernel = true;
+    R.kernels++;
+    R.pending = 0;
+}
+
+static void record_phase(Recorder& R, const StepPhase& ph) {
+    if (R.collect) R.e->h_phases.push_back(ph);
+    R.cursor++;
+    R.pending++;
+}
+
 static void record_gemv(Recorder& R, int kind, int epi, GemvArgs a) {
     lpp_engine* e = R.e;
+    if (e->persistent) {
+        a.st = e->st;
+        a.vocab = e->c.vocab_size;
+        a.seq_len = e->c.seq_len;
+        a.pf = nullptr;
+        a.pf_bytes = 0;
+        gemv_geometry(a, e->esz, kStageTarget);
+        StepPhase ph = {};
+        ph.type = kPhaseGemv;
+        ph.epi = epi;
+        ph.g = a;
+        record_phase(R, ph);
+        return;
+    }
     if (skip_mask() & (1u << kind)) return;
     a.st = e->st;
     if (const char* dbg = getenv("LPP_DEBUG_GEMV")) a.debug = (int)strtol(dbg, nullptr, 0);
@@ -332,6 +436,8 @@ static void record_gemv(Recorder& R, int kind, int epi, GemvArgs a) {
 
 static void record_allreduce(Recorder& R, float* buf, int n) {
     lpp_engine* e = R.e;
+    flush_phases(R);
+    if (R.collect) return;
     R.mark(kAllReduce);
     nccl::result_t r = nccl::AllReduce(buf, buf, (size_t)n, nccl::kFloat32, nccl::kSum, e->comm, R.s);
     if (r != 0 && R.err == cudaSuccess) {
@@ -407,32 +513,38 @@ static void record_step(Recorder& R, bool with_sampler) {
             a.k_cache = (char*)e->kcache + lofs;
             a.v_cache = (char*)e->vcache + lofs;
             a.kv_is_f32 = c.kv_dtype == LPP_F32;
-            set_prefetch(e, a, kQkv, l);
-            record_gemv(R, kQkv, kEpiQkv, a);
-        }
-        {  // split-KV flash decode
-            AttnArgs a = {};
-            a.q = e->q;
-            const size_t lofs = (size_t)l * e->KVHl * c.seq_len * e->hs * e->kvesz;
-            a.k_cache = (char*)e->kcache + lofs;
-            a.v_cache = (char*)e->vcache + lofs;
-            a.out = e->att_out;
-            a.part = e->attn_part;
-            a.counters = e->attn_counters;
-            a.st = e->st;
-            a.seq_len = c.seq_len;
-            a.head_size = e->hs;
-            a.gqa = e->gqa;
-            a.n_splits = e->attn_splits;
-            dim3 grid(e->attn_splits, e->KVHl, e->attn_z);
-            if (!(skip_mask() & (1u << kAttn))) {
-            R.mark(kAttn);
-            R.check(c.kv_dtype == LPP_F32 ? launch_attn_t<float>(e, a, grid, R.pdl(), R.s)
-                                          : launch_attn_t<__half>(e, a, grid, R.pdl(), R.s),
-                    "attention launch");
-            R.mark(-1);
-            R.prev_kernel = true;
-            R.kernels++;
+            // split-KV flash decode
+            AttnArgs at = {};
+            at.q = e->q;
+            at.k_cache = a.k_cache;
+            at.v_cache = a.v_cache;
+            at.out = e->att_out;
+            at.part = e->attn_part;
+            at.counters = e->attn_counters;
+            at.st = e->st;
+            at.seq_len = c.seq_len;
+            at.head_size = e->hs;
+            at.gqa = e->gqa;
+            at.n_splits = e->attn_splits;
+            at.n_kv_heads = e->KVHl;
+            {
+                set_prefetch(e, a, kQkv, l);
+                record_gemv(R, kQkv, kEpiQkv, a);
+                dim3 grid(e->attn_splits, e->KVHl, e->attn_z);
+                if (e->persistent) {
+                    StepPhase ph = {};
+                    ph.type = kPhaseAttn;
+                    ph.at = at;
+                    record_phase(R, ph);
+                } else if (!(skip_mask() & (1u << kAttn))) {
+                    R.mark(kAttn);
+                    R.check(c.kv_dtype == LPP_F32 ? launch_attn_t<float>(e, at, grid, R.pdl(), R.s)
+                                                  : launch_attn_t<__half>(e, at, grid, R.pdl(), R.s),
+                            "attention launch");
+                    R.mark(-1);
+                    R.prev_kernel = true;
+                    R.kernels++;
+                }
             }
         }
         {  // o_proj + residual
@@ -488,8 +600,17 @@ static void record_step(Recorder& R, bool with_sampler) {
         set_prefetch(e, a, kLmHead, 0);
         record_gemv(R, kLmHead, kEpiStore, a);
     }
+    flush_phases(R);
+    if (R.collect) return;
+    if (e->persistent && !with_sampler && e->n_gbar > 0) {
+        // no sampler in this graph to clear the grid-barrier counters: a memset node does it
+        R.check(cudaMemsetAsync(e->gbar, 0, (size_t)e->n_gbar * sizeof(unsigned int), R.s), "gbar memset");
+        R.prev_kernel = false;
+    }
     if (with_sampler && !(skip_mask() & (1u << kSampler))) {
         SampleArgs a = {};
+        a.zero = e->persistent ? e->gbar : nullptr;
+        a.zero_n = e->persistent ? e->n_gbar : 0;
         a.logits = e->logits;
         a.vocab = c.vocab_size;
         a.st = e->st;
@@ -508,10 +629,11 @@ static void record_step(Recorder& R, bool with_sampler) {
     }
 }
 
-static lpp_status capture(lpp_engine* e, bool with_sampler, cudaGraphExec_t* out, int* kernels) {
+static lpp_status capture(lpp_engine* e, bool with_sampler, bool short_ctx, cudaGraphExec_t* out, int* kernels) {
     cudaGraph_t g = nullptr;
     CU(cudaStreamBeginCapture(e->stream, cudaStreamCaptureModeThreadLocal));
     Recorder R{e, e->stream};
+    R.short_ctx = short_ctx;
     record_step(R, with_sampler);
     cudaError_t ce = cudaStreamEndCapture(e->stream, &g);
     if (R.err != cudaSuccess) {
@@ -527,14 +649,18 @@ static lpp_status capture(lpp_engine* e, bool with_sampler, cudaGraphExec_t* out
     return LPP_OK;
 }
 
-static lpp_status run_step(lpp_engine* e, bool with_sampler) {
+// pos: the position this step runs at (known to the host in every mode); it selects the variant.
+static lpp_status run_step(lpp_engine* e, bool with_sampler, int pos) {
+    const int v = 0;  // a single graph variant serves every position
+    (void)pos;
     if (e->c.flags & LPP_FLAG_NO_GRAPH) {
         Recorder R{e, e->stream};
+        R.short_ctx = v == 1;
         record_step(R, with_sampler);
         if (R.err != cudaSuccess) return fail(LPP_ERR_CUDA, "%s: %s", R.where.c_str(), cudaGetErrorString(R.err));
         return LPP_OK;
     }
-    CU(cudaGraphLaunch(with_sampler ? e->g_full : e->g_logits, e->stream));
+    CU(cudaGraphLaunch(with_sampler ? e->g_full[v] : e->g_logits[v], e->stream));
     return LPP_OK;
 }
 
@@ -693,13 +819,15 @@ extern "C" lpp_status lpp_engine_destroy(lpp_engine* e) {
     if (!e) return LPP_OK;
     cudaSetDevice(e->c.device);
     if (e->stream) cudaStreamSynchronize(e->stream);
-    if (e->g_full) cudaGraphExecDestroy(e->g_full);
-    if (e->g_logits) cudaGraphExecDestroy(e->g_logits);
+    for (int v = 0; v < 2; ++v) {
+        if (e->g_full[v]) cudaGraphExecDestroy(e->g_full[v]);
+        if (e->g_logits[v]) cudaGraphExecDestroy(e->g_logits[v]);
+    }
     if (e->comm) nccl::CommDestroy(e->comm);
     void* bufs[] = {e->wqkv, e->wo, e->w13, e->w2, e->emb, e->wcls_owned ? e->wcls : nullptr, e->rms_att, e->rms_ffn,
                     e->rms_final, e->kcache, e->vcache, e->xa, e->xb, e->q, e->att_out, e->hb, e->logits,
                     e->attn_part, e->attn_counters, e->samp_max, e->samp_sum, e->samp_idx, e->samp_counter,
-                    e->r_values, e->out_tokens, e->st, e->rope, e->stage};
+                    e->r_values, e->out_tokens, e->st, e->rope, e->stage, e->d_phases, e->gbar, e->trace};
     for (void* p : bufs)
         if (p) cudaFree(p);
     if (e->h_st) cudaFreeHost(e->h_st);
@@ -848,16 +976,50 @@ extern "C" lpp_status lpp_finalize(lpp_engine* e) {
         e->stage = nullptr;
         e->stage_bytes = 0;
     }
-    if (e->g_full) cudaGraphExecDestroy(e->g_full), e->g_full = nullptr;
-    if (e->g_logits) cudaGraphExecDestroy(e->g_logits), e->g_logits = nullptr;
+    for (int v = 0; v < 2; ++v) {
+        if (e->g_full[v]) cudaGraphExecDestroy(e->g_full[v]), e->g_full[v] = nullptr;
+        if (e->g_logits[v]) cudaGraphExecDestroy(e->g_logits[v]), e->g_logits[v] = nullptr;
+    }
     TRACE("finalize: weights complete");
+    // ---- persistent step kernel: phase table, ring/scratch geometry, grid-barrier counters
+    e->persistent = (c.flags & LPP_FLAG_PERSISTENT) && !(c.flags & LPP_FLAG_GEMV_LDG) && step_kernel_supported(e);
+    if (e->persistent) {
+        int maxK = std::max(c.dim, std::max(e->Fl, e->Dq));
+        const size_t attn_scratch = 2ull * (kAttnThreads / 32) * e->attn_gb * (e->hs + 2) * sizeof(float);
+        e->step_xs_bytes = (int)align_up(std::max((size_t)maxK * 4, attn_scratch), 128);
+        const size_t fixed = kGemvBarrierBytes + 128 + e->step_xs_bytes;
+        size_t ring = (size_t)(c.ring_kb > 0 ? c.ring_kb : 128) * 1024;
+        if (fixed + ring > e->smem_optin) ring = e->smem_optin - fixed;
+        e->step_slots = std::max(2, std::min((int)(ring / ((size_t)kGemvConsumerWarps * kStageTarget)), kGemvMaxStages));
+        e->step_smem = fixed + (size_t)kGemvConsumerWarps * e->step_slots * kStageTarget;
+        if (e->step_smem > e->smem_optin) e->persistent = false;
+    }
+    if (e->persistent) {
+        e->h_phases.clear();
+        Recorder R{e, e->stream};
+        R.collect = true;
+        record_step(R, true);
+        if (e->d_phases) cudaFree(e->d_phases);
+        CU(cudaMalloc(&e->d_phases, e->h_phases.size() * sizeof(StepPhase)));
+        CU(cudaMemcpy(e->d_phases, e->h_phases.data(), e->h_phases.size() * sizeof(StepPhase), cudaMemcpyHostToDevice));
+        e->n_gbar = c.tp_size > 1 ? 2 * c.n_layers + 1 : 1;
+        if (e->gbar) cudaFree(e->gbar);
+        CU(cudaMalloc(&e->gbar, (size_t)e->n_gbar * sizeof(unsigned int)));
+        CU(cudaMemset(e->gbar, 0, (size_t)e->n_gbar * sizeof(unsigned int)));
+        if (getenv("LPP_STEP_TRACE") && !e->trace) {
+            CU(cudaMalloc(&e->trace, (size_t)e->num_sms * e->h_phases.size() * 4 * sizeof(unsigned long long)));
+            CU(cudaMemset(e->trace, 0, (size_t)e->num_sms * e->h_phases.size() * 4 * sizeof(unsigned long long)));
+        }
+        TRACE("finalize: persistent step kernel, %zu phases, %d slots/warp, %zu B smem", e->h_phases.size(), e->step_slots, e->step_smem);
+    }
     if (!(c.flags & LPP_FLAG_NO_GRAPH)) {
-        TRY(capture(e, true, &e->g_full, &e->kernels_full));
-        TRACE("finalize: full graph captured (%d kernels)", e->kernels_full);
-        TRY(capture(e, false, &e->g_logits, nullptr));
-        TRACE("finalize: logits graph captured");
+        for (int v = 0; v < 1; ++v) {
+            TRY(capture(e, true, v == 1, &e->g_full[v], v == 0 ? &e->kernels_full : nullptr));
+            TRY(capture(e, false, v == 1, &e->g_logits[v], nullptr));
+        }
+        TRACE("finalize: graphs captured (%d kernels per long-context step)", e->kernels_full);
     } else {
-        e->kernels_full = 5 * c.n_layers + 2;
+        e->kernels_full = e->persistent ? (c.tp_size > 1 ? 2 * c.n_layers + 2 : 2) : 5 * c.n_layers + 2;
     }
     e->finalized = true;
     return LPP_OK;
@@ -912,7 +1074,7 @@ extern "C" lpp_status lpp_step(lpp_engine* e, int token, int pos, const lpp_samp
     NEED_READY(e);
     if (!sp || !next_token) return fail(LPP_ERR_INVALID_ARG, "null argument");
     TRY(push_state(e, token, pos, sp, h_history, history_len, r, 0, 0));
-    TRY(run_step(e, true));
+    TRY(run_step(e, true, pos));
     return pull_result(e, next_token);
 }
 
@@ -920,7 +1082,7 @@ extern "C" lpp_status lpp_step_logits(lpp_engine* e, int token, int pos, float* 
     NEED_READY(e);
     if (!h_logits) return fail(LPP_ERR_INVALID_ARG, "null argument");
     TRY(push_state(e, token, pos, nullptr, nullptr, 0, 0.f, 0, 0));
-    TRY(run_step(e, false));
+    TRY(run_step(e, false, pos));
     CU(cudaMemcpyAsync(h_logits, e->logits, (size_t)e->c.vocab_size * 4, cudaMemcpyDeviceToHost, e->stream));
     return pull_result(e, nullptr);
 }
@@ -938,7 +1100,7 @@ extern "C" lpp_status lpp_decode(lpp_engine* e, int first_token, int start_pos, 
     TRY(push_state(e, first_token, start_pos, sp, h_history, history_len, 0.f, 1, history_window));
     if (h_r) CU(cudaMemcpyAsync(e->r_values, h_r, (size_t)n * 4, cudaMemcpyHostToDevice, e->stream));
     CU(cudaEventRecord(e->ev0, e->stream));
-    for (int i = 0; i < n; ++i) TRY(run_step(e, true));
+    for (int i = 0; i < n; ++i) TRY(run_step(e, true, start_pos + i));
     CU(cudaEventRecord(e->ev1, e->stream));
     CU(cudaMemcpyAsync(h_out_tokens, e->out_tokens, (size_t)n * 4, cudaMemcpyDeviceToHost, e->stream));
     TRY(pull_result(e, nullptr));
@@ -1023,6 +1185,19 @@ extern "C" lpp_status lpp_kv_read(lpp_engine* e, int layer, int kv_head, int pos
 
 // ------------------------------------------------------------------ introspection
 
+// Timing aid (not part of the public header): copies the time stamps the step kernel left when the
+// engine was finalized with LPP_STEP_TRACE set; n_out = ctas * phases * 4 values.
+extern "C" int lpp_debug_step_trace(lpp_engine* e, unsigned long long* out, int max_values, int* ctas, int* phases) {
+    if (!e || !e->trace || !out) return -1;
+    const size_t n = (size_t)e->num_sms * e->h_phases.size() * 4;
+    if ((size_t)max_values < n) return -2;
+    cudaStreamSynchronize(e->stream);
+    if (cudaMemcpy(out, e->trace, n * sizeof(unsigned long long), cudaMemcpyDeviceToHost) != cudaSuccess) return -3;
+    *ctas = e->num_sms;
+    *phases = (int)e->h_phases.size();
+    return (int)n;
+}
+
 extern "C" const char* lpp_strerror(int s) {
     switch (s) {
         case LPP_OK: return "ok";
@@ -1065,6 +1240,12 @@ extern "C" lpp_status lpp_profile_step(lpp_engine* e, int pos, int iters, float*
     if (pos < 0 || pos >= e->c.seq_len) return fail(LPP_ERR_INVALID_ARG, "pos out of range");
     for (int k = 0; k < kKinds; ++k) ms[k] = 0.f, launches[k] = 0;
     kind_bytes(e, pos, bytes);
+    if (e->persistent) {  // one launch covers the GEMV and attention phases
+        for (int k = kQkv; k <= kLmHead; ++k) {
+            bytes[kStepKernel] += bytes[k];
+            bytes[k] = 0;
+        }
+    }
     lpp_sample_params sp = {0.f, 1.f};
     // The step is captured once more with an event-record node before and after every kernel and
     // replayed as a graph, so the durations carry no host launch latency.  Event nodes sit between

@@ -66,6 +66,7 @@ struct GemvArgs {
     const void* pf;
     unsigned int pf_bytes;
     int debug;        // timing experiments only: 1 = consumers skip the arithmetic, 2 = producer skips the copies
+    int xs_bytes;     // shared-memory bytes reserved for the staged input (0 = K floats rounded up to 128)
 };
 
 // ------------------------------------------------------------------ x staging layouts
@@ -286,7 +287,7 @@ __device__ __forceinline__ void gemv_epilogue(const GemvArgs& a, int g, float v0
     } else if constexpr (EPI == kEpiResid) {
         // x += W.xb (src/model.cpp:232, 239); under tensor parallelism only rank 0 passes resid
         if (a.resid) {
-            const float2 r = *reinterpret_cast<const float2*>(a.resid + row);
+            const float2 r = __ldcg(reinterpret_cast<const float2*>(a.resid + row));  // written by an earlier phase
             v0 += r.x;
             v1 += r.y;
         }
@@ -330,14 +331,16 @@ __device__ __forceinline__ void gemv_epilogue(const GemvArgs& a, int g, float v0
 
 // ------------------------------------------------------------------ ring (bulk async copy) variant
 
+// Body of the ring kernel.  Returns true on the consumer threads once all of this CTA's rows are
+// done (so a caller can append a CTA-level tail), false on the producer warp and after a timeout.
 template <typename WT, int EPI>
-__global__ void __launch_bounds__(kGemvRingThreads) gemv_ring_kernel(const GemvArgs a) {
-    extern __shared__ __align__(128) unsigned char smem[];
+__device__ __forceinline__ bool gemv_ring_body(const GemvArgs& a, unsigned char* smem) {
     uint64_t* full = reinterpret_cast<uint64_t*>(smem);                // [consumer warp][kGemvMaxStages]
     uint64_t* empty = full + kGemvConsumerWarps * kGemvMaxStages;      // [consumer warp][kGemvMaxStages]
     float* red = reinterpret_cast<float*>(smem + kGemvBarrierBytes);   // 8 floats
     float* xs = reinterpret_cast<float*>(smem + kGemvBarrierBytes + 128);
-    unsigned char* ring = smem + kGemvBarrierBytes + 128 + (((size_t)a.K * 4 + 127) & ~(size_t)127);
+    const size_t xs_bytes = a.xs_bytes > 0 ? (size_t)a.xs_bytes : (((size_t)a.K * 4 + 127) & ~(size_t)127);
+    unsigned char* ring = smem + kGemvBarrierBytes + 128 + xs_bytes;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int NS = a.n_stages;  // slots per consumer warp
@@ -353,6 +356,7 @@ __global__ void __launch_bounds__(kGemvRingThreads) gemv_ring_kernel(const GemvA
     const int m = a.pairs_per_stage;
     const int nch = m > 0 ? 1 : (a.K + a.kc - 1) / a.kc;
 
+    if (tid == 0) reinterpret_cast<int*>(smem + kGemvBarrierBytes + 64)[2] = 0;
     if (tid < kGemvConsumerWarps * NS) {
         const int bw = tid / NS, sl = tid - bw * NS;
         mbar_init(&full[bw * kGemvMaxStages + sl], 1);
@@ -417,7 +421,7 @@ __global__ void __launch_bounds__(kGemvRingThreads) gemv_ring_kernel(const GemvA
         __syncwarp();
         // all of this CTA's copies are issued: the next kernel may start launching
         if (lane == 0) pdl_launch_dependents();
-        return;
+        return false;
     }
 
     // ---------------- consumers
@@ -438,10 +442,16 @@ __global__ void __launch_bounds__(kGemvRingThreads) gemv_ring_kernel(const GemvA
             par ^= 1u;
         }
     };
+    // A warp whose wait runs out stops consuming but still returns through the common exit, so a
+    // CTA-level tail (which uses CTA barriers) is never left waiting for it.
+    bool ok = true;
     if (m > 0) {
-        for (int p = p0; p < p1; p += m) {
+        for (int p = p0; p < p1 && ok; p += m) {
             const int cnt = min(m, p1 - p);
-            if (!acquire()) return;
+            if (!acquire()) {
+                ok = false;
+                break;
+            }
             const unsigned char* st = myring + (size_t)slot * a.stage_bytes;
             for (int i = 0; i < cnt; ++i) {
                 float acc0 = 0.f, acc1 = 0.f;
@@ -454,12 +464,15 @@ __global__ void __launch_bounds__(kGemvRingThreads) gemv_ring_kernel(const GemvA
             release();
         }
     } else {
-        for (int p = p0; p < p1; ++p) {
+        for (int p = p0; p < p1 && ok; ++p) {
             float acc[kRowsPerGroup] = {0.f, 0.f};
 #pragma unroll
             for (int r = 0; r < kRowsPerGroup; ++r)
-                for (int c = 0; c < nch; ++c) {
-                    if (!acquire()) return;
+                for (int c = 0; c < nch && ok; ++c) {
+                    if (!acquire()) {
+                        ok = false;
+                        break;
+                    }
                     const int k0 = c * a.kc;
                     const int klen = min(a.kc, a.K - k0);
                     const unsigned char* st = myring + (size_t)slot * a.stage_bytes;
@@ -467,10 +480,19 @@ __global__ void __launch_bounds__(kGemvRingThreads) gemv_ring_kernel(const GemvA
                     if (!(a.debug & 1)) dot_rows<WT, 1, false>(st, st, xs, a.K, k0, klen, lane, acc[r], dummy);
                     release();
                 }
+            if (!ok) break;
             const float v0 = warp_sum(acc[0]), v1 = warp_sum(acc[1]);
             if (lane == 0) gemv_epilogue<EPI>(a, p, v0, v1);
         }
     }
+    if (!ok) reinterpret_cast<int*>(smem + kGemvBarrierBytes + 64)[2] = 1;  // abort flag for a CTA-level tail
+    return true;
+}
+
+template <typename WT, int EPI>
+__global__ void __launch_bounds__(kGemvRingThreads) gemv_ring_kernel(const GemvArgs a) {
+    extern __shared__ __align__(128) unsigned char smem[];
+    gemv_ring_body<WT, EPI>(a, smem);
 }
 
 // ------------------------------------------------------------------ direct-load variant

@@ -36,6 +36,8 @@ struct SampleArgs {
     unsigned int* counter;  // zero between launches
     const float* r_values;  // free-running mode: one uniform draw per step
     int* out_tokens;        // free-running mode: sampled token per step
+    unsigned int* zero;     // counters to clear once the step is over (grid-barrier tickets), may be null
+    int zero_n;
 };
 
 struct MaxIdx {
@@ -81,6 +83,9 @@ static __global__ void __launch_bounds__(kSampleThreads) sample_kernel(const Sam
     __shared__ int s_flag;
     __shared__ int s_found;
 
+    // the next token's step kernel may become resident and start streaming weights meanwhile; it
+    // does not read anything this kernel writes before its own dependency wait
+    pdl_launch_dependents();
     pdl_wait();
     StepState* st = a.st;
     const int tid = threadIdx.x;
@@ -239,6 +244,8 @@ static __global__ void __launch_bounds__(kSampleThreads) sample_kernel(const Sam
         }
         *a.counter = 0u;
     }
+    // every kernel of this step has completed: reset the step kernels' grid-barrier counters
+    for (int i = tid; i < a.zero_n; i += kSampleThreads) a.zero[i] = 0u;
 }
 
 }  // namespace lpp

@@ -20,11 +20,12 @@ LIB_PATH = os.path.join(_HERE, "liblpp_b200.so")
 
 LPP_F32, LPP_F16 = 0, 1
 MEM_HOST, MEM_DEVICE = 0, 1
-FLAG_GEMV_LDG, FLAG_NO_PDL, FLAG_NO_GRAPH = 1, 2, 4
+FLAG_GEMV_LDG, FLAG_NO_PDL, FLAG_NO_GRAPH, FLAG_PERSISTENT = 1, 2, 4, 8
 TENSOR_IDS = {"tok_emb": 0, "rms_att": 1, "wq": 2, "wk": 3, "wv": 4, "wo": 5, "rms_ffn": 6, "w1": 7, "w2": 8,
               "w3": 9, "rms_final": 10, "w_cls": 11}
 _UNSTACKED = ("tok_emb", "rms_final", "w_cls")
-KINDS = ["qkv_gemv", "attention", "oproj_gemv", "gateup_gemv", "down_gemv", "lmhead_gemv", "sampler", "allreduce"]
+KINDS = ["qkv_gemv", "attention", "oproj_gemv", "gateup_gemv", "down_gemv", "lmhead_gemv", "sampler", "allreduce",
+         "step_kernel", "reserved"]
 
 # every symbol include/lpp_b200.h declares; tests check the built library exports all of them
 EXPORTS = [
@@ -254,11 +255,11 @@ class Engine:
         return int(self.lib.lpp_step_bytes(self.h, int(pos)))
 
     def profile_step(self, pos: int, iters: int = 5) -> Dict[str, Dict[str, float]]:
-        ms = (C.c_float * 8)()
-        n = (C.c_int * 8)()
-        b = (C.c_int64 * 8)()
+        ms = (C.c_float * 10)()
+        n = (C.c_int * 10)()
+        b = (C.c_int64 * 10)()
         _check(self.lib.lpp_profile_step(self.h, int(pos), int(iters), ms, n, b), "lpp_profile_step")
-        return {KINDS[i]: {"ms": float(ms[i]), "launches": int(n[i]), "bytes": int(b[i])} for i in range(8)}
+        return {KINDS[i]: {"ms": float(ms[i]), "launches": int(n[i]), "bytes": int(b[i])} for i in range(10)}
 
     def close(self) -> None:
         if getattr(self, "h", None):

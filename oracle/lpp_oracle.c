@@ -295,3 +295,83 @@ void oracle_srand(unsigned seed) { srand(seed); }
 void oracle_rand_floats(float* out, int n) {
     for (int i = 0; i < n; i++) out[i] = (float)rand() / (float)RAND_MAX;
 }
+
+/* ---- CPU twin of the CUDA sampler's arithmetic (lighterpp_b200/csrc/common.cuh: exp_repro).
+ * Same operations in the same order, IEEE double add/mul/fma only, so host and device agree bit for
+ * bit.  Used to tell apart the two reasons a sampled id can differ from sample(): the summation
+ * order of the kernel, and the last-bit difference between this exp and libm's expf. */
+float oracle_exp_repro(float x) {
+    if (!(x > -104.0f)) return (x != x) ? x : 0.0f;
+    if (x > 88.8f) return INFINITY;
+    const double kLog2e = 1.4426950408889634074;
+    const double kLn2Hi = 6.93147180369123816490e-01;
+    const double kLn2Lo = 1.90821492927058770002e-10;
+    double xd = (double)x;
+    double kd = rint(xd * kLog2e);
+    double r = fma(-kd, kLn2Hi, xd);
+    r = fma(-kd, kLn2Lo, r);
+    double p = 1.0 / 6227020800.0;
+    p = fma(p, r, 1.0 / 479001600.0);
+    p = fma(p, r, 1.0 / 39916800.0);
+    p = fma(p, r, 1.0 / 3628800.0);
+    p = fma(p, r, 1.0 / 362880.0);
+    p = fma(p, r, 1.0 / 40320.0);
+    p = fma(p, r, 1.0 / 5040.0);
+    p = fma(p, r, 1.0 / 720.0);
+    p = fma(p, r, 1.0 / 120.0);
+    p = fma(p, r, 1.0 / 24.0);
+    p = fma(p, r, 1.0 / 6.0);
+    p = fma(p, r, 0.5);
+    p = fma(p, r, 1.0);
+    p = fma(p, r, 1.0);
+    long long k = (long long)kd;
+    union {
+        long long i;
+        double d;
+    } s;
+    s.i = (k + 1023) << 52;
+    return (float)(p * s.d);
+}
+
+/* sample() (src/model.cpp:256-303) with exp_repro in place of libm's expf and nothing else changed:
+ * the sequential FP32 sums of softmax() and of the cumulative distribution are kept. */
+int oracle_sample_exp_repro(float* logits, int vocab_size, float temperature, float penalty, const int* history,
+                            int history_len, float r) {
+    if (penalty > 1.0f && history && history_len > 0) {
+        for (int i = 0; i < history_len; i++) {
+            int token = history[i];
+            if (token >= 0 && token < vocab_size) {
+                if (logits[token] > 0)
+                    logits[token] /= penalty;
+                else
+                    logits[token] *= penalty;
+            }
+        }
+    }
+    if (temperature == 0.0f) {
+        int max_idx = 0;
+        float max_val = logits[0];
+        for (int i = 1; i < vocab_size; i++)
+            if (logits[i] > max_val) {
+                max_val = logits[i];
+                max_idx = i;
+            }
+        return max_idx;
+    }
+    for (int i = 0; i < vocab_size; i++) logits[i] /= temperature;
+    float max_val = logits[0];
+    for (int i = 1; i < vocab_size; i++)
+        if (logits[i] > max_val) max_val = logits[i];
+    float sum = 0.0f;
+    for (int i = 0; i < vocab_size; i++) {
+        logits[i] = oracle_exp_repro(logits[i] - max_val);
+        sum += logits[i];
+    }
+    for (int i = 0; i < vocab_size; i++) logits[i] = logits[i] / sum;
+    float cumulative = 0.0f;
+    for (int i = 0; i < vocab_size; i++) {
+        cumulative += logits[i];
+        if (r < cumulative) return i;
+    }
+    return vocab_size - 1;
+}
