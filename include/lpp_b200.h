@@ -60,6 +60,8 @@ typedef enum {
 #define LPP_FLAG_GEMV_LDG 0x1u   /* stream weights with 128-bit global loads instead of the bulk-copy ring */
 #define LPP_FLAG_NO_PDL 0x2u     /* plain stream order between kernels (no programmatic dependent launch) */
 #define LPP_FLAG_NO_GRAPH 0x4u   /* launch the step kernel by kernel instead of replaying the CUDA graph */
+#define LPP_FLAG_FAST_SAMPLER 0x10u /* tree-sum sampler: ~20 us faster per token, categorical ids no longer follow the
+                                      reference's sequential FP32 sums bit for bit */
 #define LPP_FLAG_PERSISTENT 0x8u /* one persistent kernel with grid barriers per run of phases instead of one
                                     kernel per phase (measured slower on B200; kept for comparison) */
 

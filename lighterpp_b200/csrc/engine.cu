@@ -34,6 +34,7 @@
 #include "gemv.cuh"
 #include "ops.cuh"
 #include "sampler.cuh"
+#include "sampler_exact.cuh"
 #include "step.cuh"
 
 using namespace lpp;
@@ -135,6 +136,13 @@ struct lpp_engine {
     float *attn_part = nullptr, *samp_max = nullptr, *samp_sum = nullptr, *r_values = nullptr;
     int *samp_idx = nullptr, *out_tokens = nullptr;
     unsigned int *attn_counters = nullptr, *samp_counter = nullptr;
+    // exact-order sampler scratch
+    bool exact_sampler = false;
+    unsigned int* ex_sync = nullptr;
+    double* ex_block_sum = nullptr;
+    int* ex_entry_count = nullptr;
+    ExactEntry* ex_entries = nullptr;
+    float* ex_scalars = nullptr;
     float2* rope = nullptr;
     StepState* st = nullptr;
     int run_cap = 0;  // capacity of r_values / out_tokens
@@ -448,6 +456,34 @@ static void record_allreduce(Recorder& R, float* buf, int n) {
     R.prev_kernel = false;
 }
 
+// The fused sampler: exact-order kernel by default, tree kernel when asked for or when the vocabulary
+// needs more blocks than can be co-resident.
+static cudaError_t launch_sampler(lpp_engine* e, cudaStream_t s, bool pdl, bool zero_gbar) {
+    SampleArgs a = {};
+    a.logits = e->logits;
+    a.vocab = e->c.vocab_size;
+    a.st = e->st;
+    a.part_max = e->samp_max;
+    a.part_idx = e->samp_idx;
+    a.part_sum = e->samp_sum;
+    a.counter = e->samp_counter;
+    a.r_values = e->r_values;
+    a.out_tokens = e->out_tokens;
+    a.zero = zero_gbar ? e->gbar : nullptr;
+    a.zero_n = zero_gbar ? e->n_gbar : 0;
+    if (e->exact_sampler) {
+        SampleExactArgs ea = {};
+        ea.base = a;
+        ea.sync = e->ex_sync;
+        ea.block_sum = e->ex_block_sum;
+        ea.entry_count = e->ex_entry_count;
+        ea.entries = e->ex_entries;
+        ea.scalars = e->ex_scalars;
+        return launch_kernel(sample_exact_kernel, dim3(e->sample_blocks), dim3(kSampleThreads), 0, s, pdl, ea);
+    }
+    return launch_kernel(sample_kernel, dim3(e->sample_blocks), dim3(kSampleThreads), 0, s, pdl, a);
+}
+
 // Start and size of the weight matrix a GEMV kind streams in layer l (this rank's share).
 static void matrix_span(const lpp_engine* e, int kind, int l, const void** ptr, size_t* bytes) {
     const size_t D = e->c.dim, esz = e->esz;
@@ -608,21 +644,8 @@ static void record_step(Recorder& R, bool with_sampler) {
         R.prev_kernel = false;
     }
     if (with_sampler && !(skip_mask() & (1u << kSampler))) {
-        SampleArgs a = {};
-        a.zero = e->persistent ? e->gbar : nullptr;
-        a.zero_n = e->persistent ? e->n_gbar : 0;
-        a.logits = e->logits;
-        a.vocab = c.vocab_size;
-        a.st = e->st;
-        a.part_max = e->samp_max;
-        a.part_idx = e->samp_idx;
-        a.part_sum = e->samp_sum;
-        a.counter = e->samp_counter;
-        a.r_values = e->r_values;
-        a.out_tokens = e->out_tokens;
         R.mark(kSampler);
-        R.check(launch_kernel(sample_kernel, dim3(e->sample_blocks), dim3(kSampleThreads), 0, R.s, R.pdl(), a),
-                "sampler launch");
+        R.check(launch_sampler(e, R.s, R.pdl(), e->persistent), "sampler launch");
         R.mark(-1);
         R.prev_kernel = true;
         R.kernels++;
@@ -773,6 +796,15 @@ extern "C" lpp_status lpp_engine_create(const lpp_config* cfg, const void* nccl_
     CUB(cudaMalloc(&e->samp_idx, e->sample_blocks * 4));
     CUB(cudaMalloc(&e->samp_counter, 4));
     CUB(cudaMemsetAsync(e->samp_counter, 0, 4, e->stream));
+    e->exact_sampler = !(c.flags & LPP_FLAG_FAST_SAMPLER) && e->sample_blocks <= e->num_sms;
+    if (e->exact_sampler) {
+        CUB(cudaMalloc(&e->ex_sync, 2 * sizeof(unsigned int)));
+        CUB(cudaMemsetAsync(e->ex_sync, 0, 2 * sizeof(unsigned int), e->stream));
+        CUB(cudaMalloc(&e->ex_block_sum, e->sample_blocks * sizeof(double)));
+        CUB(cudaMalloc(&e->ex_entry_count, e->sample_blocks * sizeof(int)));
+        CUB(cudaMalloc(&e->ex_entries, (size_t)e->sample_blocks * kExactMaxEntries * sizeof(ExactEntry)));
+        CUB(cudaMalloc(&e->ex_scalars, 32 * sizeof(float)));
+    }
     e->run_cap = std::max<int>(4096, c.seq_len);
     CUB(cudaMalloc(&e->r_values, (size_t)e->run_cap * 4));
     CUB(cudaMalloc(&e->out_tokens, (size_t)e->run_cap * 4));
@@ -827,7 +859,7 @@ extern "C" lpp_status lpp_engine_destroy(lpp_engine* e) {
     void* bufs[] = {e->wqkv, e->wo, e->w13, e->w2, e->emb, e->wcls_owned ? e->wcls : nullptr, e->rms_att, e->rms_ffn,
                     e->rms_final, e->kcache, e->vcache, e->xa, e->xb, e->q, e->att_out, e->hb, e->logits,
                     e->attn_part, e->attn_counters, e->samp_max, e->samp_sum, e->samp_idx, e->samp_counter,
-                    e->r_values, e->out_tokens, e->st, e->rope, e->stage, e->d_phases, e->gbar, e->trace};
+                    e->r_values, e->out_tokens, e->st, e->rope, e->stage, e->d_phases, e->gbar, e->trace, e->ex_sync, e->ex_block_sum, e->ex_entry_count, e->ex_entries, e->ex_scalars};
     for (void* p : bufs)
         if (p) cudaFree(p);
     if (e->h_st) cudaFreeHost(e->h_st);
@@ -1114,17 +1146,7 @@ extern "C" lpp_status lpp_sample_logits(lpp_engine* e, const float* h_logits, co
     if (!h_logits || !sp || !token) return fail(LPP_ERR_INVALID_ARG, "null argument");
     TRY(push_state(e, 0, 0, sp, h_history, history_len, r, 0, 0));
     CU(cudaMemcpyAsync(e->logits, h_logits, (size_t)e->c.vocab_size * 4, cudaMemcpyHostToDevice, e->stream));
-    SampleArgs a = {};
-    a.logits = e->logits;
-    a.vocab = e->c.vocab_size;
-    a.st = e->st;
-    a.part_max = e->samp_max;
-    a.part_idx = e->samp_idx;
-    a.part_sum = e->samp_sum;
-    a.counter = e->samp_counter;
-    a.r_values = e->r_values;
-    a.out_tokens = e->out_tokens;
-    CU(launch_kernel(sample_kernel, dim3(e->sample_blocks), dim3(kSampleThreads), 0, e->stream, false, a));
+    CU(launch_sampler(e, e->stream, false, false));
     return pull_result(e, token);
 }
 
@@ -1196,6 +1218,16 @@ extern "C" int lpp_debug_step_trace(lpp_engine* e, unsigned long long* out, int 
     *ctas = e->num_sms;
     *phases = (int)e->h_phases.size();
     return (int)n;
+}
+
+// Debugging aid (not part of the public header): the exact sampler's entry lists of its last stage.
+extern "C" int lpp_debug_sampler_entries(lpp_engine* e, int* counts, void* entries, float* scalars) {
+    if (!e || !e->exact_sampler) return -1;
+    cudaStreamSynchronize(e->stream);
+    cudaMemcpy(counts, e->ex_entry_count, e->sample_blocks * sizeof(int), cudaMemcpyDeviceToHost);
+    cudaMemcpy(entries, e->ex_entries, (size_t)e->sample_blocks * kExactMaxEntries * sizeof(ExactEntry), cudaMemcpyDeviceToHost);
+    cudaMemcpy(scalars, e->ex_scalars, 32 * sizeof(float), cudaMemcpyDeviceToHost);
+    return e->sample_blocks;
 }
 
 extern "C" const char* lpp_strerror(int s) {

@@ -1,0 +1,179 @@
+// The reference's model-step entry points (src/model.h:117-164) re-created on top of the C ABI, with the reference's exact signatures and
+// structures, so that its main.cpp / loader.cpp / runtests.cpp compiled with -DUSE_CUDA link against
+// liblpp_b200.so unchanged (free_weights_cuda stays the one in the reference's loader.cpp).  Compile this file with -DUSE_CUDA and the reference's src/ on the
+// include path (model.h and loader.h are used as they are).
+//
+// forward() drives the engine: the first call adopts the device weights the reference loaders
+// produced (w->d_*, reference layout) by handing them to lpp_upload_tensor as device pointers, then
+// every call is one lpp_step.  attention() / transformer_block() keep the reference's operator-by-
+// operator structure on the cuda_* wrappers for host code that calls them directly.
+#include <cmath>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+
+#include "loader.h"
+#include "model.h"
+#include "lpp_b200.h"
+
+static void must(lpp_status s, const char* what) {
+    if (s != LPP_OK) {
+        printf("Error: %s: %s (%s)\n", what, lpp_strerror(s), lpp_last_error());
+        exit(1);
+    }
+}
+
+// One engine per RunState (the reference has exactly one of each per process).
+struct ShimEngine {
+    RunState* state;
+    transformerWeights* weights;
+    lpp_engine* engine;
+};
+static ShimEngine g_shim = {nullptr, nullptr, nullptr};
+
+static size_t esz(const Config* p) { return p->weight_precision == WEIGHT_FP16 ? 2 : 4; }
+
+template <typename T>
+static void dev_alloc(T** p, size_t count, bool zero = false) {
+    if (cudaMalloc((void**)p, count * sizeof(T)) != cudaSuccess) {
+        printf("Malloc failed! Device out of memory?\n");
+        exit(1);
+    }
+    if (zero) cudaMemset(*p, 0, count * sizeof(T));
+}
+
+// Buffers of src/model.cpp:18-81: the host side as the CPU path uses it, the device side for callers of
+// the per-operator wrappers.  The engine behind forward() owns its own activations and KV cache.
+void malloc_run_state(RunState* s, Config* p) {
+    const size_t dim = p->dim, hidden = p->hidden_dim, kv_dim = (size_t)p->dim * p->n_kv_heads / p->n_heads;
+    const size_t kv_cache = (size_t)p->n_layers * p->seq_len * kv_dim;
+    memset(s, 0, sizeof(*s));
+    float** host_dim[] = {&s->x, &s->xb, &s->xb2, &s->q};
+    for (float** h : host_dim) *h = (float*)calloc(dim, sizeof(float));
+    s->k = (float*)calloc(kv_dim, sizeof(float));
+    s->v = (float*)calloc(kv_dim, sizeof(float));
+    s->hb = (float*)calloc(hidden, sizeof(float));
+    s->he = (float*)calloc(hidden, sizeof(float));
+    s->att = (float*)calloc((size_t)p->n_heads * p->seq_len, sizeof(float));
+    cudaHostAlloc((void**)&s->logits, (size_t)p->vocab_size * sizeof(float), cudaHostAllocDefault);
+    s->key_cache = (float*)calloc(kv_cache, sizeof(float));
+    s->value_cache = (float*)calloc(kv_cache, sizeof(float));
+    if (!s->x || !s->key_cache || !s->value_cache || !s->logits) {
+        printf("Malloc failed! System out of memory?\n");
+        exit(1);
+    }
+    dev_alloc(&s->d_x, dim);
+    dev_alloc(&s->d_xb, dim);
+    dev_alloc(&s->d_xb2, dim);
+    dev_alloc(&s->d_q, dim);
+    dev_alloc(&s->d_k, kv_dim);
+    dev_alloc(&s->d_v, kv_dim);
+    dev_alloc(&s->d_hb, hidden);
+    dev_alloc(&s->d_he, hidden);
+    dev_alloc(&s->d_att, (size_t)p->n_heads * p->seq_len);
+    dev_alloc(&s->d_logits, (size_t)p->vocab_size);
+    dev_alloc(&s->d_key_cache, kv_cache, true);
+    dev_alloc(&s->d_value_cache, kv_cache, true);
+    dev_alloc((unsigned short**)&s->d_workspace_f16, hidden);
+    dev_alloc(&s->d_sampled_token, 1);
+    dev_alloc(&s->d_history, (size_t)p->seq_len);
+}
+
+void free_run_state(RunState* s) {
+    if (g_shim.state == s && g_shim.engine) {
+        lpp_engine_destroy(g_shim.engine);
+        g_shim = {nullptr, nullptr, nullptr};
+    }
+    float* host[] = {s->x, s->xb, s->xb2, s->hb, s->he, s->q, s->k, s->v, s->att, s->key_cache, s->value_cache};
+    for (float* h : host) free(h);
+    cudaFreeHost(s->logits);
+    void* dev[] = {s->d_x, s->d_xb, s->d_xb2, s->d_hb, s->d_he, s->d_q, s->d_k, s->d_v, s->d_att, s->d_logits,
+                   s->d_key_cache, s->d_value_cache, s->d_workspace_f16, s->d_sampled_token, s->d_history};
+    for (void* d : dev) cudaFree(d);
+}
+
+// src/model.cpp:121-160 (USE_CUDA branch), operator by operator on the wrappers.
+void attention(RunState* s, transformerWeights* w, Config* p, int layer, int pos) {
+    const int dim = p->dim, kv_dim = (p->dim * p->n_kv_heads) / p->n_heads, head_size = dim / p->n_heads;
+    const size_t off_q = (size_t)layer * dim * dim * esz(p), off_kv = (size_t)layer * kv_dim * dim * esz(p);
+    cuda_gemv(s->d_q, s->d_xb, (char*)w->d_wq + off_q, s->d_workspace_f16, dim, dim, p->weight_precision);
+    cuda_gemv(s->d_k, s->d_xb, (char*)w->d_wk + off_kv, s->d_workspace_f16, kv_dim, dim, p->weight_precision);
+    cuda_gemv(s->d_v, s->d_xb, (char*)w->d_wv + off_kv, s->d_workspace_f16, kv_dim, dim, p->weight_precision);
+    cuda_rope(s->d_q, s->d_k, pos, dim, kv_dim, head_size, p->rope_base);
+    cuda_scatter_kv(s->d_key_cache, s->d_value_cache, s->d_k, s->d_v, layer, pos, p->n_kv_heads, head_size, p->seq_len);
+    cuda_multihead_gemv(s->d_att, s->d_q, s->d_key_cache, layer, pos, p->n_heads, p->n_kv_heads, head_size, p->seq_len);
+    cuda_scale_multihead(s->d_att, 1.0f / sqrtf((float)head_size), p->n_heads, pos + 1, p->seq_len);
+    cuda_softmax_multihead(s->d_att, s->d_att, p->n_heads, pos + 1, p->seq_len);
+    cuda_aggregation_multihead(s->d_xb, s->d_value_cache + (size_t)layer * kv_dim * p->seq_len, s->d_att, p->n_heads,
+                               pos + 1, head_size, p->n_heads / p->n_kv_heads, p->seq_len);
+    cuda_gemv(s->d_xb2, s->d_xb, (char*)w->d_wo + off_q, s->d_workspace_f16, dim, dim, p->weight_precision);
+}
+
+// src/model.cpp:205-226 (USE_CUDA branch)
+void transformer_block(RunState* s, transformerWeights* w, Config* p, int layer, int pos) {
+    const int dim = p->dim, hidden = p->hidden_dim;
+    const size_t off_ffn = (size_t)layer * hidden * dim * esz(p), off_norm = (size_t)layer * dim;
+    cuda_rmsnorm(s->d_xb, s->d_x, w->d_rms_att_weight + off_norm, dim);
+    attention(s, w, p, layer, pos);
+    cuda_residual_add(s->d_x, s->d_x, s->d_xb2, dim);
+    cuda_rmsnorm(s->d_xb, s->d_x, w->d_rms_ffn_weight + off_norm, dim);
+    cuda_gemv(s->d_hb, s->d_xb, (char*)w->d_w1 + off_ffn, s->d_workspace_f16, hidden, dim, p->weight_precision);
+    cuda_gemv(s->d_he, s->d_xb, (char*)w->d_w3 + off_ffn, s->d_workspace_f16, hidden, dim, p->weight_precision);
+    cuda_swiglu(s->d_hb, s->d_hb, s->d_he, hidden);
+    cuda_gemv(s->d_xb2, s->d_hb, (char*)w->d_w2 + off_ffn, s->d_workspace_f16, dim, hidden, p->weight_precision);
+    cuda_residual_add(s->d_x, s->d_x, s->d_xb2, dim);
+}
+
+// Creates the engine and adopts the loaders' device tensors (reference layout, src/loader.cpp:73-131, 543-632).
+static void adopt_weights(RunState* s, transformerWeights* w, Config* p) {
+    lpp_config c;
+    memset(&c, 0, sizeof c);
+    c.dim = p->dim;
+    c.hidden_dim = p->hidden_dim;
+    c.n_layers = p->n_layers;
+    c.n_heads = p->n_heads;
+    c.n_kv_heads = p->n_kv_heads;
+    c.vocab_size = p->vocab_size;
+    c.seq_len = p->seq_len;
+    c.rope_base = p->rope_base;
+    c.weight_dtype = p->weight_precision == WEIGHT_FP16 ? LPP_F16 : LPP_F32;
+    c.kv_dtype = LPP_F16;  // the reference GPU path keeps an FP16 cache (src/model.h:108-109)
+    c.tp_size = 1;
+    lpp_engine* e = nullptr;
+    must(lpp_engine_create(&c, nullptr, &e), "lpp_engine_create");
+    const int wd = c.weight_dtype, D = p->dim, F = p->hidden_dim, KV = (p->dim * p->n_kv_heads) / p->n_heads;
+    const size_t ez = esz(p);
+    must(lpp_upload_tensor(e, LPP_T_TOK_EMB, 0, w->d_token_embedding_table, LPP_F32, LPP_MEM_DEVICE), "upload tok_emb");
+    must(lpp_upload_tensor(e, LPP_T_RMS_FINAL, 0, w->d_rms_final_weight, LPP_F32, LPP_MEM_DEVICE), "upload rms_final");
+    if ((void*)w->d_w_cls != (void*)w->d_token_embedding_table)
+        must(lpp_upload_tensor(e, LPP_T_W_CLS, 0, w->d_w_cls, wd, LPP_MEM_DEVICE), "upload w_cls");
+    for (int l = 0; l < p->n_layers; ++l) {
+        const size_t L = l;
+        must(lpp_upload_tensor(e, LPP_T_RMS_ATT, l, w->d_rms_att_weight + L * D, LPP_F32, LPP_MEM_DEVICE), "upload rms_att");
+        must(lpp_upload_tensor(e, LPP_T_RMS_FFN, l, w->d_rms_ffn_weight + L * D, LPP_F32, LPP_MEM_DEVICE), "upload rms_ffn");
+        must(lpp_upload_tensor(e, LPP_T_WQ, l, (char*)w->d_wq + L * D * D * ez, wd, LPP_MEM_DEVICE), "upload wq");
+        must(lpp_upload_tensor(e, LPP_T_WK, l, (char*)w->d_wk + L * KV * D * ez, wd, LPP_MEM_DEVICE), "upload wk");
+        must(lpp_upload_tensor(e, LPP_T_WV, l, (char*)w->d_wv + L * KV * D * ez, wd, LPP_MEM_DEVICE), "upload wv");
+        must(lpp_upload_tensor(e, LPP_T_WO, l, (char*)w->d_wo + L * D * D * ez, wd, LPP_MEM_DEVICE), "upload wo");
+        must(lpp_upload_tensor(e, LPP_T_W1, l, (char*)w->d_w1 + L * F * D * ez, wd, LPP_MEM_DEVICE), "upload w1");
+        must(lpp_upload_tensor(e, LPP_T_W2, l, (char*)w->d_w2 + L * D * F * ez, wd, LPP_MEM_DEVICE), "upload w2");
+        must(lpp_upload_tensor(e, LPP_T_W3, l, (char*)w->d_w3 + L * F * D * ez, wd, LPP_MEM_DEVICE), "upload w3");
+    }
+    must(lpp_finalize(e), "lpp_finalize");
+    g_shim = {s, w, e};
+}
+
+// src/model.cpp:342-371: one decode step and the fused sampler; one uniform draw per call like cuda_sample.
+int forward(int token, int pos, RunState* s, transformerWeights* w, Config* p, float temperature, float topp,
+            float penalty, int* history, int history_len) {
+    (void)topp;
+    if (g_shim.state != s || g_shim.weights != w) {
+        if (g_shim.engine) lpp_engine_destroy(g_shim.engine);
+        adopt_weights(s, w, p);
+    }
+    lpp_sample_params sp = {temperature, penalty};
+    const float r = (float)rand() / (float)RAND_MAX;
+    int next = 0;
+    must(lpp_step(g_shim.engine, token, pos, &sp, history, history_len, r, &next), "lpp_step");
+    return next;
+}

@@ -20,7 +20,7 @@ LIB_PATH = os.path.join(_HERE, "liblpp_b200.so")
 
 LPP_F32, LPP_F16 = 0, 1
 MEM_HOST, MEM_DEVICE = 0, 1
-FLAG_GEMV_LDG, FLAG_NO_PDL, FLAG_NO_GRAPH, FLAG_PERSISTENT = 1, 2, 4, 8
+FLAG_GEMV_LDG, FLAG_NO_PDL, FLAG_NO_GRAPH, FLAG_PERSISTENT, FLAG_FAST_SAMPLER = 1, 2, 4, 8, 16
 TENSOR_IDS = {"tok_emb": 0, "rms_att": 1, "wq": 2, "wk": 3, "wv": 4, "wo": 5, "rms_ffn": 6, "w1": 7, "w2": 8,
               "w3": 9, "rms_final": 10, "w_cls": 11}
 _UNSTACKED = ("tok_emb", "rms_final", "w_cls")

@@ -29,6 +29,9 @@ SHAPES: Dict[str, Tuple[ModelConfig, str, bool, int]] = {
     # the 8B shape's attention geometry (head size 128, 4 query heads per KV head) at toy width
     "mini-8b-f16": (ModelConfig(1024, 3584, 2, 8, 2, 4096, 128, 500000.0), "f16", False, 14),
     # long-context attention: seq_len large enough to exercise every KV split
+    # full-size vocabularies on a toy body: sampler tests
+    "vocab32k-f16": (ModelConfig(64, 128, 1, 2, 2, 32000, 16, 10000.0), "f16", True, 16),
+    "vocab128k-f16": (ModelConfig(64, 128, 1, 2, 2, 128256, 16, 500000.0), "f16", True, 17),
     "mini-long-f16": (ModelConfig(512, 1024, 2, 8, 2, 512, 4608, 500000.0), "f16", True, 15),
 }
 

@@ -30,6 +30,9 @@ def build(ref: bool = True) -> None:
     subprocess.run(["make", "-s", "-C", HERE, "oracle"], check=True)
     if ref and os.path.isdir(os.path.join(REFERENCE_CHECKOUT, "src")):
         subprocess.run(["make", "-s", "-C", HERE, "ref", f"REF={REFERENCE_CHECKOUT}"], check=True)
+        # the reference's own main.cpp / runtests.cpp linked against the CUDA library through the C++ shim
+        if os.path.exists(os.path.join(HERE, "..", "lighterpp_b200", "liblpp_b200.so")):
+            subprocess.run(["make", "-s", "-C", HERE, "dropin", f"REF={REFERENCE_CHECKOUT}"], check=True)
 
 
 def have_reference() -> bool:
@@ -112,6 +115,8 @@ class Oracle:
         lib.oracle_kv_index.argtypes = [C.c_int] * 7
         lib.oracle_sample.restype = C.c_int
         lib.oracle_sample.argtypes = [_fp, C.c_int, C.c_float, C.c_float, _ip, C.c_int, C.c_float]
+        lib.oracle_sample_exp_repro.restype = C.c_int
+        lib.oracle_sample_exp_repro.argtypes = [_fp, C.c_int, C.c_float, C.c_float, _ip, C.c_int, C.c_float]
         lib.oracle_srand.argtypes = [C.c_uint]
         lib.oracle_rand_floats.argtypes = [_fp, C.c_int]
 
@@ -161,6 +166,15 @@ class Oracle:
         hp = hist.ctypes.data_as(_ip) if hist.size else None
         return int(self.lib.oracle_sample(_ptr(buf), buf.size, float(temperature), float(penalty), hp, hist.size,
                                           float(r)))
+
+    def sample_twin(self, logits, temperature, penalty, history: Sequence[int], r: float) -> int:
+        """sample() with the CUDA sampler's exp (exp_repro) in place of libm's expf, nothing else changed: what the
+        exact-order GPU sampler must reproduce bit for bit."""
+        buf = _f32(logits).copy()
+        hist = np.ascontiguousarray(history, dtype=np.int32)
+        hp = hist.ctypes.data_as(_ip) if hist.size else None
+        return int(self.lib.oracle_sample_exp_repro(_ptr(buf), buf.size, float(temperature), float(penalty), hp,
+                                                    hist.size, float(r)))
 
     def rand_floats(self, seed: int, n: int) -> np.ndarray:
         """n values of (float)rand()/(float)RAND_MAX after srand(seed): the reference's r stream."""

@@ -120,7 +120,7 @@ def test_stories15m_shape_full_run(E, oracle):
         tok = int(prompt[pos + 1]) if pos + 1 < len(prompt) else (greedy_ref if pos % 2 else hot_ref)
         hist = (hist + [tok])[-64:]
     print(f"stories15m: worst logit diff {worst:.2e}; T=1.0 ids equal to sample() in {agree}/{total} draws")
-    assert agree >= 0.9 * total
+    assert agree >= 0.995 * total
     eng.close()
 
 
@@ -204,10 +204,37 @@ def test_llama32_1b_shape_first_steps(E, oracle):
     eng.close()
 
 
+@pytest.mark.parametrize("name", ["vocab32k-f16", "vocab128k-f16"])
+def test_exact_sampler_draws_large_vocab(E, oracle, name):
+    """The engine's sampler on identical logits, history and r, >= 10k draws over both vocabularies: ids must equal,
+    draw for draw, those of sample() evaluated with the kernel's exp (the CPU twin keeps the reference's sequential FP32
+    sums); against sample() itself (libm expf) the only admissible differences are last-bit exp effects."""
+    c, dt, T, eng = make(E, name)
+    V = c.vocab_size
+    rng = np.random.default_rng(V + 7)
+    same_twin = same_ref = total = 0
+    for s in range(10):
+        std = (0.3, 0.9, 3.0, 8.0)[s % 4]  # flat to peaked
+        lg = (rng.standard_normal(V) * std).astype(np.float32)
+        hist = rng.integers(0, V, size=64).astype(np.int32)
+        hist[:8] = hist[8:16]  # duplicates: the penalty applies once per occurrence
+        assert eng.sample(lg, 0.0, 1.1, hist, 0.0) == oracle.sample(lg, 0.0, 1.1, hist, 0.0)
+        rs = rng.random(500).astype(np.float32)
+        rs[:3] = (0.0, 1.0, np.float32(1.0) - np.float32(2 ** -24))
+        for r in rs:
+            got = eng.sample(lg, 0.8, 1.1, hist, float(r))
+            assert got == oracle.sample_twin(lg, 0.8, 1.1, hist, float(r)), (s, float(r))
+            same_ref += got == oracle.sample(lg, 0.8, 1.1, hist, float(r))
+            total += 1
+    print(f"{name}: categorical ids equal to the twin in {total}/{total} draws, to sample() in {same_ref}/{total}")
+    assert same_ref >= 0.995 * total
+    eng.close()
+
+
 @pytest.mark.parametrize("V", [32000, 128256])
-def test_sampler_draws_large_vocab(E, oracle, V):
-    """>= 10k draws in total over both vocabularies on identical logits and r: argmax ids are bit-exact;
-    categorical ids are compared with sample() and every difference must sit on a CDF boundary."""
+def test_tree_sampler_wrapper_large_vocab(E, oracle, V):
+    """The stand-alone cuda_sample wrapper (tree-sum sampler): argmax ids are bit-exact; categorical ids are compared
+    with sample() and every difference must sit on a CDF boundary."""
     import torch
     from lighterpp_b200 import ops
     rng = np.random.default_rng(V)
