@@ -803,7 +803,7 @@ extern "C" lpp_status lpp_engine_create(const lpp_config* cfg, const void* nccl_
         CUB(cudaMalloc(&e->ex_block_sum, e->sample_blocks * sizeof(double)));
         CUB(cudaMalloc(&e->ex_entry_count, e->sample_blocks * sizeof(int)));
         CUB(cudaMalloc(&e->ex_entries, (size_t)e->sample_blocks * kExactMaxEntries * sizeof(ExactEntry)));
-        CUB(cudaMalloc(&e->ex_scalars, 32 * sizeof(float)));
+        CUB(cudaMalloc(&e->ex_scalars, 64 * sizeof(float)));
     }
     e->run_cap = std::max<int>(4096, c.seq_len);
     CUB(cudaMalloc(&e->r_values, (size_t)e->run_cap * 4));
@@ -1226,7 +1226,7 @@ extern "C" int lpp_debug_sampler_entries(lpp_engine* e, int* counts, void* entri
     cudaStreamSynchronize(e->stream);
     cudaMemcpy(counts, e->ex_entry_count, e->sample_blocks * sizeof(int), cudaMemcpyDeviceToHost);
     cudaMemcpy(entries, e->ex_entries, (size_t)e->sample_blocks * kExactMaxEntries * sizeof(ExactEntry), cudaMemcpyDeviceToHost);
-    cudaMemcpy(scalars, e->ex_scalars, 32 * sizeof(float), cudaMemcpyDeviceToHost);
+    cudaMemcpy(scalars, e->ex_scalars, 64 * sizeof(float), cudaMemcpyDeviceToHost);
     return e->sample_blocks;
 }
 

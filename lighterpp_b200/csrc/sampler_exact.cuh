@@ -195,10 +195,23 @@ __device__ __forceinline__ double block_scan_double(double v, double* s_warp, in
     return v + off;
 }
 
+// Sum of one double per thread over the block, returned to every thread.
+__device__ __forceinline__ double block_sum_double(double v, double* s_warp, int tid) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    if ((tid & 31) == 0) s_warp[tid >> 5] = v;
+    __syncthreads();
+    double t = 0.0;
+#pragma unroll
+    for (int w = 0; w < kSampleThreads / 32; ++w) t += s_warp[w];
+    __syncthreads();
+    return t;
+}
+
 // Stage helper: every thread owns four consecutive values x[0..3] (element indices base+4*tid+k,
 // zero past the end).  Given the approximate prefix `pre` (double, exclusive) before the quad, the
 // block writes its entry list for the sequential sum of these values.
-__device__ __forceinline__ void emit_entries(const float (&x)[4], double pre, int first_elem, int n_valid_quads,
+__device__ __noinline__ void emit_entries(const float (&x)[4], double pre, int first_elem, int n_valid_quads,
                                              ExactEntry* out, int* out_count, Map2* s_wm, int* s_wf, int* s_i,
                                              int tid) {
     const int lane = tid & 31;
@@ -210,7 +223,7 @@ __device__ __forceinline__ void emit_entries(const float (&x)[4], double pre, in
     if (valid && pre > 0.0) {
         const int e0 = binade_of(pre * (1.0 - kExactEps)), e1 = binade_of(post * (1.0 + kExactEps));
         E = e0;
-        const float lim = scalbnf(1.0f, e0 > -120 && e0 < 120 ? e0 : 0);
+        const float lim = __uint_as_float((unsigned int)((e0 > -120 && e0 < 120 ? e0 : 0) + 127) << 23);  // 2^e0
         plain = (e0 == e1) && e0 > -120 && e0 < 120 && x[0] < lim && x[1] < lim && x[2] < lim && x[3] < lim;
     }
     // runs: maximal sequences of threads of one class (plain runs also share E)
@@ -220,7 +233,8 @@ __device__ __forceinline__ void emit_entries(const float (&x)[4], double pre, in
     if (lane == 31) s_cls_last[tid >> 5] = cls;
     __syncthreads();
     const int before = (tid == 0) ? 3000 : (lane == 0 ? s_cls_last[(tid >> 5) - 1] : prev);
-    const bool start = valid && cls != before;
+    // a quad outside the plain class is an entry of its own: it travels with its four values
+    const bool start = valid && (cls != before || !plain);
     Map2 mp = map_identity();
     if (plain) {
 #pragma unroll
@@ -248,7 +262,7 @@ __device__ __forceinline__ void emit_entries(const float (&x)[4], double pre, in
     if (lane == 0) s_cls_last[tid >> 5] = cls;  // reuse as "first class of warp"
     __syncthreads();
     const int after = (tid == kSampleThreads - 1) ? 3000 : (lane == 31 ? s_cls_last[(tid >> 5) + 1] : nxt_cls);
-    const bool last = valid && cls != after;
+    const bool last = valid && (cls != after || !plain);
     if (!overflow) {
         if (start) {
             out[idx].kind = plain ? kEntryMap : kEntrySeq;
@@ -288,113 +302,210 @@ struct WalkState {
 };
 
 // Applies `count` entries (in shared memory) in order.  Returns true when the walk is over (stop
-// requested and the crossing was located).
-__device__ __forceinline__ bool walk_list(const ExactEntry* list, int count, const float* x, int n_total, bool stop,
-                                          float r, int lane, WalkState& w) {
-    float s = w.s;
+// requested and the crossing was located).  A map moves the sum by an integer number of ulps inside
+// one binade (or exactly onto the next power of two), which on the bit pattern of a positive float
+// is a plain integer addition.
+__device__ __noinline__ bool walk_list(const ExactEntry* list, int count, const float* x, int n_total,
+                                          const bool kStop, float r, int lane, WalkState& w) {
+    unsigned int bits = __float_as_uint(w.s);
+    int4 nh = *reinterpret_cast<const int4*>(&list[0]);
+    ulonglong2 nd = *reinterpret_cast<const ulonglong2*>(&list[0].d0);
     for (int i = 0; i < count; ++i) {
-        const ExactEntry e = list[i];
-        if (e.kind == kEntryMap) {
-            float s_new = s;
-            if (apply_map(s_new, e.e, e.d0, e.d1)) {
-                if (stop && r < s_new) {  // the first crossing lies inside this run
-                    w.run_lo = e.lo;
-                    w.run_hi = min(e.hi, n_total);
-                    w.run_e = e.e;
-                    w.run_s0 = s;
-                    w.s = s;
+        const int4 h = nh;  // kind, lo, hi, e
+        const ulonglong2 d = nd;
+        const int nx = min(i + 1, count - 1);  // fetched while this entry is applied
+        nh = *reinterpret_cast<const int4*>(&list[nx]);
+        nd = *reinterpret_cast<const ulonglong2*>(&list[nx].d0);
+        if (h.x == kEntryMap) {
+            const unsigned int ebase = (unsigned int)(h.w + 127) << 23;
+            const unsigned long long dd = (bits & 1u) ? d.y : d.x;
+            const unsigned int nb = bits + (unsigned int)dd;
+            // sum inside binade e before, and inside it or exactly on its upper end after
+            if (bits - ebase < 0x800000u && dd <= 0x800000ull && nb - ebase <= 0x800000u) {
+                if (kStop && r < __uint_as_float(nb)) {  // the first crossing lies inside this run
+                    w.run_lo = h.y;
+                    w.run_hi = min(h.z, n_total);
+                    w.run_e = h.w;
+                    w.run_s0 = __uint_as_float(bits);
+                    w.s = __uint_as_float(bits);
                     return true;
                 }
-                s = s_new;
+                bits = nb;
                 continue;
             }
-        } else if (e.kind == kEntryQuad) {
-            const float v[4] = {__uint_as_float((unsigned int)e.d0), __uint_as_float((unsigned int)(e.d0 >> 32)),
-                                __uint_as_float((unsigned int)e.d1), __uint_as_float((unsigned int)(e.d1 >> 32))};
+        } else if (h.x == kEntryQuad) {
+            const float v[4] = {__uint_as_float((unsigned int)d.x), __uint_as_float((unsigned int)(d.x >> 32)),
+                                __uint_as_float((unsigned int)d.y), __uint_as_float((unsigned int)(d.y >> 32))};
+            float s = __uint_as_float(bits);
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
                 s = __fadd_rn(s, v[j]);
-                if (stop && r < s && w.found < 0) {
-                    w.found = e.lo + j;
+                if (kStop && r < s) {
+                    w.found = h.y + j;
                     w.s = s;
                     return true;
                 }
             }
+            bits = __float_as_uint(s);
             continue;
         }
-        // one-by-one FP32 additions from global memory, 32 loads at a time (long windows, failed predictions)
-        const int hi = min(e.hi, n_total);
-        for (int b = e.lo; b < hi; b += 32) {
+        // one-by-one FP32 additions from global memory, 32 loads at a time (oversized blocks, failed predictions)
+        float s = __uint_as_float(bits);
+        const int hi = min(h.z, n_total);
+        for (int b = h.y; b < hi; b += 32) {
             const float v = (b + lane < hi) ? __ldcg(x + b + lane) : 0.f;
             const int m = min(32, hi - b);
             for (int j = 0; j < m; ++j) {
                 s = __fadd_rn(s, __shfl_sync(0xffffffffu, v, j));
-                if (stop && r < s) {
+                if (kStop && r < s) {
                     w.found = b + j;
                     w.s = s;
                     return true;
                 }
             }
         }
+        bits = __float_as_uint(s);
     }
-    w.s = s;
+    w.s = __uint_as_float(bits);
     return false;
 }
 
-// Whole-block walk: rounds of (stage as many blocks' entries as fit into shared memory, in order;
-// warp 0 applies them).  Returns the final state in *out (shared memory).
-__device__ __forceinline__ void walk_all(const ExactEntry* entries, const int* counts, int n_blocks, const float* x,
-                                         int n_total, bool stop, float r, ExactEntry* s_list, int* s_off, WalkState* out,
-                                         int tid) {
+#define LPP_WALK_STAMP(k) do { } while (0)
+// Whole-block walk.  The blocks' entry lists are concatenated in block order (a prefix sum of the
+// counts gives every entry its place), staged into shared memory kExactListCap at a time, and
+// applied by warp 0.  Returns the final state in *out (shared memory).
+__device__ __noinline__ void walk_all(const ExactEntry* entries, const int* counts, int n_blocks, const float* x,
+                                         int n_total, bool stop, float r, ExactEntry* s_list, int* s_pref, int* s_i,
+                                         WalkState* out, int tid, float* dbg = nullptr) {
+    static_assert(kSampleMaxBlocks <= kSampleThreads, "one thread per block's count");
     const int lane = tid & 31;
+    __shared__ int s_done;
+    __shared__ int s_ctl[2];                          // first failed entry, first crossing entry
+    __shared__ unsigned int s_before[kExactListCap + 1];  // bit pattern of the sum before every staged entry
+    // inclusive prefix of the counts: thread t owns block t
+    int c = (tid < n_blocks) ? __ldcg(counts + tid) : 0;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const int u = __shfl_up_sync(0xffffffffu, c, o);
+        if (lane >= o) c += u;
+    }
+    if (lane == 31) s_i[tid >> 5] = c;
     if (tid == 0) {
         out->s = 0.f;
         out->found = -1;
         out->run_lo = -1;
         out->run_hi = out->run_e = 0;
         out->run_s0 = 0.f;
+        s_done = 0;
+        s_pref[0] = 0;
     }
-    int b0 = 0;
-    __shared__ int s_round[2];  // [0] first block after this round, [1] done flag
-    if (tid == 0) s_round[1] = 0;
     __syncthreads();
-    while (b0 < n_blocks) {
-        // offsets of this round's blocks in the staged list
-        if (tid == 0) {
-            int tot = 0, b = b0;
-            while (b < n_blocks) {
-                const int c = __ldcg(counts + b);
-                if (tot + c > kExactListCap) break;
-                s_off[b - b0] = tot;
-                tot += c;
-                ++b;
+    int off = 0;
+    for (int w = 0; w < (tid >> 5); ++w) off += s_i[w];
+    s_pref[tid + 1] = c + off;
+    __syncthreads();
+    const int tot = s_pref[n_blocks];
+    LPP_WALK_STAMP(0);
+    for (int base = 0; base < tot; base += kExactListCap) {
+        const int m = min(kExactListCap, tot - base);
+        for (int j = tid; j < m; j += kSampleThreads) {
+            const int g = base + j;
+            int lo = 0, hi = n_blocks;  // s_pref[lo] <= g < s_pref[hi]: entry g belongs to block lo
+            while (hi - lo > 1) {
+                const int mid = (lo + hi) >> 1;
+                if (s_pref[mid] <= g)
+                    lo = mid;
+                else
+                    hi = mid;
             }
-            s_off[b - b0] = tot;
-            s_round[0] = b;
+            const uint4* src = reinterpret_cast<const uint4*>(entries + (size_t)lo * kExactMaxEntries + (g - s_pref[lo]));
+            uint4* dst = reinterpret_cast<uint4*>(s_list + j);
+            const uint4 v0 = __ldcg(src), v1 = __ldcg(src + 1);
+            dst[0] = v0;
+            dst[1] = v1;
         }
         __syncthreads();
-        const int b1 = s_round[0];
-        for (int slot = tid; slot < (b1 - b0) * kExactMaxEntries; slot += kSampleThreads) {
-            const int bl = slot / kExactMaxEntries, i = slot - bl * kExactMaxEntries;
-            if (i < s_off[bl + 1] - s_off[bl]) {
-                const uint4* src = reinterpret_cast<const uint4*>(entries + (size_t)(b0 + bl) * kExactMaxEntries + i);
-                uint4* dst = reinterpret_cast<uint4*>(s_list + s_off[bl] + i);
-                dst[0] = __ldcg(src);
-                dst[1] = __ldcg(src + 1);
-            }
-        }
-        __syncthreads();
+        // pass 1 (warp 0, every lane the same): apply the entries speculatively without a branch, keeping the
+        // sum before every entry; the first entry whose prediction fails (or that needs the one-by-one path)
+        // is remembered
         if (tid < 32) {
-            WalkState w = *out;
-            const bool done = walk_list(s_list, s_off[b1 - b0], x, n_total, stop, r, lane, w);
+            unsigned int bits = __float_as_uint(out->s);
+            int bad = 0x7fffffff;
+#pragma unroll 4
+            for (int i = 0; i < m; ++i) {
+                const int4 h = *reinterpret_cast<const int4*>(&s_list[i]);  // kind, lo, hi, e
+                const ulonglong2 d = *reinterpret_cast<const ulonglong2*>(&s_list[i].d0);
+                s_before[i] = bits;
+                // as a map
+                const unsigned int ebase = (unsigned int)(h.w + 127) << 23;
+                const unsigned long long dd = (bits & 1u) ? d.y : d.x;
+                const unsigned int nb = bits + (unsigned int)dd;
+                const bool map_ok = bits - ebase < 0x800000u && dd <= 0x800000ull && nb - ebase <= 0x800000u;
+                // as four values
+                float q = __uint_as_float(bits);
+                q = __fadd_rn(q, __uint_as_float((unsigned int)d.x));
+                q = __fadd_rn(q, __uint_as_float((unsigned int)(d.x >> 32)));
+                q = __fadd_rn(q, __uint_as_float((unsigned int)d.y));
+                q = __fadd_rn(q, __uint_as_float((unsigned int)(d.y >> 32)));
+                const bool is_map = h.x == kEntryMap;
+                const bool fine = is_map ? map_ok : (h.x == kEntryQuad);
+                bad = (!fine && bad == 0x7fffffff) ? i : bad;
+                bits = is_map ? nb : __float_as_uint(q);
+            }
+            s_before[m] = bits;
             if (lane == 0) {
-                *out = w;
-                if (done) s_round[1] = 1;
+                s_ctl[0] = bad;
+                s_ctl[1] = 0x7fffffff;
             }
         }
         __syncthreads();
-        if (s_round[1]) break;
-        b0 = b1;
+        const int bad = s_ctl[0];
+        const int good = min(m, bad);  // entries [0, good) were applied exactly
+        // pass 2: the first entry after which the running sum exceeds r (sums never decrease)
+        if (stop) {
+            for (int i = tid; i < good; i += kSampleThreads)
+                if (r < __uint_as_float(s_before[i + 1])) atomicMin(&s_ctl[1], i);
+            __syncthreads();
+        }
+        const int cross = stop ? s_ctl[1] : 0x7fffffff;
+        if (cross < good) {
+            if (tid == 0) {
+                const ExactEntry e = s_list[cross];
+                float sum = __uint_as_float(s_before[cross]);
+                if (e.kind == kEntryQuad) {
+                    const float v[4] = {__uint_as_float((unsigned int)e.d0), __uint_as_float((unsigned int)(e.d0 >> 32)),
+                                        __uint_as_float((unsigned int)e.d1), __uint_as_float((unsigned int)(e.d1 >> 32))};
+                    int j = 0;
+                    for (; j < 3; ++j) {
+                        sum = __fadd_rn(sum, v[j]);
+                        if (r < sum) break;
+                    }
+                    out->found = e.lo + j;
+                } else {  // inside a map run: the caller redoes the run element by element
+                    out->run_lo = e.lo;
+                    out->run_hi = min(e.hi, n_total);
+                    out->run_e = e.e;
+                    out->run_s0 = sum;
+                }
+                out->s = sum;
+                s_done = 1;
+            }
+        } else if (bad < m) {
+            // a prediction failed: warp 0 goes on from that entry with the checked walk
+            if (tid < 32) {
+                WalkState w = *out;
+                w.s = __uint_as_float(s_before[bad]);
+                const bool done = walk_list(s_list + bad, m - bad, x, n_total, stop, r, lane, w);
+                if (lane == 0) {
+                    *out = w;
+                    if (done) s_done = 1;
+                }
+            }
+        } else if (tid == 0) {
+            out->s = __uint_as_float(s_before[m]);
+        }
+        __syncthreads();
+        if (s_done) break;
     }
 }
 
@@ -409,7 +520,7 @@ static __global__ void __launch_bounds__(kSampleThreads) sample_exact_kernel(con
     __shared__ int s_flag;
     __shared__ int s_found;
     __shared__ __align__(16) ExactEntry s_list[kExactListCap];
-    __shared__ int s_off[kSampleMaxBlocks / 2 + 2];
+    __shared__ int s_pref[kSampleThreads + 1];
     __shared__ WalkState s_walk;
 
     pdl_launch_dependents();
@@ -498,12 +609,10 @@ static __global__ void __launch_bounds__(kSampleThreads) sample_exact_kernel(con
         stamp(3);
 
         // ---- stage 2: entry list of the sequential sum of e
-        double before_blocks = 0.0, total_d = 0.0;
-        for (int b = 0; b < nb; ++b) {
-            const double v = __ldcg(ea.block_sum + b);
-            if (b < (int)blockIdx.x) before_blocks += v;
-            total_d += v;
-        }
+        // approximate sum of e over the blocks before this one (loads in parallel, then a block reduction)
+        double mine = 0.0;
+        for (int b = tid; b < (int)blockIdx.x; b += kSampleThreads) mine += __ldcg(ea.block_sum + b);
+        const double before_blocks = block_sum_double(mine, s_d, tid);
         if (alive) {
             emit_entries(x, before_blocks + (incl - loc), base, n_quads, ea.entries + (size_t)blockIdx.x * kExactMaxEntries,
                          ea.entry_count + blockIdx.x, s_wm, s_wf, s_i, tid);
@@ -512,10 +621,11 @@ static __global__ void __launch_bounds__(kSampleThreads) sample_exact_kernel(con
         stamp(4);
         alive = alive && sampler_grid_barrier(&ea.sync[0], ++bar * nb, st, &s_flag, tid);
         stamp(5);
+        if (blockIdx.x == 0 && tid == 0) { unsigned long long t_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_)); ea.scalars[36] = (float)(t_ & 0xffffffull); ea.scalars[37] = (float)(clock64() & 0xffffffll); }
 
         // ---- stage 3: block 0, warp 0 walks the entries: the exact softmax denominator
         if (alive && blockIdx.x == 0) {
-            walk_all(ea.entries, ea.entry_count, nb, a.logits, a.vocab, false, 0.f, s_list, s_off, &s_walk, tid);
+            walk_all(ea.entries, ea.entry_count, nb, a.logits, a.vocab, false, 0.f, s_list, s_pref, s_i, &s_walk, tid, ea.scalars + 32);
             if (tid == 0) {
                 __stcg(ea.scalars, s_walk.s);
                 __threadfence();
@@ -546,11 +656,12 @@ static __global__ void __launch_bounds__(kSampleThreads) sample_exact_kernel(con
         stamp(8);
         alive = alive && sampler_grid_barrier(&ea.sync[0], ++bar * nb, st, &s_flag, tid);
         stamp(9);
+        if (blockIdx.x == 0 && tid == 0) { unsigned long long t_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_)); ea.scalars[52] = (float)(t_ & 0xffffffull); ea.scalars[53] = (float)(clock64() & 0xffffffll); }
 
         // ---- stage 5: block 0 finds the first index whose running sum exceeds r
         if (alive && blockIdx.x == 0) {
             const float r = st->advance ? a.r_values[st->step_idx] : st->r;
-            walk_all(ea.entries, ea.entry_count, nb, a.logits, a.vocab, true, r, s_list, s_off, &s_walk, tid);
+            walk_all(ea.entries, ea.entry_count, nb, a.logits, a.vocab, true, r, s_list, s_pref, s_i, &s_walk, tid, ea.scalars + 48);
             if (tid == 0) s_found = (s_walk.found >= 0) ? s_walk.found : 0x7fffffff;
             __syncthreads();
             const int run_lo = s_walk.run_lo, run_hi = s_walk.run_hi, E = s_walk.run_e;
@@ -582,7 +693,9 @@ static __global__ void __launch_bounds__(kSampleThreads) sample_exact_kernel(con
                 for (int k = 0; k < 4; ++k) {
                     const Map2 m1 = map_of(y[k], E);
                     S += (S & 1ull) ? m1.d1 : m1.d0;
-                    const float cum = scalbnf((float)(unsigned int)min(S, 1ull << 24), E - 23);
+                    const float cum = (S >= (1ull << 24))
+                                          ? __uint_as_float((unsigned int)(E + 128) << 23)
+                                          : __uint_as_float(((unsigned int)(E + 127) << 23) | ((unsigned int)S & 0x7fffffu));
                     if (q + k < run_hi && r < cum) atomicMin(&s_found, q + k);
                 }
                 __syncthreads();
