@@ -19,15 +19,17 @@
 
 namespace lpp {
 
-constexpr int kAttnThreads = 128;
+constexpr int kAttnThreads = 128;        // a team inside the persistent step kernel
+constexpr int kAttnKernelThreads = 256;  // the stand-alone kernel: 32 position groups, 128 positions in flight
 constexpr int kAttnGroups = kAttnThreads / 8;  // position groups per CTA
-constexpr int kAttnMinChunk = 64;              // fewest positions worth a CTA of its own
+constexpr int kAttnMinChunk = 128;             // fewest positions worth a CTA of its own
 
 // Number of KV splits actually used at sequence length T: short contexts use few CTAs (a split
 // with a handful of positions costs more in the final combine than it saves), long ones all of
 // them.  Every CTA evaluates this identically from the device-resident position.
-__host__ __device__ inline int attn_effective_splits(int T, int max_splits) {
-    int n = (T + kAttnMinChunk - 1) / kAttnMinChunk;
+__host__ __device__ inline int attn_effective_splits(int T, int max_splits, int min_chunk = kAttnMinChunk) {
+    if (min_chunk < 1) min_chunk = kAttnMinChunk;
+    int n = (T + min_chunk - 1) / min_chunk;
     n = n < 1 ? 1 : n;
     return n < max_splits ? n : max_splits;
 }
@@ -42,6 +44,8 @@ struct AttnArgs {
     const StepState* st;
     int seq_len, head_size, gqa, n_splits;
     int n_kv_heads;  // KV heads on this rank
+    int min_chunk;   // fewest positions per split (0 = kAttnMinChunk)
+    unsigned long long* trace;  // timing experiments only: [CTA y*z][8] global-timer stamps of split 0
 };
 
 template <typename KT, int DPL>
@@ -97,6 +101,14 @@ __device__ __forceinline__ void merge_state(float& m, float& l, float (&acc)[DPL
     m = mn;
 }
 
+__device__ __forceinline__ void attn_stamp(const AttnArgs& a, int tid, int k) {
+    if (a.trace && tid == 0 && blockIdx.x == 0) {
+        unsigned long long t;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+        a.trace[(size_t)(blockIdx.y * gridDim.z + blockIdx.z) * 8 + k] = t;
+    }
+}
+
 __device__ __forceinline__ void team_barrier(int id, int nthreads) {
     asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
 }
@@ -108,7 +120,7 @@ __device__ __forceinline__ void team_barrier(int id, int nthreads) {
 // NT = threads in the team (128 for the stand-alone kernel, 256 when a GEMV CTA's consumers run it).
 template <typename KT, int DPL, int GB, int NT = kAttnThreads>
 __device__ __forceinline__ void attn_item(const AttnArgs& a, int split, int kvh, int hz, int n_z, int T, int n_eff,
-                                          float* scratch, int* s_last, int tid, int bar) {
+                                          float* scratch, int* s_last, int tid, int bar, int pos_cur) {
     constexpr int HS = DPL * 8;
     float (*s_state)[GB][HS + 2] = reinterpret_cast<float (*)[GB][HS + 2]>(scratch);
     const int warp = tid >> 5, lane = tid & 31;
@@ -125,11 +137,33 @@ __device__ __forceinline__ void attn_item(const AttnArgs& a, int split, int kvh,
         m[h] = -INFINITY;
         l[h] = 0.f;
 #pragma unroll
-        for (int d = 0; d < DPL; ++d) {
-            q[h][d] = __ldcg(a.q + (size_t)(hbase + h) * HS + sub * DPL + d);
-            acc[h][d] = 0.f;
-        }
+        for (int d = 0; d < DPL; ++d) acc[h][d] = 0.f;
     }
+    // Rows of positions before `pos_cur` were written by earlier steps and are requested before the
+    // dependency wait; q and the row of pos_cur come from the preceding kernel and follow it.
+    bool waited = false;
+    auto wait_and_load_q = [&]() {
+        pdl_wait();
+        attn_stamp(a, tid, 1);
+#pragma unroll
+        for (int h = 0; h < GB; ++h) {
+            const float* qp = a.q + (size_t)(hbase + h) * HS + sub * DPL;
+            if constexpr (DPL % 4 == 0) {
+#pragma unroll
+                for (int d = 0; d < DPL; d += 4) {
+                    const float4 f = __ldcg(reinterpret_cast<const float4*>(qp + d));
+                    q[h][d] = f.x; q[h][d + 1] = f.y; q[h][d + 2] = f.z; q[h][d + 3] = f.w;
+                }
+            } else {
+#pragma unroll
+                for (int d = 0; d < DPL; d += 2) {
+                    const float2 f = __ldcg(reinterpret_cast<const float2*>(qp + d));
+                    q[h][d] = f.x; q[h][d + 1] = f.y;
+                }
+            }
+        }
+        waited = true;
+    };
 
     const KT* kbase = reinterpret_cast<const KT*>(a.k_cache) + (size_t)kvh * a.seq_len * HS + sub * DPL;
     const KT* vbase = reinterpret_cast<const KT*>(a.v_cache) + (size_t)kvh * a.seq_len * HS + sub * DPL;
@@ -147,12 +181,21 @@ __device__ __forceinline__ void attn_item(const AttnArgs& a, int split, int kvh,
         for (int u = 0; u < U; ++u) {
             const int t = base + u * (NT / 8) + grp;
             has[u] = t < t1;
-            if (has[u]) {
+            if (has[u] && t < pos_cur) {
                 load_row_slice<KT, DPL>(kbase + (size_t)t * HS, kk[u]);
                 load_row_slice<KT, DPL>(vbase + (size_t)t * HS, vv[u]);
             } else {
 #pragma unroll
                 for (int d = 0; d < DPL; ++d) kk[u][d] = vv[u][d] = 0.f;
+            }
+        }
+        if (!waited) wait_and_load_q();
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int t = base + u * (NT / 8) + grp;
+            if (has[u] && t >= pos_cur) {
+                load_row_slice<KT, DPL>(kbase + (size_t)t * HS, kk[u]);
+                load_row_slice<KT, DPL>(vbase + (size_t)t * HS, vv[u]);
             }
         }
 #pragma unroll
@@ -197,6 +240,8 @@ __device__ __forceinline__ void attn_item(const AttnArgs& a, int split, int kvh,
         }
     }
 
+    if (!waited) wait_and_load_q();
+    attn_stamp(a, tid, 2);
     // merge the four position groups of a warp (lanes differing in bits 3 and 4)
 #pragma unroll
     for (int h = 0; h < GB; ++h) {
@@ -219,6 +264,7 @@ __device__ __forceinline__ void attn_item(const AttnArgs& a, int split, int kvh,
         }
     }
     team_barrier(bar, NT);
+    attn_stamp(a, tid, 3);
 
     // merge the warps; with a single split the result is final, otherwise it is this split's partial
     constexpr int NW = NT / 32;
@@ -299,16 +345,42 @@ __device__ __forceinline__ void attn_item(const AttnArgs& a, int split, int kvh,
 }
 
 template <typename KT, int DPL, int GB>
-__global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const AttnArgs a) {
-    __shared__ float s_scratch[(kAttnThreads / 32) * GB * (DPL * 8 + 2)];
+__global__ void __launch_bounds__(kAttnKernelThreads) attn_decode_kernel(const AttnArgs a) {
+    __shared__ float s_scratch[(kAttnKernelThreads / 32) * GB * (DPL * 8 + 2)];
     __shared__ int s_last;
+    auto stamp = [&](int k) {
+        if (a.trace && threadIdx.x == 0 && blockIdx.x == 0) {
+            unsigned long long t;
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+            a.trace[(size_t)(blockIdx.y * gridDim.z + blockIdx.z) * 8 + k] = t;
+        }
+    };
+    stamp(0);
     pdl_launch_dependents();  // the next GEMV may start streaming its weights now
-    pdl_wait();
+    // The position was written by the previous step's sampler, which completed before this step began,
+    // and the cache rows of earlier positions by earlier steps: both may be touched before the wait.
     const int pos = a.st->pos;
     const int T = (pos < 0 || pos >= a.seq_len) ? 0 : pos + 1;
-    const int n_eff = attn_effective_splits(T, a.n_splits);
+    const int n_eff = attn_effective_splits(T, a.n_splits, a.min_chunk);
     if ((int)blockIdx.x >= n_eff) return;  // surplus CTA at this sequence length: no work, no ticket
-    attn_item<KT, DPL, GB>(a, blockIdx.x, blockIdx.y, blockIdx.z, gridDim.z, T, n_eff, s_scratch, &s_last, threadIdx.x, 0);
+    {
+        // pull this CTA's share of the K and V rows of positions < pos towards L2 while the QKV kernel
+        // is still running; only q and the row of position pos are read after the wait
+        constexpr int HS = DPL * 8;
+        constexpr int kLines = (HS * (int)sizeof(KT) + 127) / 128;  // 128-byte lines per row (<= 4)
+        const int chunk = (T + n_eff - 1) / n_eff;
+        const int t0 = blockIdx.x * chunk;
+        const int t1 = min(min(T, t0 + chunk), pos);
+        const int sub = threadIdx.x & 7, grp = threadIdx.x >> 3;
+        const char* base = reinterpret_cast<const char*>(sub < 4 ? a.k_cache : a.v_cache) +
+                           (size_t)blockIdx.y * a.seq_len * HS * sizeof(KT) + (size_t)(sub & 3) * 128;
+        if ((sub & 3) < kLines)
+            for (int t = t0 + grp; t < t1; t += kAttnKernelThreads / 8)
+                asm volatile("prefetch.global.L2 [%0];" ::"l"(base + (size_t)t * HS * sizeof(KT)));
+    }
+    attn_item<KT, DPL, GB, kAttnKernelThreads>(a, blockIdx.x, blockIdx.y, blockIdx.z, gridDim.z, T, n_eff, s_scratch, &s_last,
+                                               threadIdx.x, 0, pos);
+    stamp(4);
 }
 
 }  // namespace lpp

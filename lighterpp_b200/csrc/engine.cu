@@ -159,6 +159,7 @@ struct lpp_engine {
     unsigned int* gbar = nullptr;
     int n_gbar = 0;
     unsigned long long* trace = nullptr;  // LPP_STEP_TRACE: per-CTA per-phase time stamps
+    unsigned long long* gtrace = nullptr;  // LPP_GEMV_TRACE: per-launch per-CTA time stamps of the ring GEMV
     int step_slots = 2, step_xs_bytes = 0;
     size_t step_smem = 0;
     // graphs
@@ -246,6 +247,7 @@ static cudaError_t launch_gemv_t(lpp_engine* e, GemvArgs& a, bool pdl, cudaStrea
     if (fixed + ring > e->smem_optin) ring = e->smem_optin - fixed;
     int ns = (int)(ring / ((size_t)kGemvConsumerWarps * a.stage_bytes));  // slots per consumer warp
     ns = std::max(2, std::min(ns, kGemvMaxStages));
+    const int grid = std::max(1, std::min(groups, e->num_sms));
     a.n_stages = ns;
     const size_t smem = fixed + (size_t)kGemvConsumerWarps * ns * a.stage_bytes;
     if (smem > e->smem_optin) return cudaErrorInvalidValue;
@@ -256,7 +258,6 @@ static cudaError_t launch_gemv_t(lpp_engine* e, GemvArgs& a, bool pdl, cudaStrea
         if (r != cudaSuccess) return r;
         attr_done[e->c.device & 63] = true;
     }
-    const int grid = std::max(1, std::min(groups, e->num_sms));
     return launch_kernel(gemv_ring_kernel<WT, EPI>, dim3(grid), dim3(kGemvRingThreads), smem, s, pdl, a);
 }
 
@@ -281,11 +282,11 @@ template <typename KT, int DPL>
 static cudaError_t launch_attn_d(lpp_engine* e, const AttnArgs& a, dim3 grid, bool pdl, cudaStream_t s) {
     switch (e->attn_gb) {
         case 4:
-            return launch_kernel(attn_decode_kernel<KT, DPL, 4>, grid, dim3(kAttnThreads), 0, s, pdl, a);
+            return launch_kernel(attn_decode_kernel<KT, DPL, 4>, grid, dim3(kAttnKernelThreads), 0, s, pdl, a);
         case 2:
-            return launch_kernel(attn_decode_kernel<KT, DPL, 2>, grid, dim3(kAttnThreads), 0, s, pdl, a);
+            return launch_kernel(attn_decode_kernel<KT, DPL, 2>, grid, dim3(kAttnKernelThreads), 0, s, pdl, a);
         default:
-            return launch_kernel(attn_decode_kernel<KT, DPL, 1>, grid, dim3(kAttnThreads), 0, s, pdl, a);
+            return launch_kernel(attn_decode_kernel<KT, DPL, 1>, grid, dim3(kAttnKernelThreads), 0, s, pdl, a);
     }
 }
 template <typename KT>
@@ -433,6 +434,9 @@ static void record_gemv(Recorder& R, int kind, int epi, GemvArgs a) {
     if (skip_mask() & (1u << kind)) return;
     a.st = e->st;
     if (const char* dbg = getenv("LPP_DEBUG_GEMV")) a.debug = (int)strtol(dbg, nullptr, 0);
+    if (getenv("LPP_GEMV_TRACE")) {
+        if (e->gtrace && R.kernels < 256) a.trace = e->gtrace + (size_t)R.kernels * e->num_sms * 8;
+    }
     a.vocab = e->c.vocab_size;
     a.seq_len = e->c.seq_len;
     R.mark(kind);
@@ -510,6 +514,10 @@ static void set_prefetch(const lpp_engine* e, GemvArgs& a, int kind, int l) {
     }
     size_t cap = 8;
     if (const char* v = getenv("LPP_PF_MB")) cap = (size_t)std::max(0, atoi(v));
+    if (kind == kOproj)
+        if (const char* v = getenv("LPP_PF_OPROJ_MB")) cap = (size_t)std::max(0, atoi(v));
+    if (kind == kQkv)
+        if (const char* v = getenv("LPP_PF_QKV_MB")) cap = (size_t)std::max(0, atoi(v));
     const void* p;
     size_t bytes;
     matrix_span(e, nk, nl, &p, &bytes);
@@ -563,6 +571,7 @@ static void record_step(Recorder& R, bool with_sampler) {
             at.gqa = e->gqa;
             at.n_splits = e->attn_splits;
             at.n_kv_heads = e->KVHl;
+            if (const char* mc = getenv("LPP_ATTN_CHUNK")) at.min_chunk = atoi(mc);  // timing experiments
             {
                 set_prefetch(e, a, kQkv, l);
                 record_gemv(R, kQkv, kEpiQkv, a);
@@ -573,6 +582,7 @@ static void record_step(Recorder& R, bool with_sampler) {
                     ph.at = at;
                     record_phase(R, ph);
                 } else if (!(skip_mask() & (1u << kAttn))) {
+                    if (e->gtrace && R.kernels < 256) at.trace = e->gtrace + (size_t)R.kernels * e->num_sms * 8;
                     R.mark(kAttn);
                     R.check(c.kv_dtype == LPP_F32 ? launch_attn_t<float>(e, at, grid, R.pdl(), R.s)
                                                   : launch_attn_t<__half>(e, at, grid, R.pdl(), R.s),
@@ -1026,6 +1036,10 @@ extern "C" lpp_status lpp_finalize(lpp_engine* e) {
         e->step_smem = fixed + (size_t)kGemvConsumerWarps * e->step_slots * kStageTarget;
         if (e->step_smem > e->smem_optin) e->persistent = false;
     }
+    if (getenv("LPP_GEMV_TRACE") && !e->gtrace) {
+        CU(cudaMalloc(&e->gtrace, (size_t)256 * e->num_sms * 8 * sizeof(unsigned long long)));
+        CU(cudaMemset(e->gtrace, 0, (size_t)256 * e->num_sms * 8 * sizeof(unsigned long long)));
+    }
     if (e->persistent) {
         e->h_phases.clear();
         Recorder R{e, e->stream};
@@ -1209,6 +1223,16 @@ extern "C" lpp_status lpp_kv_read(lpp_engine* e, int layer, int kv_head, int pos
 
 // Timing aid (not part of the public header): copies the time stamps the step kernel left when the
 // engine was finalized with LPP_STEP_TRACE set; n_out = ctas * phases * 4 values.
+// Debugging aid (not part of the public header): per-CTA time stamps of the ring GEMV launches of one step.
+extern "C" int lpp_debug_gemv_trace(lpp_engine* e, unsigned long long* out, int max_values) {
+    if (!e || !e->gtrace || !out) return -1;
+    const size_t n = (size_t)256 * e->num_sms * 8;
+    if ((size_t)max_values < n) return -2;
+    cudaStreamSynchronize(e->stream);
+    if (cudaMemcpy(out, e->gtrace, n * sizeof(unsigned long long), cudaMemcpyDeviceToHost) != cudaSuccess) return -3;
+    return e->num_sms;
+}
+
 extern "C" int lpp_debug_step_trace(lpp_engine* e, unsigned long long* out, int max_values, int* ctas, int* phases) {
     if (!e || !e->trace || !out) return -1;
     const size_t n = (size_t)e->num_sms * e->h_phases.size() * 4;

@@ -67,6 +67,7 @@ struct GemvArgs {
     unsigned int pf_bytes;
     int debug;        // timing experiments only: 1 = consumers skip the arithmetic, 2 = producer skips the copies
     int xs_bytes;     // shared-memory bytes reserved for the staged input (0 = K floats rounded up to 128)
+    unsigned long long* trace;  // timing experiments only: [CTA][8] global-timer stamps, nullptr = none
 };
 
 // ------------------------------------------------------------------ x staging layouts
@@ -83,6 +84,14 @@ __device__ __forceinline__ int xs_index<__half>(int k, int K) {
 template <>
 __device__ __forceinline__ int xs_index<float>(int k, int /*K*/) {
     return k;
+}
+
+__device__ __forceinline__ void gemv_stamp(const GemvArgs& a, int k) {
+    if (a.trace) {
+        unsigned long long t;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+        a.trace[(size_t)blockIdx.x * 8 + k] = t;
+    }
 }
 
 __device__ __forceinline__ void consumer_barrier(int nthreads) {
@@ -117,6 +126,7 @@ __device__ __forceinline__ void stage_input(const GemvArgs& a, float* xs, float*
         }
     }
     pdl_wait();  // activations / KV / step state come from the previous kernel
+    if (tid == 0) gemv_stamp(a, 1);
 
     if (a.emb) {
         // first layer: the input is the embedding row of the device-resident token, widened exactly
@@ -306,7 +316,7 @@ __device__ __forceinline__ void gemv_epilogue(const GemvArgs& a, int g, float v0
         if (row < a.q_rows + a.kv_rows) {
             // adjacent-pair rotation with the table entry for (pos, (row % hs)/2) (src/ops.cpp:34-54);
             // separate multiply and subtract/add, as the reference's scalar code rounds
-            const float2 cs = a.rope[(size_t)pos * (hs >> 1) + ((row % hs) >> 1)];
+            const float2 cs = __ldg(a.rope + (size_t)pos * (hs >> 1) + ((row % hs) >> 1));
             const float r0 = __fsub_rn(__fmul_rn(v0, cs.x), __fmul_rn(v1, cs.y));
             const float r1 = __fadd_rn(__fmul_rn(v0, cs.y), __fmul_rn(v1, cs.x));
             v0 = r0;
@@ -356,6 +366,11 @@ __device__ __forceinline__ bool gemv_ring_body(const GemvArgs& a, unsigned char*
     const int m = a.pairs_per_stage;
     const int nch = m > 0 ? 1 : (a.K + a.kc - 1) / a.kc;
 
+    if (tid == 0) gemv_stamp(a, 0);
+    // The dependent kernel is released for launch at once: its CTAs take over an SM as soon as one of
+    // this kernel's CTAs leaves it and start streaming their own weights while the rest of this grid
+    // finishes (they still wait for this grid's completion before touching activations).
+    if (tid == 0 && !(a.debug & 4)) pdl_launch_dependents();
     if (tid == 0) reinterpret_cast<int*>(smem + kGemvBarrierBytes + 64)[2] = 0;
     if (tid < kGemvConsumerWarps * NS) {
         const int bw = tid / NS, sl = tid - bw * NS;
@@ -390,6 +405,7 @@ __device__ __forceinline__ bool gemv_ring_body(const GemvArgs& a, unsigned char*
                 }
                 return true;
             };
+            if (lane == 0) gemv_stamp(a, 5);
             if (m > 0) {
                 for (int p = p0; p < p1 && alive; p += m) {
                     const int cnt = min(m, p1 - p);
@@ -405,6 +421,7 @@ __device__ __forceinline__ bool gemv_ring_body(const GemvArgs& a, unsigned char*
                                           (uint32_t)(klen * sizeof(WT)));
                         }
             }
+            if (lane == 0) gemv_stamp(a, 6);
             // this lane's HBM requests are all queued: pull its share of the next kernel's weights
             // towards L2 so the memory system stays busy across the kernel boundary
             if (a.pf && alive) {
@@ -420,12 +437,23 @@ __device__ __forceinline__ bool gemv_ring_body(const GemvArgs& a, unsigned char*
         }
         __syncwarp();
         // all of this CTA's copies are issued: the next kernel may start launching
-        if (lane == 0) pdl_launch_dependents();
+        if (lane == 0 && (a.debug & 4)) pdl_launch_dependents();
         return false;
     }
 
     // ---------------- consumers
+    if constexpr (EPI == kEpiQkv) {
+        // The position is written by the previous step's sampler, which completed before this step
+        // began, and the rotation table is constant: both are pulled into L1 before the dependency
+        // wait so the epilogue of the first row pairs does not pay two L2 round trips in a row.
+        const int pos = a.st->pos;
+        if (pos >= 0 && pos < a.seq_len && tid < (a.head_size >> 1)) {
+            const float2 cs = __ldg(a.rope + (size_t)pos * (a.head_size >> 1) + tid);
+            asm volatile("" ::"f"(cs.x), "f"(cs.y));
+        }
+    }
     stage_input<WT, kGemvConsumerWarps * 32>(a, xs, red, tid);
+    if (tid == 0) gemv_stamp(a, 2);
 
     uint64_t* myfull = full + w * kGemvMaxStages;
     uint64_t* myempty = empty + w * kGemvMaxStages;
@@ -445,6 +473,12 @@ __device__ __forceinline__ bool gemv_ring_body(const GemvArgs& a, unsigned char*
     // A warp whose wait runs out stops consuming but still returns through the common exit, so a
     // CTA-level tail (which uses CTA barriers) is never left waiting for it.
     bool ok = true;
+    // Residual epilogue: the residual of this warp's first pair is requested now, so its L2 round
+    // trip runs beside the dot product instead of after it (the weights are usually in the ring
+    // already when the input arrives).  The producing kernel has completed: stage_input waited.
+    float2 r_first = make_float2(0.f, 0.f);
+    if (EPI == kEpiResid && a.resid && lane == 0 && p0 < p1)
+        r_first = __ldcg(reinterpret_cast<const float2*>(a.resid + (size_t)p0 * kRowsPerGroup));
     if (m > 0) {
         for (int p = p0; p < p1 && ok; p += m) {
             const int cnt = min(m, p1 - p);
@@ -452,6 +486,7 @@ __device__ __forceinline__ bool gemv_ring_body(const GemvArgs& a, unsigned char*
                 ok = false;
                 break;
             }
+            if (tid == 0 && p == p0) gemv_stamp(a, 3);
             const unsigned char* st = myring + (size_t)slot * a.stage_bytes;
             for (int i = 0; i < cnt; ++i) {
                 float acc0 = 0.f, acc1 = 0.f;
@@ -459,7 +494,13 @@ __device__ __forceinline__ bool gemv_ring_body(const GemvArgs& a, unsigned char*
                 if (!(a.debug & 1)) dot_rows<WT, 2, false>(r0, r0 + row_bytes, xs, a.K, 0, a.K, lane, acc0, acc1);
                 acc0 = warp_sum(acc0);
                 acc1 = warp_sum(acc1);
-                if (lane == 0) gemv_epilogue<EPI>(a, p + i, acc0, acc1);
+                if (lane == 0) {
+                    if (EPI == kEpiResid && p + i == p0)
+                        *reinterpret_cast<float2*>(a.out + (size_t)p0 * kRowsPerGroup) =
+                            make_float2(acc0 + r_first.x, acc1 + r_first.y);
+                    else
+                        gemv_epilogue<EPI>(a, p + i, acc0, acc1);
+                }
             }
             release();
         }
@@ -482,10 +523,16 @@ __device__ __forceinline__ bool gemv_ring_body(const GemvArgs& a, unsigned char*
                 }
             if (!ok) break;
             const float v0 = warp_sum(acc[0]), v1 = warp_sum(acc[1]);
-            if (lane == 0) gemv_epilogue<EPI>(a, p, v0, v1);
+            if (lane == 0) {
+                if (EPI == kEpiResid && p == p0)
+                    *reinterpret_cast<float2*>(a.out + (size_t)p0 * kRowsPerGroup) = make_float2(v0 + r_first.x, v1 + r_first.y);
+                else
+                    gemv_epilogue<EPI>(a, p, v0, v1);
+            }
         }
     }
     if (!ok) reinterpret_cast<int*>(smem + kGemvBarrierBytes + 64)[2] = 1;  // abort flag for a CTA-level tail
+    if (tid == 0) gemv_stamp(a, 4);
     return true;
 }
 

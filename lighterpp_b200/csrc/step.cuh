@@ -284,7 +284,7 @@ __global__ void __launch_bounds__(kGemvRingThreads) step_kernel(const StepArgs s
             const int team = tid >> 7, t128 = tid & 127;
             const int pos = at.st->pos;
             const int T = (pos < 0 || pos >= at.seq_len) ? 0 : pos + 1;
-            const int n_eff = attn_effective_splits(T, at.n_splits);
+            const int n_eff = attn_effective_splits(T, at.n_splits, at.min_chunk);
             const int n_z = at.gqa / GB;
             const int items = n_eff * at.n_kv_heads * n_z;
             float* scratch = xs + (size_t)team * (kAttnThreads / 32) * GB * (DPL * 8 + 2);
@@ -292,7 +292,7 @@ __global__ void __launch_bounds__(kGemvRingThreads) step_kernel(const StepArgs s
                 const int split = it % n_eff;
                 const int rest = it / n_eff;
                 attn_item<KT, DPL, GB>(at, split, rest / n_z, rest % n_z, n_z, T, n_eff, scratch, s_flag + 1 + team, t128,
-                                       2 + team);
+                                       2 + team, pos);
             }
             if (tr) tr[2] = tr[3] = global_timer_ns();
         }
