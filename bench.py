@@ -183,15 +183,21 @@ def run_ours(args, rank, world):
 
     # ---- per-kernel durations (CUDA events inside a replayed graph) for the roofline object
     prof = eng.profile_step(pos - args.steps // 2, 10)
+    gemv_kinds = {k: v for k, v in prof.items() if (k.endswith("gemv") or k == "step_kernel") and v["launches"]}
+    dom = max(gemv_kinds, key=lambda k: gemv_kinds[k]["bytes"])  # the kernel family that moves most bytes per step
+    try:
+        # its launches of one step back to back, launched as the step launches them, one event pair around
+        dom_run = eng.profile_kind(pos - args.steps // 2, dom, 10)
+    except Exception:
+        dom_run = None
     line = None
     if rank == 0:
         peak, peak_kind = measured_peak()
         us = dev_ms * 1e3 / args.steps
-        gemv = {k: v for k, v in prof.items() if (k.endswith("gemv") or k == "step_kernel") and v["launches"]}
-        dom = max(gemv, key=lambda k: gemv[k]["ms"])
-        d = gemv[dom]
+        d = gemv_kinds[dom]
         per_launch_bytes = d["bytes"] / d["launches"]
-        per_launch_us = d["ms"] * 1e3 / d["launches"]
+        isolated_us = d["ms"] * 1e3 / d["launches"]
+        per_launch_us = dom_run["ms_per_launch"] * 1e3 if dom_run and dom_run["launches"] else isolated_us
         achieved = per_launch_bytes / per_launch_us / 1e3
         step_gbs = mean_bytes / us / 1e3
         traffic = None
@@ -221,7 +227,10 @@ def run_ours(args, rank, world):
             "roofline": {"bound": "hbm", "kernel": dom, "achieved": round(achieved, 1), "peak": peak,
                          "peak_source": f"{peak_kind} copy bandwidth", "unit": "GB/s", "frac": round(achieved / peak, 4),
                          "traffic": traffic, "bytes_per_launch": int(per_launch_bytes),
-                         "us_per_launch": round(per_launch_us, 3)},
+                         "us_per_launch": round(per_launch_us, 3), "isolated_us_per_launch": round(isolated_us, 3),
+                         "timed_with": "one CUDA event pair around the step's launches of this kernel run back to back "
+                                       "with the step's launch attributes (each streams its own layer's weights); "
+                                       "isolated = event-record nodes around every single launch, no overlap"},
             "kernels": {k: {"us_per_launch": round(v["ms"] * 1e3 / v["launches"], 3), "launches": v["launches"],
                             "gbs": round(v["bytes"] / v["ms"] / 1e6, 1) if v["ms"] else None}
                         for k, v in prof.items() if v["launches"]},

@@ -162,6 +162,14 @@ int64_t lpp_step_bytes(const lpp_engine* e, int pos);
  * kind, launches[10] launches per step, bytes[10] algorithmic bytes per step. */
 lpp_status lpp_profile_step(lpp_engine* e, int pos, int iters, float* ms, int* launches, int64_t* bytes);
 
+/* Average duration of one launch of kernel kind `kind` (numbering above) when the step's launches of
+ * that kind run back to back at `pos`, launched as the step launches them (programmatic dependent
+ * launch between consecutive kernels), timed with one CUDA event pair on the engine stream around
+ * the sequence and averaged over `iters` repetitions.  Each launch streams its own layer's weights.
+ * *launches = launches of that kind per step.  The activations the kernels see are stale: call it
+ * between steps, never inside a run.  Not available with LPP_FLAG_PERSISTENT. */
+lpp_status lpp_profile_kind(lpp_engine* e, int pos, int kind, int iters, float* ms_per_launch, int* launches);
+
 /* ---- standalone operators: the host wrappers of src/kernels.cuh:24-36, device pointers in/out,
  *      launched on `stream` (a cudaStream_t, NULL = default stream) ------------------------------ */
 

@@ -174,6 +174,7 @@ struct lpp_engine {
     // profiling hooks
     bool profiling = false;
     bool profiling_capture = false;
+    int only_kind = -1;  // lpp_profile_kind: the one kind recorded
     std::vector<cudaEvent_t> prof_events;
     std::vector<int> prof_kinds;
 };
@@ -384,6 +385,10 @@ static unsigned skip_mask() {
     const char* v = getenv("LPP_DEBUG_SKIP");
     return v ? (unsigned)strtol(v, nullptr, 0) : 0u;
 }
+// only_kind >= 0 (lpp_profile_kind): every other kind is left out of the recorded sequence.
+static bool kind_skipped(const lpp_engine* e, int kind) {
+    return (skip_mask() & (1u << kind)) || (e->only_kind >= 0 && kind != e->only_kind);
+}
 
 // Persistent mode: launches the phases counted since the last flush as one step-kernel run.
 static void flush_phases(Recorder& R) {
@@ -431,7 +436,7 @@ static void record_gemv(Recorder& R, int kind, int epi, GemvArgs a) {
         record_phase(R, ph);
         return;
     }
-    if (skip_mask() & (1u << kind)) return;
+    if (kind_skipped(e, kind)) return;
     a.st = e->st;
     if (const char* dbg = getenv("LPP_DEBUG_GEMV")) a.debug = (int)strtol(dbg, nullptr, 0);
     if (getenv("LPP_GEMV_TRACE")) {
@@ -449,7 +454,7 @@ static void record_gemv(Recorder& R, int kind, int epi, GemvArgs a) {
 static void record_allreduce(Recorder& R, float* buf, int n) {
     lpp_engine* e = R.e;
     flush_phases(R);
-    if (R.collect) return;
+    if (R.collect || kind_skipped(e, kAllReduce)) return;
     R.mark(kAllReduce);
     nccl::result_t r = nccl::AllReduce(buf, buf, (size_t)n, nccl::kFloat32, nccl::kSum, e->comm, R.s);
     if (r != 0 && R.err == cudaSuccess) {
@@ -581,7 +586,7 @@ static void record_step(Recorder& R, bool with_sampler) {
                     ph.type = kPhaseAttn;
                     ph.at = at;
                     record_phase(R, ph);
-                } else if (!(skip_mask() & (1u << kAttn))) {
+                } else if (!kind_skipped(e, kAttn)) {
                     if (e->gtrace && R.kernels < 256) at.trace = e->gtrace + (size_t)R.kernels * e->num_sms * 8;
                     R.mark(kAttn);
                     R.check(c.kv_dtype == LPP_F32 ? launch_attn_t<float>(e, at, grid, R.pdl(), R.s)
@@ -653,7 +658,7 @@ static void record_step(Recorder& R, bool with_sampler) {
         R.check(cudaMemsetAsync(e->gbar, 0, (size_t)e->n_gbar * sizeof(unsigned int), R.s), "gbar memset");
         R.prev_kernel = false;
     }
-    if (with_sampler && !(skip_mask() & (1u << kSampler))) {
+    if (with_sampler && !kind_skipped(e, kSampler)) {
         R.mark(kSampler);
         R.check(launch_sampler(e, R.s, R.pdl(), e->persistent), "sampler launch");
         R.mark(-1);
@@ -1288,6 +1293,53 @@ extern "C" int64_t lpp_step_bytes(const lpp_engine* e, int pos) {
     kind_bytes(e, pos, b);
     for (int k = 0; k < kKinds; ++k) t += b[k];
     return t;
+}
+
+// Average duration of one launch of `kind` when all of the step's launches of that kind run back to
+// back, with the launch attributes the step uses (programmatic dependent launch between them) and one
+// CUDA event pair on the engine stream around the whole sequence.  Every launch streams its own
+// layer's weights, so consecutive launches never find them in L2.  Activations are whatever the
+// buffers hold: the results are meaningless and the next real step overwrites them.
+extern "C" lpp_status lpp_profile_kind(lpp_engine* e, int pos, int kind, int iters, float* ms_per_launch, int* launches) {
+    NEED_READY(e);
+    if (!ms_per_launch || !launches || iters <= 0 || kind < 0 || kind >= kKinds) return fail(LPP_ERR_INVALID_ARG, "bad argument");
+    if (pos < 0 || pos >= e->c.seq_len) return fail(LPP_ERR_INVALID_ARG, "pos out of range");
+    if (e->persistent) return fail(LPP_ERR_INVALID_ARG, "not available with the persistent step kernel");
+    *ms_per_launch = 0.f;
+    *launches = 0;
+    lpp_sample_params sp = {0.8f, 1.1f};
+    cudaGraphExec_t gx = nullptr;
+    int n_kernels = 0;
+    e->only_kind = kind;
+    lpp_status rs = capture(e, true, false, &gx, &n_kernels);
+    e->only_kind = -1;
+    if (rs != LPP_OK) return rs;
+    if (n_kernels == 0 && kind != kAllReduce) {
+        cudaGraphExecDestroy(gx);
+        return LPP_OK;
+    }
+    float total = 0.f;
+    for (int it = 0; it < iters + 2 && rs == LPP_OK; ++it) {  // two warm-up rounds
+        rs = push_state(e, 0, pos, &sp, nullptr, 0, 0.5f, 0, 0);
+        if (rs != LPP_OK) break;
+        cudaEventRecord(e->ev0, e->stream);
+        cudaError_t le = cudaGraphLaunch(gx, e->stream);
+        cudaEventRecord(e->ev1, e->stream);
+        cudaError_t se = cudaStreamSynchronize(e->stream);
+        if (le != cudaSuccess || se != cudaSuccess) {
+            rs = fail(LPP_ERR_CUDA, "profile kind: %s", cudaGetErrorString(le != cudaSuccess ? le : se));
+            break;
+        }
+        float t = 0.f;
+        cudaEventElapsedTime(&t, e->ev0, e->ev1);
+        if (it >= 2) total += t;
+    }
+    cudaGraphExecDestroy(gx);
+    if (rs == LPP_OK) {
+        *launches = n_kernels;
+        *ms_per_launch = n_kernels > 0 ? total / iters / n_kernels : total / iters;
+    }
+    return rs;
 }
 
 extern "C" lpp_status lpp_profile_step(lpp_engine* e, int pos, int iters, float* ms, int* launches, int64_t* bytes) {

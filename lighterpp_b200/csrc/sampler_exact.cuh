@@ -370,13 +370,12 @@ __device__ __noinline__ bool walk_list(const ExactEntry* list, int count, const 
     return false;
 }
 
-#define LPP_WALK_STAMP(k) do { } while (0)
 // Whole-block walk.  The blocks' entry lists are concatenated in block order (a prefix sum of the
 // counts gives every entry its place), staged into shared memory kExactListCap at a time, and
 // applied by warp 0.  Returns the final state in *out (shared memory).
 __device__ __noinline__ void walk_all(const ExactEntry* entries, const int* counts, int n_blocks, const float* x,
                                          int n_total, bool stop, float r, ExactEntry* s_list, int* s_pref, int* s_i,
-                                         WalkState* out, int tid, float* dbg = nullptr) {
+                                         WalkState* out, int tid) {
     static_assert(kSampleMaxBlocks <= kSampleThreads, "one thread per block's count");
     const int lane = tid & 31;
     __shared__ int s_done;
@@ -405,7 +404,6 @@ __device__ __noinline__ void walk_all(const ExactEntry* entries, const int* coun
     s_pref[tid + 1] = c + off;
     __syncthreads();
     const int tot = s_pref[n_blocks];
-    LPP_WALK_STAMP(0);
     for (int base = 0; base < tot; base += kExactListCap) {
         const int m = min(kExactListCap, tot - base);
         for (int j = tid; j < m; j += kSampleThreads) {
@@ -522,6 +520,7 @@ static __global__ void __launch_bounds__(kSampleThreads) sample_exact_kernel(con
     __shared__ __align__(16) ExactEntry s_list[kExactListCap];
     __shared__ int s_pref[kSampleThreads + 1];
     __shared__ WalkState s_walk;
+    __shared__ int s_hist[kHistoryMax];
 
     pdl_launch_dependents();
     pdl_wait();
@@ -536,33 +535,25 @@ static __global__ void __launch_bounds__(kSampleThreads) sample_exact_kernel(con
     const int hist_len = min(st->history_len, kHistoryMax);
     const bool greedy = (temperature == 0.0f);
     unsigned int bar = 0;  // barriers passed so far
-    // timing aid: block 0 leaves global-timer stamps (ns since its start) in scalars[4..]
-    unsigned long long t_start = 0;
-    if (blockIdx.x == 0 && tid == 0) asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_start));
-    auto stamp = [&](int k) {
-        if (blockIdx.x == 0 && tid == 0) {
-            unsigned long long t;
-            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-            ea.scalars[4 + k] = (float)(t - t_start);
-        }
-    };
-
     // ---- stage 0: penalty, temperature, block maximum (element i of the block lives in s_val[i])
     for (int i = tid; i < kSampleChunk; i += kSampleThreads) s_val[i] = (i < n) ? __ldcg(a.logits + base + i) : 0.f;
     __syncthreads();
     if (penalty > 1.0f && hist_len > 0) {
+        // the history is scanned by every thread that owns one of its entries: keep it in shared memory
+        for (int i = tid; i < hist_len; i += kSampleThreads) s_hist[i] = st->history[i];
+        __syncthreads();
         for (int i = tid; i < hist_len; i += kSampleThreads) {
-            const int tok = st->history[i];
+            const int tok = s_hist[i];
             if (tok < base || tok >= base + n) continue;
             bool first = true;
             for (int j = 0; j < i; ++j)
-                if (st->history[j] == tok) {
+                if (s_hist[j] == tok) {
                     first = false;
                     break;
                 }
             if (!first) continue;
             int cnt = 1;
-            for (int j = i + 1; j < hist_len; ++j) cnt += (st->history[j] == tok);
+            for (int j = i + 1; j < hist_len; ++j) cnt += (s_hist[j] == tok);
             float v = s_val[tok - base];
             for (int c = 0; c < cnt; ++c) v = (v > 0.f) ? __fdiv_rn(v, penalty) : __fmul_rn(v, penalty);
             s_val[tok - base] = v;
@@ -581,9 +572,7 @@ static __global__ void __launch_bounds__(kSampleThreads) sample_exact_kernel(con
         __stcg(a.part_max + blockIdx.x, best.v);
         __stcg(a.part_idx + blockIdx.x, best.i);
     }
-    stamp(0);
     bool alive = sampler_grid_barrier(&ea.sync[0], ++bar * nb, st, &s_flag, tid);
-    stamp(1);
 
     // ---- global maximum (every block reduces the partials itself)
     MaxIdx g = {-INFINITY, 0x7fffffff};
@@ -604,9 +593,7 @@ static __global__ void __launch_bounds__(kSampleThreads) sample_exact_kernel(con
         }
         const double incl = block_scan_double(loc, s_d, tid);
         if (tid == kSampleThreads - 1) ea.block_sum[blockIdx.x] = incl;
-        stamp(2);
         alive = sampler_grid_barrier(&ea.sync[0], ++bar * nb, st, &s_flag, tid);
-        stamp(3);
 
         // ---- stage 2: entry list of the sequential sum of e
         // approximate sum of e over the blocks before this one (loads in parallel, then a block reduction)
@@ -618,22 +605,17 @@ static __global__ void __launch_bounds__(kSampleThreads) sample_exact_kernel(con
                          ea.entry_count + blockIdx.x, s_wm, s_wf, s_i, tid);
             __threadfence();
         }
-        stamp(4);
         alive = alive && sampler_grid_barrier(&ea.sync[0], ++bar * nb, st, &s_flag, tid);
-        stamp(5);
-        if (blockIdx.x == 0 && tid == 0) { unsigned long long t_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_)); ea.scalars[36] = (float)(t_ & 0xffffffull); ea.scalars[37] = (float)(clock64() & 0xffffffll); }
 
         // ---- stage 3: block 0, warp 0 walks the entries: the exact softmax denominator
         if (alive && blockIdx.x == 0) {
-            walk_all(ea.entries, ea.entry_count, nb, a.logits, a.vocab, false, 0.f, s_list, s_pref, s_i, &s_walk, tid, ea.scalars + 32);
+            walk_all(ea.entries, ea.entry_count, nb, a.logits, a.vocab, false, 0.f, s_list, s_pref, s_i, &s_walk, tid);
             if (tid == 0) {
                 __stcg(ea.scalars, s_walk.s);
                 __threadfence();
             }
         }
-        stamp(6);
         alive = alive && sampler_grid_barrier(&ea.sync[0], ++bar * nb, st, &s_flag, tid);
-        stamp(7);
 
         // ---- stage 4: p = e / sum (IEEE division), entry list of the running CDF
         const float denom = __ldcg(ea.scalars);
@@ -653,15 +635,12 @@ static __global__ void __launch_bounds__(kSampleThreads) sample_exact_kernel(con
                          ea.entry_count + blockIdx.x, s_wm, s_wf, s_i, tid);
             __threadfence();
         }
-        stamp(8);
         alive = alive && sampler_grid_barrier(&ea.sync[0], ++bar * nb, st, &s_flag, tid);
-        stamp(9);
-        if (blockIdx.x == 0 && tid == 0) { unsigned long long t_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_)); ea.scalars[52] = (float)(t_ & 0xffffffull); ea.scalars[53] = (float)(clock64() & 0xffffffll); }
 
         // ---- stage 5: block 0 finds the first index whose running sum exceeds r
         if (alive && blockIdx.x == 0) {
             const float r = st->advance ? a.r_values[st->step_idx] : st->r;
-            walk_all(ea.entries, ea.entry_count, nb, a.logits, a.vocab, true, r, s_list, s_pref, s_i, &s_walk, tid, ea.scalars + 48);
+            walk_all(ea.entries, ea.entry_count, nb, a.logits, a.vocab, true, r, s_list, s_pref, s_i, &s_walk, tid);
             if (tid == 0) s_found = (s_walk.found >= 0) ? s_walk.found : 0x7fffffff;
             __syncthreads();
             const int run_lo = s_walk.run_lo, run_hi = s_walk.run_hi, E = s_walk.run_e;
@@ -706,7 +685,6 @@ static __global__ void __launch_bounds__(kSampleThreads) sample_exact_kernel(con
 
     // ---- exit ticket: the last block to get here publishes the result and resets the counters
     __syncthreads();
-    stamp(10);
     if (blockIdx.x == 0 && tid == 0) {
         st->out_token = token;
         if (st->advance) {

@@ -32,7 +32,7 @@ EXPORTS = [
     "lpp_engine_create", "lpp_engine_destroy", "lpp_nccl_unique_id", "lpp_upload_tensor", "lpp_finalize",
     "lpp_step", "lpp_step_logits", "lpp_decode", "lpp_sample_logits", "lpp_kv_prefill", "lpp_kv_read",
     "lpp_kv_index", "lpp_strerror", "lpp_last_error", "lpp_engine_stream", "lpp_kernels_per_step",
-    "lpp_step_bytes", "lpp_profile_step", "lpp_op_convert_f32_to_f16", "lpp_op_gemv", "lpp_op_rmsnorm",
+    "lpp_step_bytes", "lpp_profile_step", "lpp_profile_kind", "lpp_op_convert_f32_to_f16", "lpp_op_gemv", "lpp_op_rmsnorm",
     "lpp_op_rope", "lpp_op_swiglu", "lpp_op_softmax_multihead", "lpp_op_scale_multihead",
     "lpp_op_aggregation_multihead", "lpp_op_residual_add", "lpp_op_scatter_kv", "lpp_op_multihead_gemv",
     "lpp_op_rope_scatter", "lpp_op_sample", "lpp_op_sample_static",
@@ -94,6 +94,7 @@ def load_library() -> C.CDLL:
     lib.lpp_step_bytes.argtypes = [vp, C.c_int]
     lib.lpp_step_bytes.restype = C.c_int64
     lib.lpp_profile_step.argtypes = [vp, C.c_int, C.c_int, fp, ip, C.POINTER(C.c_int64)]
+    lib.lpp_profile_kind.argtypes = [vp, C.c_int, C.c_int, C.c_int, fp, ip]
     _lib = lib
     return lib
 
@@ -260,6 +261,14 @@ class Engine:
         b = (C.c_int64 * 10)()
         _check(self.lib.lpp_profile_step(self.h, int(pos), int(iters), ms, n, b), "lpp_profile_step")
         return {KINDS[i]: {"ms": float(ms[i]), "launches": int(n[i]), "bytes": int(b[i])} for i in range(10)}
+
+    def profile_kind(self, pos: int, kind: str, iters: int = 5) -> Dict[str, float]:
+        """Average launch duration of one kernel kind, its launches of a step run back to back."""
+        ms = C.c_float(0.0)
+        n = C.c_int(0)
+        _check(self.lib.lpp_profile_kind(self.h, int(pos), KINDS.index(kind), int(iters), C.byref(ms), C.byref(n)),
+               "lpp_profile_kind")
+        return {"ms_per_launch": float(ms.value), "launches": int(n.value)}
 
     def close(self) -> None:
         if getattr(self, "h", None):
