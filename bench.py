@@ -120,6 +120,11 @@ def run_ours(args, rank, world):
         nccl_id = ids[0]
     eng = E.Engine(cfg, dtype, "f16" if dtype == "f16" else "f32", device=local, tp_rank=rank, tp_size=world,
                    nccl_id=nccl_id, flags=args.flags, ring_kb=args.ring_kb)
+    if world > 1 and not (args.flags & E.FLAG_TP_NCCL):
+        # the o_proj / down exchange fused into the GEMVs over peer memory: map every rank's receive buffer
+        handles = [None] * world
+        dist.all_gather_object(handles, eng.tp_export())
+        eng.tp_connect(handles)
     host_copy = {} if (rank == 0 and world == 1 and not args.no_cpu_baseline) else None
     for name, l, t in gen_device_weights(cfg, dtype, tied, seed):
         eng.upload(name, t, max(l, 0))

@@ -62,6 +62,8 @@ typedef enum {
 #define LPP_FLAG_NO_GRAPH 0x4u   /* launch the step kernel by kernel instead of replaying the CUDA graph */
 #define LPP_FLAG_FAST_SAMPLER 0x10u /* tree-sum sampler: ~20 us faster per token, categorical ids no longer follow the
                                       reference's sequential FP32 sums bit for bit */
+#define LPP_FLAG_TP_NCCL 0x20u   /* tensor parallelism: keep the NCCL all-reduce after o_proj / down even when the peers
+                                  * are mapped (lpp_tp_connect); default is the exchange fused into the GEMVs */
 #define LPP_FLAG_PERSISTENT 0x8u /* one persistent kernel with grid barriers per run of phases instead of one
                                     kernel per phase (measured slower on B200; kept for comparison) */
 
@@ -104,6 +106,17 @@ lpp_status lpp_upload_tensor(lpp_engine* e, int which, int layer, const void* sr
 /* Checks that every tensor arrived, ties the classifier to the embedding if w_cls was never
  * uploaded (src/loader.cpp:66, 471, 619-632), captures the step graph. */
 lpp_status lpp_finalize(lpp_engine* e);
+
+/* Tensor parallelism over peer memory (one process per GPU, tp_size <= 8).  The reference all-reduces
+ * the partial o_proj / down results with ncclAllReduce (src/model.cpp:236, 243 under USE_NCCL); here the
+ * residual GEMV of every rank stores its rows straight into all ranks' receive areas over NVLink and the
+ * next GEMV adds the tp_size partial vectors in rank order while it stages its input.  Each rank
+ * exports an IPC handle of its receive buffer (LPP_TP_HANDLE_BYTES bytes), the caller gathers the
+ * handles of all ranks in rank order over its own host channel and hands them to every engine before
+ * lpp_finalize.  Without lpp_tp_connect (or with LPP_FLAG_TP_NCCL) the NCCL all-reduce is used. */
+#define LPP_TP_HANDLE_BYTES 64
+lpp_status lpp_tp_export(lpp_engine* e, void* handle, size_t handle_bytes);
+lpp_status lpp_tp_connect(lpp_engine* e, const void* handles, size_t handle_bytes_each);
 
 /* ---- the hot path ---------------------------------------------------------------------------- */
 

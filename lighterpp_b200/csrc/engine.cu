@@ -159,6 +159,12 @@ struct lpp_engine {
     unsigned int* gbar = nullptr;
     int n_gbar = 0;
     unsigned long long* trace = nullptr;  // LPP_STEP_TRACE: per-CTA per-phase time stamps
+    // tensor-parallel exchange over peer memory: per exchange (2 per layer) a receive area [tp][dim] floats
+    // and two counters; peer_base[p] = rank p's buffer as mapped into this process (own buffer for p == rank)
+    unsigned char* tp_buf = nullptr;
+    size_t tp_buf_bytes = 0;
+    unsigned char* peer_base[kMaxTp] = {};
+    bool peer_ready = false;
     unsigned long long* gtrace = nullptr;  // LPP_GEMV_TRACE: per-launch per-CTA time stamps of the ring GEMV
     int step_slots = 2, step_xs_bytes = 0;
     size_t step_smem = 0;
@@ -465,9 +471,12 @@ static void record_allreduce(Recorder& R, float* buf, int n) {
     R.prev_kernel = false;
 }
 
+static bool tp_peer_path(const lpp_engine* e);
+static unsigned int* tp_epoch_word(const lpp_engine* e);
+
 // The fused sampler: exact-order kernel by default, tree kernel when asked for or when the vocabulary
 // needs more blocks than can be co-resident.
-static cudaError_t launch_sampler(lpp_engine* e, cudaStream_t s, bool pdl, bool zero_gbar) {
+static cudaError_t launch_sampler(lpp_engine* e, cudaStream_t s, bool pdl, bool zero_gbar, bool end_of_step = false) {
     SampleArgs a = {};
     a.logits = e->logits;
     a.vocab = e->c.vocab_size;
@@ -480,6 +489,7 @@ static cudaError_t launch_sampler(lpp_engine* e, cudaStream_t s, bool pdl, bool 
     a.out_tokens = e->out_tokens;
     a.zero = zero_gbar ? e->gbar : nullptr;
     a.zero_n = zero_gbar ? e->n_gbar : 0;
+    a.bump = (end_of_step && tp_peer_path(e)) ? tp_epoch_word(e) : nullptr;
     if (e->exact_sampler) {
         SampleExactArgs ea = {};
         ea.base = a;
@@ -531,6 +541,51 @@ static void set_prefetch(const lpp_engine* e, GemvArgs& a, int kind, int l) {
     a.pf_bytes = (unsigned int)bytes;
 }
 
+// ---- tensor-parallel exchange buffer layout: [epoch word, padded to 256 B][2 * n_layers receive areas],
+//      a receive area = [tp][dim] 64-bit {value, flag} words
+static size_t tp_header_bytes() { return 1024; }  // epoch word at 0, hint counters (one per exchange) from byte 256
+static size_t tp_area_bytes(const lpp_engine* e) { return (size_t)e->c.tp_size * e->c.dim * sizeof(unsigned long long); }
+static unsigned long long* tp_area(const lpp_engine* e, int p, int ex) {
+    return reinterpret_cast<unsigned long long*>(e->peer_base[p] + tp_header_bytes() + (size_t)ex * tp_area_bytes(e));
+}
+static unsigned int* tp_epoch_word(const lpp_engine* e) { return reinterpret_cast<unsigned int*>(e->tp_buf); }
+static unsigned int* tp_hint(const lpp_engine* e, int p, int ex) { return reinterpret_cast<unsigned int*>(e->peer_base[p] + 256) + ex; }
+static unsigned int tp_hint_per_step(const lpp_engine* e) {
+    const int groups = e->c.dim / kRowsPerGroup;  // the producing GEMVs have dim rows
+    return (unsigned int)(e->c.tp_size * std::max(1, std::min(groups, e->num_sms)));
+}
+// (a single-kind timing run must not take part in exchanges: its producers would have no consumers)
+static bool tp_peer_path(const lpp_engine* e) {
+    return e->c.tp_size > 1 && e->peer_ready && !e->persistent && e->only_kind < 0 &&
+           !(e->c.flags & (LPP_FLAG_GEMV_LDG | LPP_FLAG_TP_NCCL));
+}
+// producer side: exchange `ex` takes the rows of this residual GEMV
+static void tp_set_producer(const lpp_engine* e, GemvArgs& a, int ex) {
+    const bool use_hint = 2 * e->c.n_layers <= 192 && !getenv("LPP_TP_NO_HINT");
+    a.tp_size = e->c.tp_size;
+    a.tp_epoch = tp_epoch_word(e);
+    for (int p = 0; p < e->c.tp_size; ++p) {
+        a.tp_out[p] = tp_area(e, p, ex) + (size_t)e->c.tp_rank * e->c.dim;
+        a.tp_hint_out[p] = use_hint ? tp_hint(e, p, ex) : nullptr;
+    }
+}
+// consumer side: this GEMV's input is the sum of the slots of exchange `ex`
+static void tp_set_consumer(const lpp_engine* e, GemvArgs& a, int ex, float* x_store) {
+    a.tp_size = e->c.tp_size;
+    a.tp_epoch = tp_epoch_word(e);
+    a.tp_in = tp_area(e, e->c.tp_rank, ex);
+    a.tp_hint_in = (2 * e->c.n_layers <= 192 && !getenv("LPP_TP_NO_HINT")) ? tp_hint(e, e->c.tp_rank, ex) : nullptr;
+    a.tp_hint_per_step = tp_hint_per_step(e);
+    a.x = nullptr;
+    a.x_store = x_store;
+}
+
+// Ends a step that has no sampler kernel: bumps the exchange epoch.
+static __global__ void tp_bump_kernel(unsigned int* epoch) {
+    pdl_wait();
+    *epoch = *epoch + 1u;
+}
+
 static void record_step(Recorder& R, bool with_sampler) {
     lpp_engine* e = R.e;
     const lpp_config& c = e->c;
@@ -538,6 +593,7 @@ static void record_step(Recorder& R, bool with_sampler) {
     const size_t esz = e->esz;
     const int qkv_rows = e->Dq + 2 * e->KVd;
     const bool tp = c.tp_size > 1;
+    const bool peers = tp_peer_path(e);  // fused exchange over peer memory instead of an NCCL all-reduce
     float* cur = e->xa;
     float* oth = e->xb;
     for (int l = 0; l < L; ++l) {
@@ -552,6 +608,7 @@ static void record_step(Recorder& R, bool with_sampler) {
                 a.x_store = cur;
             } else {
                 a.x = cur;
+                if (peers) tp_set_consumer(e, a, 2 * (l - 1) + 1, cur);  // the previous layer's down exchange
             }
             a.out = e->q;
             a.q_rows = e->Dq;
@@ -606,9 +663,10 @@ static void record_step(Recorder& R, bool with_sampler) {
             a.x = e->att_out;
             a.resid = (!tp || c.tp_rank == 0) ? cur : nullptr;
             a.out = tp ? oth : cur;
+            if (peers) tp_set_producer(e, a, 2 * l);
             set_prefetch(e, a, kOproj, l);
             record_gemv(R, kOproj, kEpiResid, a);
-            if (tp) {
+            if (tp && !peers) {
                 record_allreduce(R, oth, D);
                 std::swap(cur, oth);
             }
@@ -619,6 +677,7 @@ static void record_step(Recorder& R, bool with_sampler) {
             a.n_rows = 2 * e->Fl;
             a.K = D;
             a.x = cur;
+            if (peers) tp_set_consumer(e, a, 2 * l, cur);
             a.norm_w = e->rms_ffn + (size_t)l * D;
             a.out = e->hb;
             set_prefetch(e, a, kGateUp, l);
@@ -632,9 +691,10 @@ static void record_step(Recorder& R, bool with_sampler) {
             a.x = e->hb;
             a.resid = (!tp || c.tp_rank == 0) ? cur : nullptr;
             a.out = tp ? oth : cur;
+            if (peers) tp_set_producer(e, a, 2 * l + 1);
             set_prefetch(e, a, kDown, l);
             record_gemv(R, kDown, kEpiResid, a);
-            if (tp) {
+            if (tp && !peers) {
                 record_allreduce(R, oth, D);
                 std::swap(cur, oth);
             }
@@ -646,6 +706,7 @@ static void record_step(Recorder& R, bool with_sampler) {
         a.n_rows = c.vocab_size;
         a.K = D;
         a.x = cur;
+        if (peers) tp_set_consumer(e, a, 2 * (L - 1) + 1, cur);
         a.norm_w = e->rms_final;
         a.out = e->logits;
         set_prefetch(e, a, kLmHead, 0);
@@ -658,9 +719,14 @@ static void record_step(Recorder& R, bool with_sampler) {
         R.check(cudaMemsetAsync(e->gbar, 0, (size_t)e->n_gbar * sizeof(unsigned int), R.s), "gbar memset");
         R.prev_kernel = false;
     }
+    if (!with_sampler && tp_peer_path(e)) {
+        // no sampler in this graph to end the step: a one-thread kernel bumps the exchange epoch
+        R.check(launch_kernel(tp_bump_kernel, dim3(1), dim3(1), 0, R.s, R.pdl(), tp_epoch_word(e)), "epoch bump launch");
+        R.prev_kernel = true;
+    }
     if (with_sampler && !kind_skipped(e, kSampler)) {
         R.mark(kSampler);
-        R.check(launch_sampler(e, R.s, R.pdl(), e->persistent), "sampler launch");
+        R.check(launch_sampler(e, R.s, R.pdl(), e->persistent, true), "sampler launch");
         R.mark(-1);
         R.prev_kernel = true;
         R.kernels++;
@@ -854,6 +920,13 @@ extern "C" lpp_status lpp_engine_create(const lpp_config* cfg, const void* nccl_
         memcpy(&id, nccl_id, sizeof id);
         nccl::result_t r = nccl::CommInitRank(&e->comm, c.tp_size, id, c.tp_rank);
         if (r != 0) return bail(fail(LPP_ERR_NCCL, "ncclCommInitRank: %s", nccl::GetErrorString(r)));
+        if (c.tp_size <= kMaxTp) {
+            // receive areas and counters of the peer-memory exchange (used once lpp_tp_connect has mapped the peers)
+            e->tp_buf_bytes = tp_header_bytes() + (size_t)2 * c.n_layers * tp_area_bytes(e);
+            CUB(cudaMalloc(&e->tp_buf, e->tp_buf_bytes));
+            CUB(cudaMemset(e->tp_buf, 0, e->tp_buf_bytes));
+            e->peer_base[c.tp_rank] = e->tp_buf;
+        }
     }
     CUB(cudaStreamSynchronize(e->stream));
 #undef CUB
@@ -871,6 +944,9 @@ extern "C" lpp_status lpp_engine_destroy(lpp_engine* e) {
         if (e->g_logits[v]) cudaGraphExecDestroy(e->g_logits[v]);
     }
     if (e->comm) nccl::CommDestroy(e->comm);
+    for (int p = 0; p < kMaxTp; ++p)
+        if (e->peer_base[p] && p != e->c.tp_rank) cudaIpcCloseMemHandle(e->peer_base[p]);
+    if (e->tp_buf) cudaFree(e->tp_buf);
     void* bufs[] = {e->wqkv, e->wo, e->w13, e->w2, e->emb, e->wcls_owned ? e->wcls : nullptr, e->rms_att, e->rms_ffn,
                     e->rms_final, e->kcache, e->vcache, e->xa, e->xb, e->q, e->att_out, e->hb, e->logits,
                     e->attn_part, e->attn_counters, e->samp_max, e->samp_sum, e->samp_idx, e->samp_counter,
@@ -1228,6 +1304,43 @@ extern "C" lpp_status lpp_kv_read(lpp_engine* e, int layer, int kv_head, int pos
 
 // Timing aid (not part of the public header): copies the time stamps the step kernel left when the
 // engine was finalized with LPP_STEP_TRACE set; n_out = ctas * phases * 4 values.
+// ---- tensor-parallel peer mapping ---------------------------------------------------------------
+
+static_assert(sizeof(cudaIpcMemHandle_t) == LPP_TP_HANDLE_BYTES, "IPC handle size");
+
+extern "C" lpp_status lpp_tp_export(lpp_engine* e, void* handle, size_t handle_bytes) {
+    if (!e || !handle) return fail(LPP_ERR_INVALID_ARG, "null argument");
+    if (handle_bytes < sizeof(cudaIpcMemHandle_t)) return fail(LPP_ERR_INVALID_ARG, "handle buffer needs %zu bytes", sizeof(cudaIpcMemHandle_t));
+    if (!e->tp_buf) return fail(LPP_ERR_INVALID_ARG, "engine has no tensor-parallel exchange buffer (tp_size 1 or > %d)", kMaxTp);
+    CU(cudaSetDevice(e->c.device));
+    cudaIpcMemHandle_t h;
+    CU(cudaIpcGetMemHandle(&h, e->tp_buf));
+    memcpy(handle, &h, sizeof h);
+    return LPP_OK;
+}
+
+extern "C" lpp_status lpp_tp_connect(lpp_engine* e, const void* handles, size_t handle_bytes) {
+    if (!e || !handles) return fail(LPP_ERR_INVALID_ARG, "null argument");
+    if (handle_bytes < sizeof(cudaIpcMemHandle_t)) return fail(LPP_ERR_INVALID_ARG, "handles are %zu bytes each", sizeof(cudaIpcMemHandle_t));
+    if (!e->tp_buf) return fail(LPP_ERR_INVALID_ARG, "engine has no tensor-parallel exchange buffer");
+    if (e->finalized) return fail(LPP_ERR_INVALID_ARG, "lpp_tp_connect must precede lpp_finalize");
+    CU(cudaSetDevice(e->c.device));
+    for (int p = 0; p < e->c.tp_size; ++p) {
+        if (p == e->c.tp_rank || e->peer_base[p]) continue;
+        cudaIpcMemHandle_t h;
+        memcpy(&h, (const char*)handles + (size_t)p * handle_bytes, sizeof h);
+        void* ptr = nullptr;
+        cudaError_t r = cudaIpcOpenMemHandle(&ptr, h, cudaIpcMemLazyEnablePeerAccess);
+        if (r != cudaSuccess) {
+            (void)cudaGetLastError();
+            return fail(LPP_ERR_CUDA, "cudaIpcOpenMemHandle for rank %d: %s", p, cudaGetErrorString(r));
+        }
+        e->peer_base[p] = (unsigned char*)ptr;
+    }
+    e->peer_ready = true;
+    return LPP_OK;
+}
+
 // Debugging aid (not part of the public header): per-CTA time stamps of the ring GEMV launches of one step.
 extern "C" int lpp_debug_gemv_trace(lpp_engine* e, unsigned long long* out, int max_values) {
     if (!e || !e->gtrace || !out) return -1;

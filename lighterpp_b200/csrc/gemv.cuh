@@ -38,6 +38,8 @@ constexpr int kGemvMaxStages = 16;  // ring slots per consumer warp
 constexpr int kGemvBarrierBytes = 2 * kGemvConsumerWarps * kGemvMaxStages * 8;
 constexpr int kRowsPerGroup = 2;                           // rows handled together by one warp
 
+constexpr int kMaxTp = 8;  // ranks of a tensor-parallel group
+
 struct GemvArgs {
     const void* W;  // [n_rows][K] row-major, element type WT
     int n_rows, K;
@@ -68,6 +70,24 @@ struct GemvArgs {
     int debug;        // timing experiments only: 1 = consumers skip the arithmetic, 2 = producer skips the copies
     int xs_bytes;     // shared-memory bytes reserved for the staged input (0 = K floats rounded up to 128)
     unsigned long long* trace;  // timing experiments only: [CTA][8] global-timer stamps, nullptr = none
+    // ---- tensor-parallel exchange over peer memory (tp_size <= 1 or null pointers = not used).
+    // Every result travels as one 64-bit word {value, flag}, flag = the step's epoch + 1, so a word is
+    // either old or complete and no fence or counter is needed.  Residual epilogue: every rank stores its
+    // partial rows into slot `rank` of the exchange's receive area on EVERY rank (plain peer stores over
+    // NVLink).  Prologue of the next GEMV: polls the tp_size slots of its own receive area until the
+    // words carry this step's flag and adds them in rank order, so all ranks go on with bit-identical
+    // activations.  The epoch word is local to each rank and bumped once at the end of every step.
+    unsigned long long* tp_out[kMaxTp];  // this rank's slot [n_rows] in rank p's receive area
+    const unsigned long long* tp_in;     // local receive area [tp_size][K] of the exchange that produced the input
+    const unsigned int* tp_epoch;        // local epoch word
+    int tp_size;
+    // Arrival hint: every CTA of a producing GEMV bumps (relaxed, unordered with the data) one counter per
+    // rank and exchange when its rows are out, so that a consumer can sleep on a single word instead of
+    // having all its threads poll the receive area; the flags in the data words stay the only proof of
+    // arrival.  Counters only grow: an exchange is probably complete at (epoch + 1) * tp_hint_per_step.
+    unsigned int* tp_hint_out[kMaxTp];   // rank p's hint counter of the exchange this GEMV produces
+    const unsigned int* tp_hint_in;      // local hint counter of the exchange this GEMV consumes
+    unsigned int tp_hint_per_step;       // tp_size * CTAs of the producing GEMV
 };
 
 // ------------------------------------------------------------------ x staging layouts
@@ -107,6 +127,124 @@ __device__ __forceinline__ void xs_store4(float* xs, int k, int K, float4 v) {
         *reinterpret_cast<float4*>(xs + k) = v;
 }
 
+// The ranks of a tensor-parallel group are separate processes whose launches may be skewed by host-side
+// delays, so the limit of a wait on a peer is long (seconds); once it has run out on this engine no
+// later poll waits.
+constexpr long long kTpWaitCycles = 8ll * 1000 * 1000 * 1000;
+
+// Address of the float4 holding inputs k..k+3 (k % 4 == 0) in the staging layout.
+template <typename WT>
+__device__ __forceinline__ float4* xs_ptr4(float* xs, int k, int K) {
+    if constexpr (sizeof(WT) == 2)
+        return reinterpret_cast<float4*>(xs + ((k >> 3) << 2) + ((k & 4) ? (K >> 1) : 0));
+    else
+        return reinterpret_cast<float4*>(xs + k);
+}
+
+// Input staging when the input vector arrives through the tensor-parallel exchange: the sum, in rank
+// order, of the tp_size slots of the local receive area.  All words a thread needs from two ranks are
+// requested together and only then checked for the step's flag (a failed check repeats the batch), so a
+// slot costs one round trip to L2, not one per element.
+template <typename WT, int NT>
+__device__ __forceinline__ void stage_input_peers(const GemvArgs& a, float* xs, float* red, int tid) {
+    const int K = a.K, nv4 = K >> 2;
+    const unsigned int flag = *a.tp_epoch + 1u;
+    if (a.tp_hint_in) {
+        // one thread sleeps on the hint counter (a few seconds at most, then the data poll decides)
+        if (tid == 0) {
+            const unsigned int want = flag * a.tp_hint_per_step;
+            const long long t0 = clock64();
+            while (true) {
+                unsigned int v;
+                asm volatile("ld.volatile.global.u32 %0, [%1];" : "=r"(v) : "l"(a.tp_hint_in) : "memory");
+                if ((int)(v - want) >= 0 || clock64() - t0 > kTpWaitCycles) break;
+                __nanosleep(20);
+            }
+        }
+        consumer_barrier(NT);
+    }
+    if (tid == 0) gemv_stamp(a, 1);
+    constexpr int kPer = 4, kRanks = 2;
+    const bool store = a.x_store && blockIdx.x == 0;
+    float ss = 0.f;
+    for (int base = 0; base < nv4; base += kPer * NT) {
+        float4 sum[kPer];
+        for (int r0 = 0; r0 < a.tp_size; r0 += kRanks) {
+            unsigned long long w[kRanks][kPer][4];
+            long long t0 = 0;
+            while (true) {
+#pragma unroll
+                for (int rr = 0; rr < kRanks; ++rr)
+#pragma unroll
+                    for (int j = 0; j < kPer; ++j) {
+                        const int i = base + tid + j * NT;
+                        if (r0 + rr < a.tp_size && i < nv4) {
+                            const unsigned long long* p = a.tp_in + (size_t)(r0 + rr) * K + ((size_t)i << 2);
+                            asm volatile("ld.volatile.global.v2.u64 {%0,%1}, [%2];" : "=l"(w[rr][j][0]), "=l"(w[rr][j][1]) : "l"(p) : "memory");
+                            asm volatile("ld.volatile.global.v2.u64 {%0,%1}, [%2];" : "=l"(w[rr][j][2]), "=l"(w[rr][j][3]) : "l"(p + 2) : "memory");
+                        }
+                    }
+                bool pending = false;
+#pragma unroll
+                for (int rr = 0; rr < kRanks; ++rr)
+#pragma unroll
+                    for (int j = 0; j < kPer; ++j)
+                        if (r0 + rr < a.tp_size && base + tid + j * NT < nv4)
+#pragma unroll
+                            for (int q = 0; q < 4; ++q) pending |= (unsigned int)(w[rr][j][q] >> 32) != flag;
+                if (!pending) break;
+                if (t0 == 0) {
+                    if (*reinterpret_cast<volatile int*>(&a.st->status) & kStatusBarrierTimeout) break;
+                    t0 = clock64();
+                } else if (clock64() - t0 > kTpWaitCycles) {
+                    atomicOr(&a.st->status, kStatusBarrierTimeout);
+                    break;
+                }
+                __nanosleep(20);
+            }
+#pragma unroll
+            for (int rr = 0; rr < kRanks; ++rr)
+#pragma unroll
+                for (int j = 0; j < kPer; ++j)
+                    if (r0 + rr < a.tp_size && base + tid + j * NT < nv4) {
+                        const float4 u = make_float4(__uint_as_float((unsigned int)w[rr][j][0]), __uint_as_float((unsigned int)w[rr][j][1]),
+                                                     __uint_as_float((unsigned int)w[rr][j][2]), __uint_as_float((unsigned int)w[rr][j][3]));
+                        if (r0 + rr == 0) {
+                            sum[j] = u;
+                        } else {
+                            sum[j].x = __fadd_rn(sum[j].x, u.x); sum[j].y = __fadd_rn(sum[j].y, u.y);
+                            sum[j].z = __fadd_rn(sum[j].z, u.z); sum[j].w = __fadd_rn(sum[j].w, u.w);
+                        }
+                    }
+        }
+#pragma unroll
+        for (int j = 0; j < kPer; ++j) {
+            const int i = base + tid + j * NT;
+            if (i < nv4) {
+                ss = fmaf(sum[j].x, sum[j].x, fmaf(sum[j].y, sum[j].y, fmaf(sum[j].z, sum[j].z, fmaf(sum[j].w, sum[j].w, ss))));
+                *xs_ptr4<WT>(xs, i << 2, K) = sum[j];
+                if (store) reinterpret_cast<float4*>(a.x_store)[i] = sum[j];  // the residual stream
+            }
+        }
+    }
+    if (a.norm_w) {
+        ss = warp_sum(ss);
+        if ((tid & 31) == 0) red[tid >> 5] = ss;
+        consumer_barrier(NT);
+        float tot = 0.f;
+#pragma unroll
+        for (int w = 0; w < NT / 32; ++w) tot += red[w];
+        const float scale = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(tot, (float)K), 1e-5f)));
+        for (int i = tid; i < nv4; i += NT) {  // the elements this thread staged itself
+            float4* p = xs_ptr4<WT>(xs, i << 2, K);
+            const float4 v = *p, g = __ldg(reinterpret_cast<const float4*>(a.norm_w) + i);
+            *p = make_float4(__fmul_rn(__fmul_rn(v.x, scale), g.x), __fmul_rn(__fmul_rn(v.y, scale), g.y),
+                             __fmul_rn(__fmul_rn(v.z, scale), g.z), __fmul_rn(__fmul_rn(v.w, scale), g.w));
+        }
+    }
+    consumer_barrier(NT);
+}
+
 // Waits for the producing kernel, loads the input vector (embedding row or x), optionally
 // RMS-normalises it (ss = 1/sqrt(mean(x^2) + 1e-5); out = x*ss*w, src/ops.cpp:20-32) and leaves it
 // in shared memory in the layout xs_index<WT> describes.  Executed by `NT` threads (tid 0..NT-1).
@@ -124,6 +262,14 @@ __device__ __forceinline__ void stage_input(const GemvArgs& a, float* xs, float*
             const int i = tid + j * NT;
             if (i < nv4) wr[j] = __ldg(reinterpret_cast<const float4*>(a.norm_w) + i);
         }
+    }
+    // An input that arrives through the tensor-parallel exchange validates itself word by word (this
+    // rank's own slot included): its flags can only be complete once every rank's producing GEMV has
+    // stored all its rows, which in turn follows everything earlier in the step, so that case does not
+    // wait for the local kernel to drain its peer stores and exit.
+    if (a.tp_in != nullptr && a.tp_size > 1) {
+        stage_input_peers<WT, NT>(a, xs, red, tid);
+        return;
     }
     pdl_wait();  // activations / KV / step state come from the previous kernel
     if (tid == 0) gemv_stamp(a, 1);
@@ -166,8 +312,9 @@ __device__ __forceinline__ void stage_input(const GemvArgs& a, float* xs, float*
     }
 
     const float4* x4 = reinterpret_cast<const float4*>(a.x);
+    auto load_x4 = [&](int i) -> float4 { return __ldcg(x4 + i); };
     if (!a.norm_w) {
-        for (int i = tid; i < nv4; i += NT) xs_store4<WT>(xs, i << 2, K, __ldcg(x4 + i));
+        for (int i = tid; i < nv4; i += NT) xs_store4<WT>(xs, i << 2, K, load_x4(i));
         consumer_barrier(NT);
         return;
     }
@@ -177,7 +324,7 @@ __device__ __forceinline__ void stage_input(const GemvArgs& a, float* xs, float*
 #pragma unroll
         for (int j = 0; j < kPer; ++j) {
             const int i = tid + j * NT;
-            if (i < nv4) xr[j] = __ldcg(x4 + i);
+            if (i < nv4) xr[j] = load_x4(i);
         }
 #pragma unroll
         for (int j = 0; j < kPer; ++j) {
@@ -186,7 +333,7 @@ __device__ __forceinline__ void stage_input(const GemvArgs& a, float* xs, float*
         }
     } else {
         for (int i = tid; i < nv4; i += NT) {
-            const float4 v = __ldcg(x4 + i);
+            const float4 v = load_x4(i);
             ss = fmaf(v.x, v.x, fmaf(v.y, v.y, fmaf(v.z, v.z, fmaf(v.w, v.w, ss))));
         }
     }
@@ -209,7 +356,7 @@ __device__ __forceinline__ void stage_input(const GemvArgs& a, float* xs, float*
         }
     } else {
         for (int i = tid; i < nv4; i += NT)
-            xs_store4<WT>(xs, i << 2, K, normed(__ldcg(x4 + i), __ldg(reinterpret_cast<const float4*>(a.norm_w) + i)));
+            xs_store4<WT>(xs, i << 2, K, normed(load_x4(i), __ldg(reinterpret_cast<const float4*>(a.norm_w) + i)));
     }
     consumer_barrier(NT);
 }
@@ -288,6 +435,21 @@ __device__ __forceinline__ void dot_rows(const unsigned char* row0, const unsign
     if constexpr (NR == 2) acc1 += a1 + b1;
 }
 
+// Residual epilogue store: locally, or as {value, flag} words into this rank's slot on every rank of the
+// tensor-parallel group.
+__device__ __forceinline__ void store_resid_rows(const GemvArgs& a, int row, float v0, float v1) {
+    if (a.tp_size > 1 && a.tp_out[0]) {
+        const unsigned long long flag = (unsigned long long)(*a.tp_epoch + 1u) << 32;
+        const unsigned long long w0 = flag | __float_as_uint(v0), w1 = flag | __float_as_uint(v1);
+#pragma unroll
+        for (int p = 0; p < kMaxTp; ++p)
+            if (p < a.tp_size)
+                asm volatile("st.volatile.global.v2.u64 [%0], {%1,%2};" ::"l"(a.tp_out[p] + row), "l"(w0), "l"(w1) : "memory");
+    } else {
+        *reinterpret_cast<float2*>(a.out + row) = make_float2(v0, v1);
+    }
+}
+
 // Writes the results of row pair `g` (rows 2g, 2g+1); called by one lane with the warp-reduced sums.
 template <int EPI>
 __device__ __forceinline__ void gemv_epilogue(const GemvArgs& a, int g, float v0, float v1) {
@@ -301,7 +463,7 @@ __device__ __forceinline__ void gemv_epilogue(const GemvArgs& a, int g, float v0
             v0 += r.x;
             v1 += r.y;
         }
-        *reinterpret_cast<float2*>(a.out + row) = make_float2(v0, v1);
+        store_resid_rows(a, row, v0, v1);
     } else if constexpr (EPI == kEpiSwiglu) {
         // rows are interleaved (gate_i, up_i); hb = (h1*sigmoid(h1))*h3 (src/ops.cpp:78-87)
         const float sig = __fdiv_rn(1.0f, 1.0f + expf(-v0));
@@ -496,8 +658,7 @@ __device__ __forceinline__ bool gemv_ring_body(const GemvArgs& a, unsigned char*
                 acc1 = warp_sum(acc1);
                 if (lane == 0) {
                     if (EPI == kEpiResid && p + i == p0)
-                        *reinterpret_cast<float2*>(a.out + (size_t)p0 * kRowsPerGroup) =
-                            make_float2(acc0 + r_first.x, acc1 + r_first.y);
+                        store_resid_rows(a, p0 * kRowsPerGroup, acc0 + r_first.x, acc1 + r_first.y);
                     else
                         gemv_epilogue<EPI>(a, p + i, acc0, acc1);
                 }
@@ -525,7 +686,7 @@ __device__ __forceinline__ bool gemv_ring_body(const GemvArgs& a, unsigned char*
             const float v0 = warp_sum(acc[0]), v1 = warp_sum(acc[1]);
             if (lane == 0) {
                 if (EPI == kEpiResid && p == p0)
-                    *reinterpret_cast<float2*>(a.out + (size_t)p0 * kRowsPerGroup) = make_float2(v0 + r_first.x, v1 + r_first.y);
+                    store_resid_rows(a, p0 * kRowsPerGroup, v0 + r_first.x, v1 + r_first.y);
                 else
                     gemv_epilogue<EPI>(a, p, v0, v1);
             }
@@ -539,7 +700,16 @@ __device__ __forceinline__ bool gemv_ring_body(const GemvArgs& a, unsigned char*
 template <typename WT, int EPI>
 __global__ void __launch_bounds__(kGemvRingThreads) gemv_ring_kernel(const GemvArgs a) {
     extern __shared__ __align__(128) unsigned char smem[];
-    gemv_ring_body<WT, EPI>(a, smem);
+    const bool consumer = gemv_ring_body<WT, EPI>(a, smem);
+    if constexpr (EPI == kEpiResid) {
+        // tensor-parallel exchange: this CTA's rows are on their way, tell every rank (a hint, see GemvArgs)
+        if (consumer && a.tp_size > 1 && a.tp_hint_out[0]) {
+            consumer_barrier(kGemvConsumerWarps * 32);
+            if (threadIdx.x == 0) gemv_stamp(a, 7);
+            if ((int)threadIdx.x < a.tp_size)
+                asm volatile("red.relaxed.sys.global.add.u32 [%0], 1;" ::"l"(a.tp_hint_out[threadIdx.x]) : "memory");
+        }
+    }
 }
 
 // ------------------------------------------------------------------ direct-load variant

@@ -38,6 +38,7 @@ struct SampleArgs {
     int* out_tokens;        // free-running mode: sampled token per step
     unsigned int* zero;     // counters to clear once the step is over (grid-barrier tickets), may be null
     int zero_n;
+    unsigned int* bump;     // word to increment once the step is over (tensor-parallel exchange epoch), may be null
 };
 
 struct MaxIdx {
@@ -246,6 +247,7 @@ static __global__ void __launch_bounds__(kSampleThreads) sample_kernel(const Sam
     }
     // every kernel of this step has completed: reset the step kernels' grid-barrier counters
     for (int i = tid; i < a.zero_n; i += kSampleThreads) a.zero[i] = 0u;
+    if (a.bump && tid == 0) *a.bump = *a.bump + 1u;
 }
 
 }  // namespace lpp

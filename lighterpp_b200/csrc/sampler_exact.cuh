@@ -714,6 +714,7 @@ static __global__ void __launch_bounds__(kSampleThreads) sample_exact_kernel(con
             ea.sync[1] = 0u;
         }
         for (int i = tid; i < a.zero_n; i += kSampleThreads) a.zero[i] = 0u;
+        if (a.bump && tid == 0) *a.bump = *a.bump + 1u;
     }
 }
 

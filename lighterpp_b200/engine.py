@@ -24,6 +24,8 @@ FLAG_GEMV_LDG, FLAG_NO_PDL, FLAG_NO_GRAPH, FLAG_PERSISTENT, FLAG_FAST_SAMPLER = 
 TENSOR_IDS = {"tok_emb": 0, "rms_att": 1, "wq": 2, "wk": 3, "wv": 4, "wo": 5, "rms_ffn": 6, "w1": 7, "w2": 8,
               "w3": 9, "rms_final": 10, "w_cls": 11}
 _UNSTACKED = ("tok_emb", "rms_final", "w_cls")
+TP_HANDLE_BYTES = 64
+FLAG_TP_NCCL = 32
 KINDS = ["qkv_gemv", "attention", "oproj_gemv", "gateup_gemv", "down_gemv", "lmhead_gemv", "sampler", "allreduce",
          "step_kernel", "reserved"]
 
@@ -32,7 +34,7 @@ EXPORTS = [
     "lpp_engine_create", "lpp_engine_destroy", "lpp_nccl_unique_id", "lpp_upload_tensor", "lpp_finalize",
     "lpp_step", "lpp_step_logits", "lpp_decode", "lpp_sample_logits", "lpp_kv_prefill", "lpp_kv_read",
     "lpp_kv_index", "lpp_strerror", "lpp_last_error", "lpp_engine_stream", "lpp_kernels_per_step",
-    "lpp_step_bytes", "lpp_profile_step", "lpp_profile_kind", "lpp_op_convert_f32_to_f16", "lpp_op_gemv", "lpp_op_rmsnorm",
+    "lpp_step_bytes", "lpp_profile_step", "lpp_profile_kind", "lpp_tp_export", "lpp_tp_connect", "lpp_op_convert_f32_to_f16", "lpp_op_gemv", "lpp_op_rmsnorm",
     "lpp_op_rope", "lpp_op_swiglu", "lpp_op_softmax_multihead", "lpp_op_scale_multihead",
     "lpp_op_aggregation_multihead", "lpp_op_residual_add", "lpp_op_scatter_kv", "lpp_op_multihead_gemv",
     "lpp_op_rope_scatter", "lpp_op_sample", "lpp_op_sample_static",
@@ -95,6 +97,8 @@ def load_library() -> C.CDLL:
     lib.lpp_step_bytes.restype = C.c_int64
     lib.lpp_profile_step.argtypes = [vp, C.c_int, C.c_int, fp, ip, C.POINTER(C.c_int64)]
     lib.lpp_profile_kind.argtypes = [vp, C.c_int, C.c_int, C.c_int, fp, ip]
+    lib.lpp_tp_export.argtypes = [vp, vp, C.c_size_t]
+    lib.lpp_tp_connect.argtypes = [vp, vp, C.c_size_t]
     _lib = lib
     return lib
 
@@ -261,6 +265,19 @@ class Engine:
         b = (C.c_int64 * 10)()
         _check(self.lib.lpp_profile_step(self.h, int(pos), int(iters), ms, n, b), "lpp_profile_step")
         return {KINDS[i]: {"ms": float(ms[i]), "launches": int(n[i]), "bytes": int(b[i])} for i in range(10)}
+
+    def tp_export(self) -> bytes:
+        """IPC handle of this rank's exchange buffer (to be gathered over the caller's host channel)."""
+        buf = C.create_string_buffer(TP_HANDLE_BYTES)
+        _check(self.lib.lpp_tp_export(self.h, buf, TP_HANDLE_BYTES), "lpp_tp_export")
+        return buf.raw
+
+    def tp_connect(self, handles: Sequence[bytes]) -> None:
+        """Maps every rank's exchange buffer (handles in rank order); call before the weights are finalized."""
+        if len(handles) != self.tp_size or any(len(h) != TP_HANDLE_BYTES for h in handles):
+            raise ValueError("need one %d-byte handle per rank, in rank order" % TP_HANDLE_BYTES)
+        blob = C.create_string_buffer(b"".join(handles), TP_HANDLE_BYTES * self.tp_size)
+        _check(self.lib.lpp_tp_connect(self.h, blob, TP_HANDLE_BYTES), "lpp_tp_connect")
 
     def profile_kind(self, pos: int, kind: str, iters: int = 5) -> Dict[str, float]:
         """Average launch duration of one kernel kind, its launches of a step run back to back."""

@@ -288,14 +288,21 @@ def test_error_statuses(E):
 
 
 def test_two_gpu_tensor_parallel(E, oracle, tmp_path):
-    """TP=2 over NCCL (needs two GPUs): both ranks reproduce the oracle logits and the same token."""
-    import subprocess, sys, os, torch
+    """TP=2 (needs two GPUs): both ranks reproduce the oracle logits and sample the same tokens, with the
+    exchange fused into the GEMVs over peer memory and with the NCCL all-reduce; both give the same ids."""
+    import subprocess, sys, os, re, torch
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
     script = os.path.join(root, "tests", "tp_worker.py")
-    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
-                        "--master-addr", "127.0.0.1", "--master-port", "29611", script, "tiny-tp8-f16"],
-                       capture_output=True, text=True, timeout=600, env={**os.environ, "NCCL_NVLS_ENABLE": "0"})
-    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
-    assert "TP_OK" in r.stdout
+    tokens = {}
+    for mode, port in (("peer", "29611"), ("nccl", "29612")):
+        r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
+                            "--master-addr", "127.0.0.1", "--master-port", port, script, "tiny-tp8-f16", mode],
+                           capture_output=True, text=True, timeout=600, env={**os.environ, "NCCL_NVLS_ENABLE": "0"})
+        assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+        m = re.search(r"TP_OK world=2 mode=%s .*tokens=(\[.*\])" % mode, r.stdout)
+        assert m, r.stdout[-2000:]
+        tokens[mode] = m.group(1)
+    # both paths add the partial vectors in rank order (NCCL's ring for two ranks does the same)
+    assert tokens["peer"] == tokens["nccl"]

@@ -21,7 +21,14 @@ def main():
     dist.broadcast_object_list(ids, src=0)
     name = sys.argv[1]
     c, dt, tied, seed, T = synth.named(name)
-    eng = E.Engine(c, dt, "f16", device=local, tp_rank=rank, tp_size=world, nccl_id=ids[0])
+    mode = sys.argv[2] if len(sys.argv) > 2 else "peer"
+    eng = E.Engine(c, dt, "f16", device=local, tp_rank=rank, tp_size=world, nccl_id=ids[0],
+                   flags=E.FLAG_TP_NCCL if mode == "nccl" else 0)
+    if mode == "peer":
+        # the exchange fused into the residual GEMVs: every rank maps every rank's receive buffer
+        handles = [None] * world
+        dist.all_gather_object(handles, eng.tp_export())
+        eng.tp_connect(handles)
     eng.load_weights(T)  # full tensors in, this rank's share kept
     m = Oracle().model(c, synth.as_f32(T))
     toks = synth.prompt_tokens(c.vocab_size, 8, seed)
@@ -37,7 +44,7 @@ def main():
     assert all(g == gathered[0] for g in gathered), gathered
     dist.barrier()
     if rank == 0:
-        print(f"TP_OK world={world} worst={worst:.2e}")
+        print(f"TP_OK world={world} mode={mode} worst={worst:.2e} tokens={out.tolist()}")
     eng.close()
     dist.destroy_process_group()
 
