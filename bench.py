@@ -102,6 +102,38 @@ def gen_device_weights(cfg, dtype, tied, seed, layers=None):
             yield name, l, t
 
 
+def tp1_same_workload(args, cfg, dtype, tied, seed, local, n_prompt, temp, pen):
+    """tok/s of the N>1 workload on one GPU: same prompt handling, a shorter timed region."""
+    import torch
+    from lighterpp_b200 import engine as E, synth
+    steps = max(16, min(args.steps, 64))
+    eng = E.Engine(cfg, dtype, "f16" if dtype == "f16" else "f32", device=local, flags=args.flags & ~E.FLAG_TP_NCCL,
+                   ring_kb=args.ring_kb)
+    for name, l, t in gen_device_weights(cfg, dtype, tied, seed):
+        eng.upload(name, t, max(l, 0))
+    eng.finalize()
+    torch.cuda.empty_cache()
+    prompt = synth.prompt_tokens(cfg.vocab_size, n_prompt, seed)
+    rs = np.random.default_rng(seed).random(8 + steps).astype(np.float32)
+    hist = []
+    for pos, t in enumerate(prompt[:-1]):
+        hist = (hist + [int(t)])[-64:]
+        eng.forward(int(t), pos, temp, 1.1, hist, 0.5)
+    tok, pos = int(prompt[-1]), n_prompt - 1
+    hist = (hist + [tok])[-64:]
+    out, _ = eng.decode(tok, pos, 8, temp, pen, hist, 64, rs[:8])
+    hist = (hist + [int(x) for x in out])[-64:]
+    tok, pos = int(out[-1]), pos + 8
+    torch.cuda.synchronize()
+    out, dev_ms = eng.decode(tok, pos, steps, temp, pen, hist, 64, rs[8:8 + steps])
+    torch.cuda.synchronize()
+    bytes_per_step = float(np.mean([eng.step_bytes(p) for p in range(pos, pos + steps)]))
+    eng.close()
+    us = dev_ms * 1e3 / steps
+    return {"value": round(steps / (dev_ms / 1e3), 2), "unit": "tok/s", "n_gpus": 1, "steps": steps,
+            "ms_per_step": round(dev_ms / steps, 5), "achieved_gbs": round(bytes_per_step / us / 1e3, 1)}
+
+
 def run_ours(args, rank, world):
     import torch
     import torch.distributed as dist
@@ -240,9 +272,17 @@ def run_ours(args, rank, world):
                             "gbs": round(v["bytes"] / v["ms"] / 1e6, 1) if v["ms"] else None}
                         for k, v in prof.items() if v["launches"]},
         }
-        if world > 1 and not args.no_tp1:
-            line["tp1_baseline"] = "run `bench.py --gpus 1 --workload %s` for the single-GPU number of this shape" % args.workload
     eng.close()
+    if world > 1 and not args.no_tp1:
+        # the same workload on ONE GPU (rank 0 alone, the other ranks wait): the number the sharded run is a
+        # speed-up over.  N=1 of the default run is a different, smaller shape.
+        torch.cuda.empty_cache()
+        if rank == 0:
+            try:
+                line["tp1_same_workload"] = tp1_same_workload(args, cfg, dtype, tied, seed, local, n_prompt, temp, pen)
+            except Exception as ex:  # e.g. a shape that does not fit one GPU
+                line["tp1_same_workload"] = {"unavailable": str(ex)[:200]}
+        dist.barrier()
     if rank == 0 and host_copy is not None:
         W = {k: (np.stack(v) if len(v) > 1 or k in ("rms_att", "rms_ffn", "wq") else v[0]) for k, v in host_copy.items()}
         line["cpu_baseline"] = cpu_baseline(cfg, W, prompt, temp, pen, budget_s=args.cpu_seconds)
