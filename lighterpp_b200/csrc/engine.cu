@@ -529,10 +529,6 @@ static void set_prefetch(const lpp_engine* e, GemvArgs& a, int kind, int l) {
     }
     size_t cap = 8;
     if (const char* v = getenv("LPP_PF_MB")) cap = (size_t)std::max(0, atoi(v));
-    if (kind == kOproj)
-        if (const char* v = getenv("LPP_PF_OPROJ_MB")) cap = (size_t)std::max(0, atoi(v));
-    if (kind == kQkv)
-        if (const char* v = getenv("LPP_PF_QKV_MB")) cap = (size_t)std::max(0, atoi(v));
     const void* p;
     size_t bytes;
     matrix_span(e, nk, nl, &p, &bytes);

@@ -522,11 +522,21 @@ __device__ __forceinline__ bool gemv_ring_body(const GemvArgs& a, unsigned char*
     const int g1 = (int)(((long long)(blockIdx.x + 1) * groups) / gridDim.x);
     const int ng = g1 - g0;
     const int w = (warp == kGemvConsumerWarps) ? lane : warp;  // pipeline index
-    const int p0 = g0 + (w < kGemvConsumerWarps ? (ng * w) / kGemvConsumerWarps : 0);
-    const int p1 = g0 + (w < kGemvConsumerWarps ? (ng * (w + 1)) / kGemvConsumerWarps : 0);
+    int p0 = g0 + (w < kGemvConsumerWarps ? (ng * w) / kGemvConsumerWarps : 0);
+    int p1 = g0 + (w < kGemvConsumerWarps ? (ng * (w + 1)) / kGemvConsumerWarps : 0);
     const size_t row_bytes = (size_t)a.K * sizeof(WT);
     const int m = a.pairs_per_stage;
     const int nch = m > 0 ? 1 : (a.K + a.kc - 1) / a.kc;
+    // pairs advance by `pstep` from p0 to p1.  Timing experiment (debug bit 16): stages are dealt round
+    // robin over all warps of the grid, so that all SMs sweep the matrix front to back together.
+    int pstep = m > 0 ? m : 1;
+    if ((a.debug & 16) && w < kGemvConsumerWarps) {
+        p0 = (w * (int)gridDim.x + (int)blockIdx.x) * pstep;
+        p1 = groups;
+        pstep *= kGemvConsumerWarps * (int)gridDim.x;
+        if (p0 > p1) p0 = p1;
+    }
+    const int unit = m > 0 ? m : 1;
 
     if (tid == 0) gemv_stamp(a, 0);
     // The dependent kernel is released for launch at once: its CTAs take over an SM as soon as one of
@@ -551,6 +561,7 @@ __device__ __forceinline__ bool gemv_ring_body(const GemvArgs& a, unsigned char*
             unsigned char* myring = ring + (size_t)w * NS * a.stage_bytes;
             int slot = 0, pass = 0;  // pass = completed trips around the ring
             bool alive = true;
+            const unsigned long long policy = (a.debug & 8) ? l2_policy_evict_first() : 0ull;
             auto issue = [&](const unsigned char* src, uint32_t bytes) -> bool {
                 // trip p > 0 reuses a slot once its release number p-1 has happened
                 if (pass > 0 && !mbar_wait_bounded(&myempty[slot], (uint32_t)(pass - 1) & 1u, &a.st->status))
@@ -559,7 +570,10 @@ __device__ __forceinline__ bool gemv_ring_body(const GemvArgs& a, unsigned char*
                     mbar_arrive(&myfull[slot]);
                 } else {
                     mbar_arrive_expect_tx(&myfull[slot], bytes);
-                    bulk_g2s(myring + (size_t)slot * a.stage_bytes, src, bytes, &myfull[slot]);
+                    if (a.debug & 8)
+                        bulk_g2s_hint(myring + (size_t)slot * a.stage_bytes, src, bytes, &myfull[slot], policy);
+                    else
+                        bulk_g2s(myring + (size_t)slot * a.stage_bytes, src, bytes, &myfull[slot]);
                 }
                 if (++slot == NS) {
                     slot = 0;
@@ -569,12 +583,12 @@ __device__ __forceinline__ bool gemv_ring_body(const GemvArgs& a, unsigned char*
             };
             if (lane == 0) gemv_stamp(a, 5);
             if (m > 0) {
-                for (int p = p0; p < p1 && alive; p += m) {
-                    const int cnt = min(m, p1 - p);
+                for (int p = p0; p < p1 && alive; p += pstep) {
+                    const int cnt = min(unit, p1 - p);
                     alive = issue(W + (size_t)p * kRowsPerGroup * row_bytes, (uint32_t)(cnt * kRowsPerGroup * row_bytes));
                 }
             } else {
-                for (int p = p0; p < p1 && alive; ++p)
+                for (int p = p0; p < p1 && alive; p += pstep)
                     for (int r = 0; r < kRowsPerGroup && alive; ++r)
                         for (int c = 0; c < nch && alive; ++c) {
                             const int k0 = c * a.kc;
@@ -642,8 +656,8 @@ __device__ __forceinline__ bool gemv_ring_body(const GemvArgs& a, unsigned char*
     if (EPI == kEpiResid && a.resid && lane == 0 && p0 < p1)
         r_first = __ldcg(reinterpret_cast<const float2*>(a.resid + (size_t)p0 * kRowsPerGroup));
     if (m > 0) {
-        for (int p = p0; p < p1 && ok; p += m) {
-            const int cnt = min(m, p1 - p);
+        for (int p = p0; p < p1 && ok; p += pstep) {
+            const int cnt = min(unit, p1 - p);
             if (!acquire()) {
                 ok = false;
                 break;
@@ -666,7 +680,7 @@ __device__ __forceinline__ bool gemv_ring_body(const GemvArgs& a, unsigned char*
             release();
         }
     } else {
-        for (int p = p0; p < p1 && ok; ++p) {
+        for (int p = p0; p < p1 && ok; p += pstep) {
             float acc[kRowsPerGroup] = {0.f, 0.f};
 #pragma unroll
             for (int r = 0; r < kRowsPerGroup; ++r)
