@@ -152,11 +152,33 @@ def run_ours(args, rank, world):
         nccl_id = ids[0]
     eng = E.Engine(cfg, dtype, "f16" if dtype == "f16" else "f32", device=local, tp_rank=rank, tp_size=world,
                    nccl_id=nccl_id, flags=args.flags, ring_kb=args.ring_kb)
+    tp_exchange = "none" if world == 1 else "nccl all-reduce"
     if world > 1 and not (args.flags & E.FLAG_TP_NCCL):
-        # the o_proj / down exchange fused into the GEMVs over peer memory: map every rank's receive buffer
+        # the o_proj / down exchange fused into the GEMVs over peer memory: map every rank's receive buffer.
+        # If any rank cannot map its peers, every rank stays on the NCCL all-reduce.
         handles = [None] * world
-        dist.all_gather_object(handles, eng.tp_export())
-        eng.tp_connect(handles)
+        try:
+            mine = eng.tp_export()
+        except E.LppError:
+            mine = None
+        dist.all_gather_object(handles, mine)
+        ok = all(h is not None for h in handles)
+        if ok:
+            try:
+                eng.tp_connect(handles)
+            except E.LppError:
+                ok = False
+        oks = [None] * world
+        dist.all_gather_object(oks, ok)
+        if all(oks):
+            tp_exchange = "fused into the GEMVs over peer memory"
+        else:
+            eng.close()
+            ids = [E.nccl_unique_id() if rank == 0 else None]  # a communicator id is good for one group only
+            dist.broadcast_object_list(ids, src=0)
+            nccl_id = ids[0]
+            eng = E.Engine(cfg, dtype, "f16" if dtype == "f16" else "f32", device=local, tp_rank=rank, tp_size=world,
+                           nccl_id=nccl_id, flags=args.flags | E.FLAG_TP_NCCL, ring_kb=args.ring_kb)
     host_copy = {} if (rank == 0 and world == 1 and not args.no_cpu_baseline) else None
     for name, l, t in gen_device_weights(cfg, dtype, tied, seed):
         eng.upload(name, t, max(l, 0))
@@ -250,7 +272,7 @@ def run_ours(args, rank, world):
             "scaling": "strong", "vs_baseline": None, "dtype": "f16 weights, f32 accumulate" if dtype == "f16" else "f32",
             "data": "synthetic",
             "config": {"workload": args.workload, "shape": cfg.asdict(), "prompt_tokens": n_prompt, "temperature": temp,
-                       "penalty": pen, "parallelism": f"tp{world}", "positions": [pos - 2 * args.steps, pos - args.steps],
+                       "penalty": pen, "parallelism": f"tp{world}", "tp_exchange": tp_exchange, "positions": [pos - 2 * args.steps, pos - args.steps],
                        "l2": "inputs larger than L2 (every step streams all weights, >> 126 MB)",
                        "timed_with": "CUDA events on the engine stream around K graph launches, max over ranks"},
             "clocks": clk.summary(),

@@ -472,6 +472,7 @@ static void record_allreduce(Recorder& R, float* buf, int n) {
 }
 
 static bool tp_peer_path(const lpp_engine* e);
+static bool tp_cls_sharded(const lpp_engine* e);
 static unsigned int* tp_epoch_word(const lpp_engine* e);
 
 // The fused sampler: exact-order kernel by default, tree kernel when asked for or when the vocabulary
@@ -512,7 +513,14 @@ static void matrix_span(const lpp_engine* e, int kind, int l, const void** ptr, 
         case kOproj: *bytes = D * e->Dq * esz; *ptr = (const char*)e->wo + l * *bytes; break;
         case kGateUp: *bytes = 2 * (size_t)e->Fl * D * esz; *ptr = (const char*)e->w13 + l * *bytes; break;
         case kDown: *bytes = D * e->Fl * esz; *ptr = (const char*)e->w2 + l * *bytes; break;
-        default: *bytes = (size_t)e->c.vocab_size * D * esz; *ptr = e->wcls; break;
+        default:
+            *bytes = (size_t)e->c.vocab_size * D * esz;
+            *ptr = e->wcls;
+            if (tp_cls_sharded(e)) {  // this rank's vocabulary rows
+                *bytes /= e->c.tp_size;
+                *ptr = (const char*)e->wcls + (size_t)e->c.tp_rank * *bytes;
+            }
+            break;
     }
 }
 // What the GEMV (kind, l) should pull towards L2 for its successor in the step: the next matrix, or
@@ -574,6 +582,49 @@ static void tp_set_consumer(const lpp_engine* e, GemvArgs& a, int ex, float* x_s
     a.tp_hint_per_step = tp_hint_per_step(e);
     a.x = nullptr;
     a.x_store = x_store;
+}
+
+// The classifier is sharded by vocabulary rows when the peers are mapped: every rank computes
+// vocab/tp logits and stores them, as flagged words, into every rank's logits area (after the
+// exchange areas of the buffer); a small kernel turns the words into the float logits the sampler reads.
+static bool tp_cls_sharded(const lpp_engine* e) {
+    return tp_peer_path(e) && e->c.vocab_size % (kRowsPerGroup * e->c.tp_size) == 0 && getenv("LPP_TP_SHARD_CLS");
+}
+static unsigned long long* tp_logits_area(const lpp_engine* e, int p) {
+    return reinterpret_cast<unsigned long long*>(e->peer_base[p] + tp_header_bytes() + (size_t)2 * e->c.n_layers * tp_area_bytes(e));
+}
+
+// words [0, n) = {logit, flag}: waits for the local classifier kernel (so that its CTAs, which this kernel's
+// CTAs would otherwise sit beside, are not slowed by polling), then polls until every word, local or from a
+// peer, carries this step's flag (bounded) and writes the floats.
+static __global__ void __launch_bounds__(256) tp_unpack_logits_kernel(const unsigned long long* words, float* logits, int n,
+                                                                    const unsigned int* epoch, StepState* st) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const unsigned int flag = *epoch + 1u;
+    const int i = (blockIdx.x * 256 + threadIdx.x) * 4;
+    if (i >= n) return;
+    unsigned long long w[4];
+    long long t0 = 0;
+    while (true) {
+        asm volatile("ld.volatile.global.v2.u64 {%0,%1}, [%2];" : "=l"(w[0]), "=l"(w[1]) : "l"(words + i) : "memory");
+        asm volatile("ld.volatile.global.v2.u64 {%0,%1}, [%2];" : "=l"(w[2]), "=l"(w[3]) : "l"(words + i + 2) : "memory");
+        bool pending = false;
+#pragma unroll
+        for (int q = 0; q < 4; ++q) pending |= (i + q < n) && (unsigned int)(w[q] >> 32) != flag;
+        if (!pending) break;
+        if (t0 == 0) {
+            if (*reinterpret_cast<volatile int*>(&st->status) & kStatusBarrierTimeout) break;
+            t0 = clock64();
+        } else if (clock64() - t0 > kTpWaitCycles) {
+            atomicOr(&st->status, kStatusBarrierTimeout);
+            break;
+        }
+        __nanosleep(40);
+    }
+#pragma unroll
+    for (int q = 0; q < 4; ++q)
+        if (i + q < n) logits[i + q] = __uint_as_float((unsigned int)w[q]);
 }
 
 // Ends a step that has no sampler kernel: bumps the exchange epoch.
@@ -705,8 +756,24 @@ static void record_step(Recorder& R, bool with_sampler) {
         if (peers) tp_set_consumer(e, a, 2 * (L - 1) + 1, cur);
         a.norm_w = e->rms_final;
         a.out = e->logits;
+        const bool sharded = tp_cls_sharded(e);
+        if (sharded) {
+            const int Vl = c.vocab_size / c.tp_size, r0 = c.tp_rank * Vl;
+            a.W = (const char*)e->wcls + (size_t)r0 * D * esz;
+            a.n_rows = Vl;
+            for (int p = 0; p < c.tp_size; ++p) a.tp_out[p] = tp_logits_area(e, p) + r0;
+        }
         set_prefetch(e, a, kLmHead, 0);
         record_gemv(R, kLmHead, kEpiStore, a);
+        if (sharded && !kind_skipped(e, kLmHead)) {
+            const int V = c.vocab_size;
+            R.check(launch_kernel(tp_unpack_logits_kernel, dim3((V + 1023) / 1024), dim3(256), 0, R.s, R.pdl(),
+                                  (const unsigned long long*)tp_logits_area(e, c.tp_rank), e->logits, V,
+                                  (const unsigned int*)tp_epoch_word(e), e->st),
+                    "logits unpack launch");
+            R.prev_kernel = true;
+            R.kernels++;
+        }
     }
     flush_phases(R);
     if (R.collect) return;
@@ -918,7 +985,8 @@ extern "C" lpp_status lpp_engine_create(const lpp_config* cfg, const void* nccl_
         if (r != 0) return bail(fail(LPP_ERR_NCCL, "ncclCommInitRank: %s", nccl::GetErrorString(r)));
         if (c.tp_size <= kMaxTp) {
             // receive areas and counters of the peer-memory exchange (used once lpp_tp_connect has mapped the peers)
-            e->tp_buf_bytes = tp_header_bytes() + (size_t)2 * c.n_layers * tp_area_bytes(e);
+            e->tp_buf_bytes = tp_header_bytes() + (size_t)2 * c.n_layers * tp_area_bytes(e) +
+                              (size_t)c.vocab_size * sizeof(unsigned long long);  // exchange areas + logits area
             CUB(cudaMalloc(&e->tp_buf, e->tp_buf_bytes));
             CUB(cudaMemset(e->tp_buf, 0, e->tp_buf_bytes));
             e->peer_base[c.tp_rank] = e->tp_buf;
@@ -1142,7 +1210,7 @@ extern "C" lpp_status lpp_finalize(lpp_engine* e) {
         }
         TRACE("finalize: graphs captured (%d kernels per long-context step)", e->kernels_full);
     } else {
-        e->kernels_full = e->persistent ? (c.tp_size > 1 ? 2 * c.n_layers + 2 : 2) : 5 * c.n_layers + 2;
+        e->kernels_full = e->persistent ? (c.tp_size > 1 ? 2 * c.n_layers + 2 : 2) : 5 * c.n_layers + 2 + (tp_cls_sharded(e) ? 1 : 0);
     }
     e->finalized = true;
     return LPP_OK;
@@ -1394,7 +1462,7 @@ static void kind_bytes(const lpp_engine* e, int pos, int64_t* b) {
     b[kOproj] = L * D * e->Dq * esz;
     b[kGateUp] = L * ((int64_t)2 * e->Fl * D * esz + 4 * D);
     b[kDown] = L * D * e->Fl * esz;
-    b[kLmHead] = V * D * esz + 4 * D;
+    b[kLmHead] = (tp_cls_sharded(e) ? V / c.tp_size : V) * D * esz + 4 * D;
 }
 extern "C" int64_t lpp_step_bytes(const lpp_engine* e, int pos) {
     if (!e) return 0;

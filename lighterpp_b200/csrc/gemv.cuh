@@ -435,9 +435,9 @@ __device__ __forceinline__ void dot_rows(const unsigned char* row0, const unsign
     if constexpr (NR == 2) acc1 += a1 + b1;
 }
 
-// Residual epilogue store: locally, or as {value, flag} words into this rank's slot on every rank of the
-// tensor-parallel group.
-__device__ __forceinline__ void store_resid_rows(const GemvArgs& a, int row, float v0, float v1) {
+// Store of a finished row pair: locally, or as {value, flag} words into this rank's slot (residual GEMVs) or
+// row range (vocabulary-sharded classifier) on every rank of the tensor-parallel group.
+__device__ __forceinline__ void store_rows(const GemvArgs& a, int row, float v0, float v1) {
     if (a.tp_size > 1 && a.tp_out[0]) {
         const unsigned long long flag = (unsigned long long)(*a.tp_epoch + 1u) << 32;
         const unsigned long long w0 = flag | __float_as_uint(v0), w1 = flag | __float_as_uint(v1);
@@ -455,7 +455,7 @@ template <int EPI>
 __device__ __forceinline__ void gemv_epilogue(const GemvArgs& a, int g, float v0, float v1) {
     const int row = g * kRowsPerGroup;
     if constexpr (EPI == kEpiStore) {
-        *reinterpret_cast<float2*>(a.out + row) = make_float2(v0, v1);
+        store_rows(a, row, v0, v1);
     } else if constexpr (EPI == kEpiResid) {
         // x += W.xb (src/model.cpp:232, 239); under tensor parallelism only rank 0 passes resid
         if (a.resid) {
@@ -463,7 +463,7 @@ __device__ __forceinline__ void gemv_epilogue(const GemvArgs& a, int g, float v0
             v0 += r.x;
             v1 += r.y;
         }
-        store_resid_rows(a, row, v0, v1);
+        store_rows(a, row, v0, v1);
     } else if constexpr (EPI == kEpiSwiglu) {
         // rows are interleaved (gate_i, up_i); hb = (h1*sigmoid(h1))*h3 (src/ops.cpp:78-87)
         const float sig = __fdiv_rn(1.0f, 1.0f + expf(-v0));
@@ -672,7 +672,7 @@ __device__ __forceinline__ bool gemv_ring_body(const GemvArgs& a, unsigned char*
                 acc1 = warp_sum(acc1);
                 if (lane == 0) {
                     if (EPI == kEpiResid && p + i == p0)
-                        store_resid_rows(a, p0 * kRowsPerGroup, acc0 + r_first.x, acc1 + r_first.y);
+                        store_rows(a, p0 * kRowsPerGroup, acc0 + r_first.x, acc1 + r_first.y);
                     else
                         gemv_epilogue<EPI>(a, p + i, acc0, acc1);
                 }
@@ -700,7 +700,7 @@ __device__ __forceinline__ bool gemv_ring_body(const GemvArgs& a, unsigned char*
             const float v0 = warp_sum(acc[0]), v1 = warp_sum(acc[1]);
             if (lane == 0) {
                 if (EPI == kEpiResid && p == p0)
-                    store_resid_rows(a, p0 * kRowsPerGroup, v0 + r_first.x, v1 + r_first.y);
+                    store_rows(a, p0 * kRowsPerGroup, v0 + r_first.x, v1 + r_first.y);
                 else
                     gemv_epilogue<EPI>(a, p, v0, v1);
             }
