@@ -522,20 +522,12 @@ __device__ __forceinline__ bool gemv_ring_body(const GemvArgs& a, unsigned char*
     const int g1 = (int)(((long long)(blockIdx.x + 1) * groups) / gridDim.x);
     const int ng = g1 - g0;
     const int w = (warp == kGemvConsumerWarps) ? lane : warp;  // pipeline index
-    int p0 = g0 + (w < kGemvConsumerWarps ? (ng * w) / kGemvConsumerWarps : 0);
-    int p1 = g0 + (w < kGemvConsumerWarps ? (ng * (w + 1)) / kGemvConsumerWarps : 0);
+    const int p0 = g0 + (w < kGemvConsumerWarps ? (ng * w) / kGemvConsumerWarps : 0);
+    const int p1 = g0 + (w < kGemvConsumerWarps ? (ng * (w + 1)) / kGemvConsumerWarps : 0);
     const size_t row_bytes = (size_t)a.K * sizeof(WT);
     const int m = a.pairs_per_stage;
     const int nch = m > 0 ? 1 : (a.K + a.kc - 1) / a.kc;
-    // pairs advance by `pstep` from p0 to p1.  Timing experiment (debug bit 16): stages are dealt round
-    // robin over all warps of the grid, so that all SMs sweep the matrix front to back together.
-    int pstep = m > 0 ? m : 1;
-    if ((a.debug & 16) && w < kGemvConsumerWarps) {
-        p0 = (w * (int)gridDim.x + (int)blockIdx.x) * pstep;
-        p1 = groups;
-        pstep *= kGemvConsumerWarps * (int)gridDim.x;
-        if (p0 > p1) p0 = p1;
-    }
+    const int pstep = m > 0 ? m : 1;  // pairs advance by pstep from p0 to p1
     const int unit = m > 0 ? m : 1;
 
     if (tid == 0) gemv_stamp(a, 0);
@@ -561,7 +553,9 @@ __device__ __forceinline__ bool gemv_ring_body(const GemvArgs& a, unsigned char*
             unsigned char* myring = ring + (size_t)w * NS * a.stage_bytes;
             int slot = 0, pass = 0;  // pass = completed trips around the ring
             bool alive = true;
-            const unsigned long long policy = (a.debug & 8) ? l2_policy_evict_first() : 0ull;
+            // streamed weights are marked evict-first in L2: they are used once per token and would
+            // otherwise push the K/V cache and the activations out (debug bit 8 turns the hint off)
+            const unsigned long long policy = !(a.debug & 8) ? l2_policy_evict_first() : 0ull;
             auto issue = [&](const unsigned char* src, uint32_t bytes) -> bool {
                 // trip p > 0 reuses a slot once its release number p-1 has happened
                 if (pass > 0 && !mbar_wait_bounded(&myempty[slot], (uint32_t)(pass - 1) & 1u, &a.st->status))
@@ -570,7 +564,7 @@ __device__ __forceinline__ bool gemv_ring_body(const GemvArgs& a, unsigned char*
                     mbar_arrive(&myfull[slot]);
                 } else {
                     mbar_arrive_expect_tx(&myfull[slot], bytes);
-                    if (a.debug & 8)
+                    if (!(a.debug & 8))
                         bulk_g2s_hint(myring + (size_t)slot * a.stage_bytes, src, bytes, &myfull[slot], policy);
                     else
                         bulk_g2s(myring + (size_t)slot * a.stage_bytes, src, bytes, &myfull[slot]);
