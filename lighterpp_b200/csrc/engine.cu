@@ -554,6 +554,14 @@ static unsigned long long* tp_area(const lpp_engine* e, int p, int ex) {
 }
 static unsigned int* tp_epoch_word(const lpp_engine* e) { return reinterpret_cast<unsigned int*>(e->tp_buf); }
 static unsigned int* tp_hint(const lpp_engine* e, int p, int ex) { return reinterpret_cast<unsigned int*>(e->peer_base[p] + 256) + ex; }
+// The arrival hint spares the receive area the polling of every thread of every CTA; with two ranks that
+// polling is light and measured faster (2051 against 2078 us/step on the 8B shape), so the hint is used from
+// three ranks on (LPP_TP_HINT=0/1 overrides).
+static bool tp_use_hint(const lpp_engine* e) {
+    if (2 * e->c.n_layers > 192) return false;
+    if (const char* v = getenv("LPP_TP_HINT")) return atoi(v) != 0;
+    return e->c.tp_size > 2;
+}
 static unsigned int tp_hint_per_step(const lpp_engine* e) {
     const int groups = e->c.dim / kRowsPerGroup;  // the producing GEMVs have dim rows
     return (unsigned int)(e->c.tp_size * std::max(1, std::min(groups, e->num_sms)));
@@ -565,7 +573,7 @@ static bool tp_peer_path(const lpp_engine* e) {
 }
 // producer side: exchange `ex` takes the rows of this residual GEMV
 static void tp_set_producer(const lpp_engine* e, GemvArgs& a, int ex) {
-    const bool use_hint = 2 * e->c.n_layers <= 192 && !getenv("LPP_TP_NO_HINT");
+    const bool use_hint = tp_use_hint(e);
     a.tp_size = e->c.tp_size;
     a.tp_epoch = tp_epoch_word(e);
     for (int p = 0; p < e->c.tp_size; ++p) {
@@ -578,7 +586,7 @@ static void tp_set_consumer(const lpp_engine* e, GemvArgs& a, int ex, float* x_s
     a.tp_size = e->c.tp_size;
     a.tp_epoch = tp_epoch_word(e);
     a.tp_in = tp_area(e, e->c.tp_rank, ex);
-    a.tp_hint_in = (2 * e->c.n_layers <= 192 && !getenv("LPP_TP_NO_HINT")) ? tp_hint(e, e->c.tp_rank, ex) : nullptr;
+    a.tp_hint_in = tp_use_hint(e) ? tp_hint(e, e->c.tp_rank, ex) : nullptr;
     a.tp_hint_per_step = tp_hint_per_step(e);
     a.x = nullptr;
     a.x_store = x_store;
@@ -588,7 +596,7 @@ static void tp_set_consumer(const lpp_engine* e, GemvArgs& a, int ex, float* x_s
 // vocab/tp logits and stores them, as flagged words, into every rank's logits area (after the
 // exchange areas of the buffer); a small kernel turns the words into the float logits the sampler reads.
 static bool tp_cls_sharded(const lpp_engine* e) {
-    return tp_peer_path(e) && e->c.vocab_size % (kRowsPerGroup * e->c.tp_size) == 0 && getenv("LPP_TP_SHARD_CLS");
+    return tp_peer_path(e) && e->c.vocab_size % (kRowsPerGroup * e->c.tp_size) == 0 && !getenv("LPP_TP_FULL_CLS");
 }
 static unsigned long long* tp_logits_area(const lpp_engine* e, int p) {
     return reinterpret_cast<unsigned long long*>(e->peer_base[p] + tp_header_bytes() + (size_t)2 * e->c.n_layers * tp_area_bytes(e));
