@@ -185,6 +185,31 @@ def test_long_context_prefilled_cache(E, oracle):
         e.close()
 
 
+@pytest.mark.parametrize("kv_dtype", ["f16", "f32"])
+def test_long_context_head_size_128(E, oracle, kv_dtype):
+    """The 8B attention geometry (head size 128, 4 query heads per KV head) with a pre-filled cache of 2500
+    positions (all KV splits in use) against the oracle, with the FP16 and the FP32 cache."""
+    c, dt, tied, seed = synth.SHAPES["mini-8b-f16"]
+    c = type(c)(**{**c.asdict(), "seq_len": 2600})
+    T = synth.gen_model(c, seed, dt, tied)
+    n_pre = 2500
+    rng = np.random.default_rng(5)
+    m = oracle.model(c, synth.as_f32(T))
+    ko, vo = m.kv_cache()
+    eng = E.Engine(c, dt, kv_dtype)
+    eng.load_weights(T)
+    for l in range(c.n_layers):
+        k = rng.standard_normal((c.n_kv_heads, n_pre, c.head_size)).astype(np.float16)
+        v = rng.standard_normal((c.n_kv_heads, n_pre, c.head_size)).astype(np.float16)
+        ko[l, :, :n_pre] = k
+        vo[l, :, :n_pre] = v
+        eng.kv_prefill(l, k.astype(np.float16 if kv_dtype == "f16" else np.float32), v.astype(np.float16 if kv_dtype == "f16" else np.float32), n_pre)
+    toks = synth.prompt_tokens(c.vocab_size, 4, seed)
+    for i, t in enumerate(toks):
+        check_logits(m.step_logits(int(t), n_pre + i), eng.step_logits(int(t), n_pre + i), dt)
+    eng.close()
+
+
 def test_llama32_1b_shape_first_steps(E, oracle):
     """Config 3 shape (128K vocabulary, tied classifier): first steps against the oracle."""
     c, dt, tied, seed = synth.SHAPES["llama-3.2-1b"]
