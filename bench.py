@@ -32,6 +32,8 @@ WORKLOADS = {
     "tinyllama-1.1b": ("tinyllama-1.1b", 32, 0.8, 1.1),
     "llama-3-8b": ("llama-3-8b", 64, 0.8, 1.1),
     "stories15m": ("stories15m", 16, 1.0, 1.0),
+    # long context: K/V cache pre-filled with 32768 positions of seeded N(0,1) values, then prompt + decode
+    "llama-3-8b-32k": ("llama-3-8b-32k", 64, 0.8, 1.1, 32768),
 }
 
 
@@ -140,9 +142,10 @@ def run_ours(args, rank, world):
     from lighterpp_b200 import engine as E, synth
     local = int(os.environ.get("LOCAL_RANK", 0))
     torch.cuda.set_device(local)
-    shape, n_prompt, temp, pen = WORKLOADS[args.workload]
+    shape, n_prompt, temp, pen, *rest = WORKLOADS[args.workload]
+    prefill = rest[0] if rest else 0
     cfg, dtype, tied, seed = synth.SHAPES[shape]
-    need = n_prompt + args.warmup + 2 * args.steps + 8
+    need = prefill + n_prompt + args.warmup + 2 * args.steps + 8
     if need > cfg.seq_len:
         cfg = type(cfg)(**{**cfg.asdict(), "seq_len": need})
     nccl_id = None
@@ -179,7 +182,9 @@ def run_ours(args, rank, world):
             nccl_id = ids[0]
             eng = E.Engine(cfg, dtype, "f16" if dtype == "f16" else "f32", device=local, tp_rank=rank, tp_size=world,
                            nccl_id=nccl_id, flags=args.flags | E.FLAG_TP_NCCL, ring_kb=args.ring_kb)
-    host_copy = {} if (rank == 0 and world == 1 and not args.no_cpu_baseline) else None
+    # the CPU baseline keeps FP32 host copies of all weights: only for shapes where that is a few GB
+    small = cfg.dim * cfg.n_layers <= 2048 * 22
+    host_copy = {} if (rank == 0 and world == 1 and not args.no_cpu_baseline and small) else None
     for name, l, t in gen_device_weights(cfg, dtype, tied, seed):
         eng.upload(name, t, max(l, 0))
         if host_copy is not None:
@@ -196,12 +201,20 @@ def run_ours(args, rank, world):
             dist.barrier()
             torch.cuda.synchronize()
 
+    if prefill:
+        g = torch.Generator(device="cuda")
+        g.manual_seed(seed + 1000)
+        for l in range(cfg.n_layers):  # every rank draws the same full-head tensors and keeps its heads
+            k = torch.randn((cfg.n_kv_heads, prefill, cfg.head_size), device="cuda", generator=g).half()
+            v = torch.randn((cfg.n_kv_heads, prefill, cfg.head_size), device="cuda", generator=g).half()
+            eng.kv_prefill(l, k, v, prefill)
+        del k, v
     # prompt: token by token through the same step, as the reference does (src/main.cpp:163-179)
     hist = []
-    for pos, t in enumerate(prompt[:-1]):
+    for i, t in enumerate(prompt[:-1]):
         hist = (hist + [int(t)])[-64:]
-        eng.forward(int(t), pos, temp, 1.1, hist, 0.5)
-    tok, pos = int(prompt[-1]), n_prompt - 1
+        eng.forward(int(t), prefill + i, temp, 1.1, hist, 0.5)
+    tok, pos = int(prompt[-1]), prefill + n_prompt - 1
     hist = (hist + [tok])[-64:]
     # warm-up (untimed), device-resident loop
     if args.warmup > 0:
@@ -271,7 +284,7 @@ def run_ours(args, rank, world):
             "ms_per_step": round(dev_ms / args.steps, 5), "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "f16 weights, f32 accumulate" if dtype == "f16" else "f32",
             "data": "synthetic",
-            "config": {"workload": args.workload, "shape": cfg.asdict(), "prompt_tokens": n_prompt, "temperature": temp,
+            "config": {"workload": args.workload, "shape": cfg.asdict(), "prefilled_positions": prefill, "prompt_tokens": n_prompt, "temperature": temp,
                        "penalty": pen, "parallelism": f"tp{world}", "tp_exchange": tp_exchange, "positions": [pos - 2 * args.steps, pos - args.steps],
                        "l2": "inputs larger than L2 (every step streams all weights, >> 126 MB)",
                        "timed_with": "CUDA events on the engine stream around K graph launches, max over ranks"},
@@ -295,7 +308,7 @@ def run_ours(args, rank, world):
                         for k, v in prof.items() if v["launches"]},
         }
     eng.close()
-    if world > 1 and not args.no_tp1:
+    if world > 1 and not args.no_tp1 and not prefill:
         # the same workload on ONE GPU (rank 0 alone, the other ranks wait): the number the sharded run is a
         # speed-up over.  N=1 of the default run is a different, smaller shape.
         torch.cuda.empty_cache()
@@ -344,7 +357,7 @@ def run_reference(args, rank, world):
     if rank != 0:
         return None
     from lighterpp_b200 import synth
-    shape, n_prompt, temp, pen = WORKLOADS[args.workload]
+    shape, n_prompt, temp, pen = WORKLOADS[args.workload][:4]
     cfg, dtype, tied, seed = synth.SHAPES[shape]
     small = type(cfg)(**{**cfg.asdict(), "seq_len": 256})
     try:
