@@ -113,6 +113,93 @@ __device__ __forceinline__ void team_barrier(int id, int nthreads) {
     asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
 }
 
+// Second half of a work item.  `scratch` holds one online-softmax state per warp of the team,
+// [NT/32][GB][HS+2] floats (HS accumulated values, then the running maximum and the running sum); the team
+// has passed a barrier since they were written.  Merges them, writes the result (one split) or this
+// split's partial, and lets the last team of the (kv head, head batch) combine the partials.
+template <int HS, int GB, int NT>
+__device__ __forceinline__ void attn_merge_and_combine(const AttnArgs& a, float* scratch, int split, int kvh, int hz, int n_z,
+                                                       int n_eff, int* s_last, int tid, int bar) {
+    float (*s_state)[GB][HS + 2] = reinterpret_cast<float (*)[GB][HS + 2]>(scratch);
+    const int hbase = kvh * a.gqa + hz * GB;
+    // merge the warps; with a single split the result is final, otherwise it is this split's partial
+    constexpr int NW = NT / 32;
+    float* part = a.part;
+    const int PS = HS + 2;
+    for (int idx = tid; idx < GB * HS; idx += NT) {
+        const int h = idx / HS, d = idx % HS;
+        float mm = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < NW; ++w) mm = fmaxf(mm, s_state[w][h][HS]);
+        float av = 0.f, lv = 0.f;
+#pragma unroll
+        for (int w = 0; w < NW; ++w) {
+            const float mw = s_state[w][h][HS];
+            const float f = (mw == -INFINITY) ? 0.f : __expf(mw - mm);
+            av += s_state[w][h][d] * f;
+            lv += s_state[w][h][HS + 1] * f;
+        }
+        if (n_eff == 1) {
+            a.out[(size_t)(hbase + h) * HS + d] = (lv > 0.f) ? __fdiv_rn(av, lv) : 0.f;
+        } else {
+            float* p = part + ((size_t)(hbase + h) * a.n_splits + split) * PS;
+            __stcg(p + d, av);
+            if (d == 0) {
+                __stcg(p + HS, mm);
+                __stcg(p + HS + 1, lv);
+            }
+        }
+    }
+    if (n_eff == 1) {
+        team_barrier(bar, NT);  // scratch may be reused by the team's next item
+        return;  // short context: no partials, no ticket, no second pass
+    }
+    __threadfence();
+    team_barrier(bar, NT);
+    if (tid == 0) {
+        const unsigned int ticket = atomicAdd(&a.counters[kvh * n_z + hz], 1u);
+        *s_last = (ticket == (unsigned int)n_eff - 1);
+    }
+    team_barrier(bar, NT);
+    if (!*s_last) return;
+    __threadfence();
+
+    // last team of this (kv head, head batch): combine the splits in index order.  Loads are issued
+    // in batches of eight before they are consumed; up to eight splits need a single round trip.
+    for (int idx = tid; idx < GB * HS; idx += NT) {
+        const int h = idx / HS, d = idx % HS;
+        const float* p = part + (size_t)(hbase + h) * a.n_splits * PS;
+        float mm = -INFINITY, av = 0.f, lv = 0.f;
+        for (int s0 = 0; s0 < n_eff; s0 += 8) {
+            float ms[8], ls[8], as[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const bool ok = s0 + i < n_eff;
+                const float* ps = p + (size_t)(s0 + i) * PS;
+                ms[i] = ok ? __ldcg(ps + HS) : -INFINITY;
+                ls[i] = ok ? __ldcg(ps + HS + 1) : 0.f;
+                as[i] = ok ? __ldcg(ps + d) : 0.f;
+            }
+            float mb = mm;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) mb = fmaxf(mb, ms[i]);
+            // rescale what has been accumulated so far to the new running maximum (fixed order)
+            const float fo = (mm == -INFINITY) ? 0.f : __expf(mm - mb);
+            av *= fo;
+            lv *= fo;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const float f = (ms[i] == -INFINITY) ? 0.f : __expf(ms[i] - mb);
+                av = fmaf(as[i], f, av);
+                lv = fmaf(ls[i], f, lv);
+            }
+            mm = mb;
+        }
+        a.out[(size_t)(hbase + h) * HS + d] = (lv > 0.f) ? __fdiv_rn(av, lv) : 0.f;
+    }
+    if (tid == 0) a.counters[kvh * n_z + hz] = 0u;
+}
+
 // One work item = (split, kv head, batch hz of GB query heads) at sequence length T with n_eff
 // splits in use, executed by a team of 128 threads (tid 0..127) that synchronise on named barrier
 // `bar`.  `scratch` holds [NT/32 warps][GB][HS+2] floats of shared memory, `s_last` one int.
@@ -266,82 +353,7 @@ __device__ __forceinline__ void attn_item(const AttnArgs& a, int split, int kvh,
     team_barrier(bar, NT);
     attn_stamp(a, tid, 3);
 
-    // merge the warps; with a single split the result is final, otherwise it is this split's partial
-    constexpr int NW = NT / 32;
-    float* part = a.part;
-    const int PS = HS + 2;
-    for (int idx = tid; idx < GB * HS; idx += NT) {
-        const int h = idx / HS, d = idx % HS;
-        float mm = -INFINITY;
-#pragma unroll
-        for (int w = 0; w < NW; ++w) mm = fmaxf(mm, s_state[w][h][HS]);
-        float av = 0.f, lv = 0.f;
-#pragma unroll
-        for (int w = 0; w < NW; ++w) {
-            const float mw = s_state[w][h][HS];
-            const float f = (mw == -INFINITY) ? 0.f : __expf(mw - mm);
-            av += s_state[w][h][d] * f;
-            lv += s_state[w][h][HS + 1] * f;
-        }
-        if (n_eff == 1) {
-            a.out[(size_t)(hbase + h) * HS + d] = (lv > 0.f) ? __fdiv_rn(av, lv) : 0.f;
-        } else {
-            float* p = part + ((size_t)(hbase + h) * a.n_splits + split) * PS;
-            __stcg(p + d, av);
-            if (d == 0) {
-                __stcg(p + HS, mm);
-                __stcg(p + HS + 1, lv);
-            }
-        }
-    }
-    if (n_eff == 1) {
-        team_barrier(bar, NT);  // scratch may be reused by the team's next item
-        return;  // short context: no partials, no ticket, no second pass
-    }
-    __threadfence();
-    team_barrier(bar, NT);
-    if (tid == 0) {
-        const unsigned int ticket = atomicAdd(&a.counters[kvh * n_z + hz], 1u);
-        *s_last = (ticket == (unsigned int)n_eff - 1);
-    }
-    team_barrier(bar, NT);
-    if (!*s_last) return;
-    __threadfence();
-
-    // last team of this (kv head, head batch): combine the splits in index order.  Loads are issued
-    // in batches of eight before they are consumed; up to eight splits need a single round trip.
-    for (int idx = tid; idx < GB * HS; idx += NT) {
-        const int h = idx / HS, d = idx % HS;
-        const float* p = part + (size_t)(hbase + h) * a.n_splits * PS;
-        float mm = -INFINITY, av = 0.f, lv = 0.f;
-        for (int s0 = 0; s0 < n_eff; s0 += 8) {
-            float ms[8], ls[8], as[8];
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                const bool ok = s0 + i < n_eff;
-                const float* ps = p + (size_t)(s0 + i) * PS;
-                ms[i] = ok ? __ldcg(ps + HS) : -INFINITY;
-                ls[i] = ok ? __ldcg(ps + HS + 1) : 0.f;
-                as[i] = ok ? __ldcg(ps + d) : 0.f;
-            }
-            float mb = mm;
-#pragma unroll
-            for (int i = 0; i < 8; ++i) mb = fmaxf(mb, ms[i]);
-            // rescale what has been accumulated so far to the new running maximum (fixed order)
-            const float fo = (mm == -INFINITY) ? 0.f : __expf(mm - mb);
-            av *= fo;
-            lv *= fo;
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                const float f = (ms[i] == -INFINITY) ? 0.f : __expf(ms[i] - mb);
-                av = fmaf(as[i], f, av);
-                lv = fmaf(ls[i], f, lv);
-            }
-            mm = mb;
-        }
-        a.out[(size_t)(hbase + h) * HS + d] = (lv > 0.f) ? __fdiv_rn(av, lv) : 0.f;
-    }
-    if (tid == 0) a.counters[kvh * n_z + hz] = 0u;
+    attn_merge_and_combine<HS, GB, NT>(a, scratch, split, kvh, hz, n_z, n_eff, s_last, tid, bar);
 }
 
 template <typename KT, int DPL, int GB>
@@ -381,6 +393,215 @@ __global__ void __launch_bounds__(kAttnKernelThreads) attn_decode_kernel(const A
     attn_item<KT, DPL, GB, kAttnKernelThreads>(a, blockIdx.x, blockIdx.y, blockIdx.z, gridDim.z, T, n_eff, s_scratch, &s_last,
                                                threadIdx.x, 0, pos);
     stamp(4);
+}
+
+// ------------------------------------------------------------------ tensor-core variant (FP16 cache)
+//
+// The kernel above spends its time in FP32 shuffles and exponentials (1.7 TB/s at 32 K positions, and
+// slower than this one from a few dozen positions on).  Here the scores q.K^T and the product P.V run
+// as mma.sync.m16n8k16 (FP16 operands, FP32 accumulators): the up to 8 query heads of a KV head are the
+// rows of the 16-row operand (the rest is zero), a warp handles 16 positions per step and keeps the rows
+// of its next step in flight.  No shared memory is involved in the operands: the dot product over head
+// dimensions and the sum over positions do not care about order, so the dimension / position that an
+// operand register stands for is chosen such that every lane reads whole 16-byte pieces of the rows
+// straight from global memory (a quad of lanes covers one K row; lane quad-row g owns head dims
+// [g*HS/8, (g+1)*HS/8) of its V rows).  Same splits, partials and combine as above.  As there, the
+// position and the rows of earlier positions are read before the dependency wait.
+__device__ __forceinline__ void mma_16816(float (&d)[4], unsigned int a0, unsigned int a1, unsigned int a2, unsigned int a3,
+                                          unsigned int b0, unsigned int b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ unsigned int pack_half2(float lo, float hi) {
+    const __half2 h = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<const unsigned int*>(&h);
+}
+
+template <int HS, int GQA>
+__global__ void __launch_bounds__(kAttnKernelThreads) attn_mma_kernel(const AttnArgs a) {
+    static_assert(HS == 64 || HS == 128, "head size");
+    static_assert(GQA >= 1 && GQA <= 8, "query heads per KV head");
+    constexpr int NT = kAttnKernelThreads, NW = NT / 32;
+    constexpr int KS = HS / 16;   // k-steps of the score product; a lane owns HS/4 dims of its K row = 2*KS registers
+    constexpr int NTL = HS / 8;   // n-tiles of the output; a lane owns NTL dims of its V rows = NTL/2 registers
+    __shared__ float s_scratch[NW * GQA * (HS + 2)];
+    __shared__ int s_last;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int g = lane >> 2, j = lane & 3;
+    pdl_launch_dependents();
+    // the position was written by the previous step's sampler, which completed before this step began
+    const int pos = a.st->pos;
+    const int T = (pos < 0 || pos >= a.seq_len) ? 0 : pos + 1;
+    const int n_eff = attn_effective_splits(T, a.n_splits, a.min_chunk);
+    const int split = blockIdx.x, kvh = blockIdx.y;
+    if (split >= n_eff) return;
+    const int chunk = (T + n_eff - 1) / n_eff;
+    const int t0 = split * chunk;
+    const int t1 = min(T, t0 + chunk);
+    const __half* kb = reinterpret_cast<const __half*>(a.k_cache) + (size_t)kvh * a.seq_len * HS;
+    const __half* vb = reinterpret_cast<const __half*>(a.v_cache) + (size_t)kvh * a.seq_len * HS;
+    const int hbase = kvh * a.gqa;
+
+    float o[NTL][4];
+#pragma unroll
+    for (int t = 0; t < NTL; ++t) o[t][0] = o[t][1] = o[t][2] = o[t][3] = 0.f;
+    float m = -INFINITY, l = 0.f;  // running maximum / sum of head g (identical on the 4 lanes of a quad)
+
+    // K rows of one step: group 0 = positions base..base+7, group 1 = base+8..base+15; this lane reads the
+    // piece [j*HS/4, (j+1)*HS/4) of the rows base+g and base+8+g
+    auto load_k = [&](int base, unsigned int (&kr)[2][2 * KS], int lim) {
+#pragma unroll
+        for (int grp = 0; grp < 2; ++grp) {
+            const int t = base + grp * 8 + g;
+            if (t < lim) {
+                const uint4* p = reinterpret_cast<const uint4*>(kb + (size_t)t * HS + j * (HS / 4));
+#pragma unroll
+                for (int i = 0; i < KS / 2; ++i) {
+                    const uint4 u = __ldcg(p + i);
+                    kr[grp][4 * i] = u.x; kr[grp][4 * i + 1] = u.y; kr[grp][4 * i + 2] = u.z; kr[grp][4 * i + 3] = u.w;
+                }
+            } else {
+#pragma unroll
+                for (int i = 0; i < 2 * KS; ++i) kr[grp][i] = 0u;
+            }
+        }
+    };
+    // V rows of one step: positions base+2j, base+2j+1, base+8+2j, base+8+2j+1 (the order in which the
+    // probabilities sit in the A operand below), head dims [g*NTL, (g+1)*NTL)
+    auto load_v = [&](int base, unsigned int (&vr)[4][NTL / 2], int lim) {
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+            const int t = base + (r >> 1) * 8 + 2 * j + (r & 1);
+            if (t < lim) {
+                const uint4* p = reinterpret_cast<const uint4*>(vb + (size_t)t * HS + g * NTL);
+#pragma unroll
+                for (int i = 0; i < NTL / 8; ++i) {
+                    const uint4 u = __ldcg(p + i);
+                    vr[r][4 * i] = u.x; vr[r][4 * i + 1] = u.y; vr[r][4 * i + 2] = u.z; vr[r][4 * i + 3] = u.w;
+                }
+            } else {
+#pragma unroll
+                for (int i = 0; i < NTL / 2; ++i) vr[r][i] = 0u;
+            }
+        }
+    };
+    unsigned int kr[2][2 * KS], vr[4][NTL / 2];
+    int base = t0 + warp * 16;
+    // first step: rows of earlier positions (written by earlier steps) are requested before the wait; the
+    // row of the current position, like q, comes from the QKV kernel of this step and follows it
+    const int stable = min(t1, pos);
+    if (base < t1) {
+        load_k(base, kr, stable);
+        load_v(base, vr, stable);
+    }
+    pdl_wait();
+    // A operand of the score product: row g = head g (zero from GQA on), this lane's HS/4 dims, pre-scaled
+    unsigned int qa[KS][2];
+    {
+        const float scale = __fdiv_rn(1.0f, __fsqrt_rn((float)HS));
+#pragma unroll
+        for (int s = 0; s < KS; ++s) {
+            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (g < GQA) v = __ldcg(reinterpret_cast<const float4*>(a.q + (size_t)(hbase + g) * HS + j * (HS / 4) + 4 * s));
+            qa[s][0] = pack_half2(v.x * scale, v.y * scale);
+            qa[s][1] = pack_half2(v.z * scale, v.w * scale);
+        }
+    }
+    if (pos < t1 && pos >= base && pos < base + 16) {
+#pragma unroll
+        for (int grp = 0; grp < 2; ++grp)
+            if (base + grp * 8 + g == pos) {
+                const uint4* p = reinterpret_cast<const uint4*>(kb + (size_t)pos * HS + j * (HS / 4));
+#pragma unroll
+                for (int i = 0; i < KS / 2; ++i) {
+                    const uint4 u = __ldcg(p + i);
+                    kr[grp][4 * i] = u.x; kr[grp][4 * i + 1] = u.y; kr[grp][4 * i + 2] = u.z; kr[grp][4 * i + 3] = u.w;
+                }
+            }
+#pragma unroll
+        for (int r = 0; r < 4; ++r)
+            if (base + (r >> 1) * 8 + 2 * j + (r & 1) == pos) {
+                const uint4* p = reinterpret_cast<const uint4*>(vb + (size_t)pos * HS + g * NTL);
+#pragma unroll
+                for (int i = 0; i < NTL / 8; ++i) {
+                    const uint4 u = __ldcg(p + i);
+                    vr[r][4 * i] = u.x; vr[r][4 * i + 1] = u.y; vr[r][4 * i + 2] = u.z; vr[r][4 * i + 3] = u.w;
+                }
+            }
+    }
+    for (; base < t1; base += NW * 16) {
+        // the rows of this warp's next step are requested before this step is computed
+        unsigned int krn[2][2 * KS], vrn[4][NTL / 2];
+        const int nbase = base + NW * 16;
+        if (nbase < t1) {
+            load_k(nbase, krn, t1);
+            load_v(nbase, vrn, t1);
+        }
+        // scores of the two groups
+        float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int s = 0; s < KS; ++s) {
+            mma_16816(s0, qa[s][0], 0u, qa[s][1], 0u, kr[0][2 * s], kr[0][2 * s + 1]);
+            mma_16816(s1, qa[s][0], 0u, qa[s][1], 0u, kr[1][2 * s], kr[1][2 * s + 1]);
+        }
+        // row g of s0 / s1: positions base+2j, base+2j+1 / base+8+2j, base+8+2j+1
+        float sc[4] = {s0[0], s0[1], s1[0], s1[1]};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int t = base + (i >> 1) * 8 + 2 * j + (i & 1);
+            if (t >= t1) sc[i] = -INFINITY;
+        }
+        float mx = fmaxf(fmaxf(sc[0], sc[1]), fmaxf(sc[2], sc[3]));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+        const float mn = fmaxf(m, mx);  // finite: position `base` is valid for every row
+        const float alpha = (m == -INFINITY) ? 0.f : __expf(m - mn);
+        float p[4], ps = 0.f;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            p[i] = (sc[i] == -INFINITY) ? 0.f : __expf(sc[i] - mn);
+            ps += p[i];
+        }
+        ps += __shfl_xor_sync(0xffffffffu, ps, 1);
+        ps += __shfl_xor_sync(0xffffffffu, ps, 2);
+        l = l * alpha + ps;
+        m = mn;
+        const unsigned int pa0 = pack_half2(p[0], p[1]), pa2 = pack_half2(p[2], p[3]);
+#pragma unroll
+        for (int t = 0; t < NTL; ++t) {
+            o[t][0] *= alpha;
+            o[t][1] *= alpha;
+            // B operand of n-tile t: column g = head dim g*NTL + t, rows = the four positions above
+            const unsigned int sel = (t & 1) ? 0x7632u : 0x5410u;
+            const unsigned int b0 = __byte_perm(vr[0][t >> 1], vr[1][t >> 1], sel);
+            const unsigned int b1 = __byte_perm(vr[2][t >> 1], vr[3][t >> 1], sel);
+            mma_16816(o[t], pa0, 0u, pa2, 0u, b0, b1);
+        }
+        if (nbase < t1) {
+#pragma unroll
+            for (int i = 0; i < 2 * KS; ++i) kr[0][i] = krn[0][i], kr[1][i] = krn[1][i];
+#pragma unroll
+            for (int r = 0; r < 4; ++r)
+#pragma unroll
+                for (int i = 0; i < NTL / 2; ++i) vr[r][i] = vrn[r][i];
+        }
+    }
+    // this warp's state: row g of n-tile t, columns 2j and 2j+1 = head dims (2j)*NTL + t and (2j+1)*NTL + t
+    float (*s_state)[GQA][HS + 2] = reinterpret_cast<float (*)[GQA][HS + 2]>(s_scratch);
+    if (g < GQA) {
+#pragma unroll
+        for (int t = 0; t < NTL; ++t) {
+            s_state[warp][g][(2 * j) * NTL + t] = o[t][0];
+            s_state[warp][g][(2 * j + 1) * NTL + t] = o[t][1];
+        }
+        if (j == 0) {
+            s_state[warp][g][HS] = m;
+            s_state[warp][g][HS + 1] = l;
+        }
+    }
+    __syncthreads();
+    attn_merge_and_combine<HS, GQA, NT>(a, s_scratch, split, kvh, 0, 1, n_eff, &s_last, tid, 0);
 }
 
 }  // namespace lpp

@@ -122,6 +122,7 @@ struct lpp_engine {
     int esz, kvesz;
     int num_sms;
     int attn_splits, attn_gb, attn_z;
+    int attn_splits_long;  // splits of the tensor-core kernel: one CTA per SM, one wave
     int sample_blocks;
     size_t smem_optin;
     cudaStream_t stream = nullptr;
@@ -309,6 +310,22 @@ static cudaError_t launch_attn_t(lpp_engine* e, const AttnArgs& a, dim3 grid, bo
     return cudaErrorInvalidValue;
 }
 
+// Attention with the scores and P.V on the tensor cores (FP16 cache, head size 64 or 128, 1/2/4/8 query heads
+// per KV head); other shapes keep the CUDA-core kernel.
+static cudaError_t launch_attn_mma(lpp_engine* e, const AttnArgs& a, bool pdl, cudaStream_t s) {
+    if (e->c.kv_dtype != LPP_F16) return cudaErrorNotSupported;
+    const dim3 grid(a.n_splits, e->KVHl, 1), block(kAttnKernelThreads);
+#define LPP_MMA_CASE(HS_, G_) \
+    if (e->hs == HS_ && e->gqa == G_) return launch_kernel(attn_mma_kernel<HS_, G_>, grid, block, 0, s, pdl, a);
+    LPP_MMA_CASE(64, 1) LPP_MMA_CASE(64, 2) LPP_MMA_CASE(64, 4) LPP_MMA_CASE(64, 8)
+    LPP_MMA_CASE(128, 1) LPP_MMA_CASE(128, 2) LPP_MMA_CASE(128, 4) LPP_MMA_CASE(128, 8)
+#undef LPP_MMA_CASE
+    return cudaErrorNotSupported;
+}
+static bool attn_mma_supported(const lpp_engine* e) {
+    return e->c.kv_dtype == LPP_F16 && (e->hs == 64 || e->hs == 128) && (e->gqa == 1 || e->gqa == 2 || e->gqa == 4 || e->gqa == 8);
+}
+
 // ---- one decode step as a sequence of launches (captured into the graph, or run directly)
 
 struct Recorder {
@@ -320,7 +337,7 @@ struct Recorder {
     // table exists, counted off and launched as runs of consecutive phases
     bool collect = false;
     int cursor = 0, pending = 0, launch_idx = 0;
-    bool short_ctx = false;  // record the short-context variant of the step
+    bool long_ctx = false;  // record the long-context variant of the step (tensor-core attention kernel)
     cudaError_t err = cudaSuccess;
     std::string where;
 
@@ -701,9 +718,14 @@ static void record_step(Recorder& R, bool with_sampler) {
                 } else if (!kind_skipped(e, kAttn)) {
                     if (e->gtrace && R.kernels < 256) at.trace = e->gtrace + (size_t)R.kernels * e->num_sms * 8;
                     R.mark(kAttn);
-                    R.check(c.kv_dtype == LPP_F32 ? launch_attn_t<float>(e, at, grid, R.pdl(), R.s)
-                                                  : launch_attn_t<__half>(e, at, grid, R.pdl(), R.s),
-                            "attention launch");
+                    if (attn_mma_supported(e) && !getenv("LPP_ATTN_CUDA_CORES")) {
+                        at.n_splits = e->attn_splits_long;
+                        R.check(launch_attn_mma(e, at, R.pdl(), R.s), "attention (tensor-core) launch");
+                    } else {
+                        R.check(c.kv_dtype == LPP_F32 ? launch_attn_t<float>(e, at, grid, R.pdl(), R.s)
+                                                      : launch_attn_t<__half>(e, at, grid, R.pdl(), R.s),
+                                "attention launch");
+                    }
                     R.mark(-1);
                     R.prev_kernel = true;
                     R.kernels++;
@@ -804,11 +826,11 @@ static void record_step(Recorder& R, bool with_sampler) {
     }
 }
 
-static lpp_status capture(lpp_engine* e, bool with_sampler, bool short_ctx, cudaGraphExec_t* out, int* kernels) {
+static lpp_status capture(lpp_engine* e, bool with_sampler, bool long_ctx, cudaGraphExec_t* out, int* kernels) {
     cudaGraph_t g = nullptr;
     CU(cudaStreamBeginCapture(e->stream, cudaStreamCaptureModeThreadLocal));
     Recorder R{e, e->stream};
-    R.short_ctx = short_ctx;
+    R.long_ctx = long_ctx;
     record_step(R, with_sampler);
     cudaError_t ce = cudaStreamEndCapture(e->stream, &g);
     if (R.err != cudaSuccess) {
@@ -830,7 +852,7 @@ static lpp_status run_step(lpp_engine* e, bool with_sampler, int pos) {
     (void)pos;
     if (e->c.flags & LPP_FLAG_NO_GRAPH) {
         Recorder R{e, e->stream};
-        R.short_ctx = v == 1;
+        R.long_ctx = v == 1;
         record_step(R, with_sampler);
         if (R.err != cudaSuccess) return fail(LPP_ERR_CUDA, "%s: %s", R.where.c_str(), cudaGetErrorString(R.err));
         return LPP_OK;
@@ -899,6 +921,7 @@ extern "C" lpp_status lpp_engine_create(const lpp_config* cfg, const void* nccl_
     e->attn_z = e->gqa / e->attn_gb;
     int splits = c.attn_splits > 0 ? c.attn_splits : (2 * e->num_sms + e->KVHl * e->attn_z - 1) / (e->KVHl * e->attn_z);
     e->attn_splits = std::max(1, std::min(splits, 64));
+    e->attn_splits_long = std::max(1, std::min(e->attn_splits, e->num_sms / std::max(1, e->KVHl)));
     e->sample_blocks = (c.vocab_size + kSampleChunk - 1) / kSampleChunk;
     if (e->sample_blocks > kSampleMaxBlocks) {
         delete e;
