@@ -418,6 +418,8 @@ __device__ __forceinline__ unsigned int pack_half2(float lo, float hi) {
     return *reinterpret_cast<const unsigned int*>(&h);
 }
 
+constexpr int kAttnPrefetchSteps = 1;  // how many steps past the next one the L2 prefetch runs ahead
+
 template <int HS, int GQA>
 __global__ void __launch_bounds__(kAttnKernelThreads) attn_mma_kernel(const AttnArgs a) {
     static_assert(HS == 64 || HS == 128, "head size");
@@ -537,6 +539,19 @@ __global__ void __launch_bounds__(kAttnKernelThreads) attn_mma_kernel(const Attn
         if (nbase < t1) {
             load_k(nbase, krn, t1);
             load_v(nbase, vrn, t1);
+        }
+        // the rows of the step after that are pulled towards L2 (no registers to hold them yet), so that
+        // their loads, one iteration from now, take an L2 round trip instead of an HBM one
+        {
+            const int pbase = nbase + kAttnPrefetchSteps * NW * 16;
+#pragma unroll
+            for (int grp = 0; grp < 2; ++grp)
+                if (pbase + grp * 8 + g < t1)
+                    asm volatile("prefetch.global.L2 [%0];" ::"l"(kb + (size_t)(pbase + grp * 8 + g) * HS + j * (HS / 4)));
+#pragma unroll
+            for (int r = 0; r < 4; ++r)
+                if (pbase + (r >> 1) * 8 + 2 * j + (r & 1) < t1)
+                    asm volatile("prefetch.global.L2 [%0];" ::"l"(vb + (size_t)(pbase + (r >> 1) * 8 + 2 * j + (r & 1)) * HS + g * NTL));
         }
         // scores of the two groups
         float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
