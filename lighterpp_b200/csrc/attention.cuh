@@ -435,7 +435,10 @@ __global__ void __launch_bounds__(kAttnKernelThreads) attn_mma_kernel(const Attn
     // the position was written by the previous step's sampler, which completed before this step began
     const int pos = a.st->pos;
     const int T = (pos < 0 || pos >= a.seq_len) ? 0 : pos + 1;
-    const int n_eff = attn_effective_splits(T, a.n_splits, a.min_chunk);
+    // one CTA per KV head up to two chunks of positions: below that a second split costs more in the
+    // combine (partials, ticket, second pass) than it saves (measured: 602 against 620 us/token at 180-243)
+    const int min_chunk = a.min_chunk > 0 ? a.min_chunk : kAttnMinChunk;
+    const int n_eff = (T <= 2 * min_chunk) ? 1 : attn_effective_splits(T, a.n_splits, min_chunk);
     const int split = blockIdx.x, kvh = blockIdx.y;
     if (split >= n_eff) return;
     const int chunk = (T + n_eff - 1) / n_eff;
