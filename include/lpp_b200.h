@@ -64,8 +64,8 @@ typedef enum {
                                       reference's sequential FP32 sums bit for bit */
 #define LPP_FLAG_TP_NCCL 0x20u   /* tensor parallelism: keep the NCCL all-reduce after o_proj / down even when the peers
                                   * are mapped (lpp_tp_connect); default is the exchange fused into the GEMVs */
-#define LPP_FLAG_PERSISTENT 0x8u /* one persistent kernel with grid barriers per run of phases instead of one
-                                    kernel per phase (measured slower on B200; kept for comparison) */
+#define LPP_FLAG_TP_LOCAL 0x40u  /* tensor parallelism without NCCL: the engine never loads or initialises NCCL and
+                                  * nccl_id may be NULL; only the peer-memory exchange (lpp_tp_connect) can run */
 
 /* Mirror of the reference Config (src/model.h:21-31) plus what a device engine needs. */
 typedef struct {
@@ -79,6 +79,10 @@ typedef struct {
     uint32_t flags;       /* LPP_FLAG_*                                                             */
     int32_t ring_kb;      /* shared-memory weight ring per CTA in KiB (0 = default)                 */
     int32_t attn_splits;  /* KV splits of the flash-decode kernel (0 = default)                     */
+    int32_t wait_ms;      /* limit of a device-side wait on this GPU's own work, in milliseconds of SM
+                             clocks (0 = default, about 50 ms); when it runs out the step ends with
+                             LPP_ERR_DEVICE_STATUS instead of hanging                               */
+    int32_t tp_wait_ms;   /* the same for a wait on a tensor-parallel peer (0 = default, seconds)   */
 } lpp_config;
 
 /* Sampling parameters of one step: forward()'s temperature / penalty arguments
@@ -107,10 +111,11 @@ lpp_status lpp_upload_tensor(lpp_engine* e, int which, int layer, const void* sr
  * uploaded (src/loader.cpp:66, 471, 619-632), captures the step graph. */
 lpp_status lpp_finalize(lpp_engine* e);
 
-/* Tensor parallelism over peer memory (one process per GPU, tp_size <= 8).  The reference all-reduces
- * the partial o_proj / down results with ncclAllReduce (src/model.cpp:236, 243 under USE_NCCL); here the
- * residual GEMV of every rank stores its rows straight into all ranks' receive areas over NVLink and the
- * next GEMV adds the tp_size partial vectors in rank order while it stages its input.  Each rank
+/* Tensor parallelism over peer memory (one process per GPU, tp_size <= 8).  No counterpart in the
+ * reference, which has no multi-GPU code: its o_proj / down results (src/model.cpp:201, 238) are
+ * complete on the one device.  Here every rank holds a slice of the heads and of the FFN columns, the
+ * residual GEMV of every rank stores its partial rows straight into all ranks' receive areas over NVLink and
+ * the next GEMV adds the tp_size partial vectors in rank order while it stages its input.  Each rank
  * exports an IPC handle of its receive buffer (LPP_TP_HANDLE_BYTES bytes), the caller gathers the
  * handles of all ranks in rank order over its own host channel and hands them to every engine before
  * lpp_finalize.  Without lpp_tp_connect (or with LPP_FLAG_TP_NCCL) the NCCL all-reduce is used. */
@@ -170,17 +175,18 @@ int64_t lpp_step_bytes(const lpp_engine* e, int pos);
 /* Per-kernel-kind timing of one step at `pos`: the step is captured with a CUDA event-record node
  * before and after every kernel and replayed iters times (isolated kernel durations, no programmatic
  * overlap, no host launch latency).  kinds: 0 qkv gemv, 1 attention, 2 o_proj gemv, 3 gate|up gemv, 4 down gemv,
- * 5 lm-head gemv, 6 sampler, 7 all-reduce, 8 persistent step kernel (all GEMV and attention phases of
- * a run in one launch; kinds 0-5 then stay empty), 9 reserved.  ms[10] total device ms per step per
- * kind, launches[10] launches per step, bytes[10] algorithmic bytes per step. */
-lpp_status lpp_profile_step(lpp_engine* e, int pos, int iters, float* ms, int* launches, int64_t* bytes);
+ * 5 lm-head gemv, 6 sampler, 7 all-reduce, 8-9 reserved.  ms[10] total device ms per step per
+ * kind, launches[10] launches per step, bytes[10] algorithmic bytes per step.  The sampler runs with the
+ * temperature and penalty given in *sp (NULL = temperature 0, no penalty). */
+lpp_status lpp_profile_step(lpp_engine* e, int pos, int iters, const lpp_sample_params* sp, float* ms, int* launches,
+                            int64_t* bytes);
 
 /* Average duration of one launch of kernel kind `kind` (numbering above) when the step's launches of
  * that kind run back to back at `pos`, launched as the step launches them (programmatic dependent
  * launch between consecutive kernels), timed with one CUDA event pair on the engine stream around
  * the sequence and averaged over `iters` repetitions.  Each launch streams its own layer's weights.
  * *launches = launches of that kind per step.  The activations the kernels see are stale: call it
- * between steps, never inside a run.  Not available with LPP_FLAG_PERSISTENT. */
+ * between steps, never inside a run. */
 lpp_status lpp_profile_kind(lpp_engine* e, int pos, int kind, int iters, float* ms_per_launch, int* launches);
 
 /* ---- standalone operators: the host wrappers of src/kernels.cuh:24-36, device pointers in/out,

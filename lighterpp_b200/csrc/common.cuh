@@ -37,6 +37,8 @@ struct StepState {
     float r;           // uniform draw for teacher-forced steps (advance == 0)
     int out_token;     // sampled token of the last step
     int status;        // kStatus* bits, sticky until the host clears them
+    long long wait_cycles;     // limit of a wait on this GPU's own work in SM clocks (0 = kWaitCycles)
+    long long tp_wait_cycles;  // limit of a wait on a tensor-parallel peer in SM clocks (0 = kTpWaitCycles)
     int history[kHistoryMax];
 };
 
@@ -106,16 +108,49 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
-// Bounded wait: polls until the phase completes or ~kWaitCycles SM clocks (tens of milliseconds)
-// have passed, then records the timeout in *status and returns false.  Callers stop consuming and
-// fall through to the kernel's end, so a lost copy cannot hang the GPU; the host sees the status.
+// Non-blocking test of a barrier phase (try_wait may suspend the whole warp for a while, which a warp whose
+// lanes watch DIFFERENT barriers cannot afford).
+__device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+
+// Limits of device-side waits, in SM clocks.  A wait on this GPU's own work (a bulk copy, a grid barrier)
+// gives up after tens of milliseconds.  The ranks of a tensor-parallel group are separate processes whose
+// launches may be skewed by host-side delays, so the limit of a wait on a peer is seconds.  Both can be
+// shortened per engine (StepState::wait_cycles / tp_wait_cycles, from lpp_config); once a wait has run
+// out the status bit is set and no later wait of the engine spins again.
 constexpr long long kWaitCycles = 100ll * 1000 * 1000;
-__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity, int* status) {
+constexpr long long kTpWaitCycles = 8ll * 1000 * 1000 * 1000;
+__device__ __forceinline__ long long wait_limit(const StepState* st) {
+    const long long v = st ? *reinterpret_cast<const volatile long long*>(&st->wait_cycles) : 0;
+    return v > 0 ? v : kWaitCycles;
+}
+__device__ __forceinline__ long long tp_wait_limit(const StepState* st) {
+    const long long v = st ? *reinterpret_cast<const volatile long long*>(&st->tp_wait_cycles) : 0;
+    return v > 0 ? v : kTpWaitCycles;
+}
+__device__ __forceinline__ bool status_timed_out(const StepState* st) {
+    return (*reinterpret_cast<const volatile int*>(&st->status) & kStatusBarrierTimeout) != 0;
+}
+
+// Bounded wait: polls until the phase completes or the limit has passed, then records the timeout in
+// st->status and returns false.  Callers stop consuming and fall through to the kernel's end, so a lost
+// copy cannot hang the GPU; the host sees the status (LPP_ERR_DEVICE_STATUS).
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity, StepState* st) {
     if (mbar_try_wait(bar, parity)) return true;
     const long long t0 = clock64();
+    const long long limit = wait_limit(st);
     while (!mbar_try_wait(bar, parity)) {
-        if (clock64() - t0 > kWaitCycles) {
-            if (status) atomicOr(status, kStatusBarrierTimeout);
+        if (clock64() - t0 > limit) {
+            if (st) atomicOr(&st->status, kStatusBarrierTimeout);
             return false;
         }
     }

@@ -35,7 +35,6 @@
 #include "ops.cuh"
 #include "sampler.cuh"
 #include "sampler_exact.cuh"
-#include "step.cuh"
 
 using namespace lpp;
 
@@ -63,6 +62,15 @@ void lpp_internal_set_error(const char* msg) { g_err = msg ? msg : ""; }
         lpp_status s_ = (call);        \
         if (s_ != LPP_OK) return s_;   \
     } while (0)
+
+// Timing aids: environment switches that change what a step launches (kernel kinds left out, arithmetic
+// skipped, stage sizes, prefetch depth ...).  Some make the results meaningless, so they exist only in
+// builds made with -DLPP_TIMING_AIDS; the product build never looks at them.
+#ifdef LPP_TIMING_AIDS
+static const char* aid_env(const char* name) { return getenv(name); }
+#else
+static const char* aid_env(const char*) { return nullptr; }
+#endif
 
 // LPP_TRACE=1 in the environment prints one line per host-side phase and synchronises after every
 // launch of an un-graphed step, to localise a failing kernel.
@@ -114,7 +122,7 @@ static bool load() {
 
 // ------------------------------------------------------------------ engine
 
-enum Kind { kQkv = 0, kAttn = 1, kOproj = 2, kGateUp = 3, kDown = 4, kLmHead = 5, kSampler = 6, kAllReduce = 7, kStepKernel = 8, kKinds = 10 };
+enum Kind { kQkv = 0, kAttn = 1, kOproj = 2, kGateUp = 3, kDown = 4, kLmHead = 5, kSampler = 6, kAllReduce = 7, kKinds = 10 };
 
 struct lpp_engine {
     lpp_config c;
@@ -153,22 +161,14 @@ struct lpp_engine {
     // upload staging
     void* stage = nullptr;
     size_t stage_bytes = 0;
-    // persistent step kernel: phase table (host copy + device), per-launch grid-barrier counters
-    bool persistent = false;
-    std::vector<StepPhase> h_phases;
-    StepPhase* d_phases = nullptr;
-    unsigned int* gbar = nullptr;
-    int n_gbar = 0;
-    unsigned long long* trace = nullptr;  // LPP_STEP_TRACE: per-CTA per-phase time stamps
     // tensor-parallel exchange over peer memory: per exchange (2 per layer) a receive area [tp][dim] floats
     // and two counters; peer_base[p] = rank p's buffer as mapped into this process (own buffer for p == rank)
     unsigned char* tp_buf = nullptr;
     size_t tp_buf_bytes = 0;
     unsigned char* peer_base[kMaxTp] = {};
     bool peer_ready = false;
+    unsigned char* absent_peer = nullptr;  // test aid: where stores to ranks that do not exist go (lpp_debug_tp_absent_peers)
     unsigned long long* gtrace = nullptr;  // LPP_GEMV_TRACE: per-launch per-CTA time stamps of the ring GEMV
-    int step_slots = 2, step_xs_bytes = 0;
-    size_t step_smem = 0;
     // graphs
     // graph variants by context length; only [0] is used at present
     cudaGraphExec_t g_full[2] = {nullptr, nullptr}, g_logits[2] = {nullptr, nullptr};
@@ -212,21 +212,18 @@ struct GemvPlan {
     size_t smem;
 };
 
-constexpr int kStageTarget = 8192;  // bytes per bulk copy / ring slot (see gemv.cuh)
+constexpr int kStageTarget = 8192;  // bytes per ring slot (see gemv.cuh)
 
-// A stage is one bulk copy of about stage_target bytes: whole row pairs when they fit, else one
-// K-chunk of one row.
+// Ring geometry of one GEMV: rows per stage and bytes per slot.  A row that is a single K-chunk travels
+// with its neighbours in one bulk copy (as many whole rows as fit the slot, a power of two up to the
+// group size); longer rows travel chunk by chunk, `target / chunk bytes` rows per slot.
 static void gemv_geometry(GemvArgs& a, int esz, int stage_target) {
-    const int pair_bytes = kRowsPerGroup * a.K * esz;
-    if (pair_bytes <= stage_target) {
-        a.pairs_per_stage = stage_target / pair_bytes;
-        a.kc = a.K;
-        a.stage_bytes = a.pairs_per_stage * pair_bytes;
-    } else {
-        a.pairs_per_stage = 0;
-        a.kc = std::max(8, std::min(a.K, stage_target / esz) / 8 * 8);
-        a.stage_bytes = a.kc * esz;
-    }
+    const int xc = 32 * kVecPerLane * (16 / esz);  // inputs per chunk
+    const int chunk_bytes = std::min(a.K, xc) * esz;
+    int rps = 1;
+    while (rps * 2 <= kGroupRows && rps * 2 * chunk_bytes <= stage_target) rps *= 2;
+    a.rps = rps;
+    a.stage_bytes = (int)align_up((size_t)rps * chunk_bytes, 128);
 }
 
 template <typename WT, int EPI>
@@ -248,11 +245,15 @@ static cudaError_t launch_gemv_t(lpp_engine* e, GemvArgs& a, bool pdl, cudaStrea
     }
     // LPP_STAGE_KB (timing experiments) overrides the 8 KiB stage size.
     int stage_target = kStageTarget;
-    if (const char* sk = getenv("LPP_STAGE_KB")) stage_target = std::max(1, atoi(sk)) * 1024;
+    if (const char* sk = aid_env("LPP_STAGE_KB")) stage_target = std::max(1, atoi(sk)) * 1024;
     gemv_geometry(a, esz, stage_target);
     const size_t fixed = kGemvBarrierBytes + 128 + xbytes;
-    size_t ring = (size_t)(e->c.ring_kb > 0 ? e->c.ring_kb : 128) * 1024;
+    size_t ring = (size_t)(e->c.ring_kb > 0 ? e->c.ring_kb : 192) * 1024;
     if (fixed + ring > e->smem_optin) ring = e->smem_optin - fixed;
+    if (ring < (size_t)2 * kGemvConsumerWarps * a.stage_bytes && stage_target > 4096) {
+        // two slots per warp do not fit beside a long staged input: halve the slots
+        gemv_geometry(a, esz, stage_target / 2);
+    }
     int ns = (int)(ring / ((size_t)kGemvConsumerWarps * a.stage_bytes));  // slots per consumer warp
     ns = std::max(2, std::min(ns, kGemvMaxStages));
     const int grid = std::max(1, std::min(groups, e->num_sms));
@@ -333,10 +334,6 @@ struct Recorder {
     cudaStream_t s;
     bool prev_kernel = false;  // previous stream item was one of our kernels -> PDL edge allowed
     int kernels = 0;
-    // persistent mode: phases are either collected into the engine's table (collect) or, once the
-    // table exists, counted off and launched as runs of consecutive phases
-    bool collect = false;
-    int cursor = 0, pending = 0, launch_idx = 0;
     bool long_ctx = false;  // record the long-context variant of the step (tensor-core attention kernel)
     cudaError_t err = cudaSuccess;
     std::string where;
@@ -366,46 +363,10 @@ struct Recorder {
     }
 };
 
-// ---- persistent step kernel dispatch
-
-template <typename WT, typename KT, int DPL>
-static cudaError_t launch_step_g(lpp_engine* e, const StepArgs& sa, bool pdl, cudaStream_t s) {
-    auto go = [&](auto kernel) -> cudaError_t {
-        static bool attr_done[64] = {};
-        if (!attr_done[e->c.device & 63]) {
-            cudaError_t r = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)e->smem_optin);
-            if (r != cudaSuccess) return r;
-            attr_done[e->c.device & 63] = true;
-        }
-        return launch_kernel(kernel, dim3(e->num_sms), dim3(kGemvRingThreads), e->step_smem, s, pdl, sa);
-    };
-    switch (e->attn_gb) {
-        case 4: return go(step_kernel<WT, KT, DPL, 4>);
-        case 2: return go(step_kernel<WT, KT, DPL, 2>);
-        default: return go(step_kernel<WT, KT, DPL, 1>);
-    }
-}
-template <typename WT, typename KT>
-static cudaError_t launch_step_t(lpp_engine* e, const StepArgs& sa, bool pdl, cudaStream_t s) {
-    switch (e->hs / 8) {
-        case 4: return launch_step_g<WT, KT, 4>(e, sa, pdl, s);
-        case 6: return launch_step_g<WT, KT, 6>(e, sa, pdl, s);
-        case 8: return launch_step_g<WT, KT, 8>(e, sa, pdl, s);
-        case 16: return launch_step_g<WT, KT, 16>(e, sa, pdl, s);
-    }
-    return cudaErrorInvalidValue;
-}
-// The persistent kernel is instantiated for FP16 weights + FP16 cache and FP32 weights + FP32 cache,
-// head sizes 32/48/64/128; other combinations use the kernel-per-phase path.
-static bool step_kernel_supported(const lpp_engine* e) {
-    const int d = e->hs / 8;
-    return e->c.weight_dtype == e->c.kv_dtype && (d == 4 || d == 6 || d == 8 || d == 16);
-}
-
 // LPP_DEBUG_SKIP=<bitmask of Kind> leaves those kernels out of the step (results become
 // meaningless): a timing aid that shows what each kernel kind costs inside the replayed graph.
 static unsigned skip_mask() {
-    const char* v = getenv("LPP_DEBUG_SKIP");
+    const char* v = aid_env("LPP_DEBUG_SKIP");
     return v ? (unsigned)strtol(v, nullptr, 0) : 0u;
 }
 // only_kind >= 0 (lpp_profile_kind): every other kind is left out of the recorded sequence.
@@ -413,56 +374,12 @@ static bool kind_skipped(const lpp_engine* e, int kind) {
     return (skip_mask() & (1u << kind)) || (e->only_kind >= 0 && kind != e->only_kind);
 }
 
-// Persistent mode: launches the phases counted since the last flush as one step-kernel run.
-static void flush_phases(Recorder& R) {
-    lpp_engine* e = R.e;
-    if (!e->persistent || R.collect || R.pending == 0) return;
-    StepArgs sa = {};
-    sa.phases = e->d_phases;
-    sa.first = R.cursor - R.pending;
-    sa.count = R.pending;
-    sa.gbar = e->gbar + R.launch_idx++;
-    sa.st = e->st;
-    sa.n_slots = e->step_slots;
-    sa.slot_bytes = kStageTarget;
-    sa.xs_bytes = e->step_xs_bytes;
-    sa.trace = e->trace;
-    R.mark(kStepKernel);
-    R.check(e->c.weight_dtype == LPP_F16 ? launch_step_t<__half, __half>(e, sa, R.pdl(), R.s)
-                                         : launch_step_t<float, float>(e, sa, R.pdl(), R.s),
-            "step kernel launch");
-    R.mark(-1);
-    R.prev_kernel = true;
-    R.kernels++;
-    R.pending = 0;
-}
-
-static void record_phase(Recorder& R, const StepPhase& ph) {
-    if (R.collect) R.e->h_phases.push_back(ph);
-    R.cursor++;
-    R.pending++;
-}
-
 static void record_gemv(Recorder& R, int kind, int epi, GemvArgs a) {
     lpp_engine* e = R.e;
-    if (e->persistent) {
-        a.st = e->st;
-        a.vocab = e->c.vocab_size;
-        a.seq_len = e->c.seq_len;
-        a.pf = nullptr;
-        a.pf_bytes = 0;
-        gemv_geometry(a, e->esz, kStageTarget);
-        StepPhase ph = {};
-        ph.type = kPhaseGemv;
-        ph.epi = epi;
-        ph.g = a;
-        record_phase(R, ph);
-        return;
-    }
     if (kind_skipped(e, kind)) return;
     a.st = e->st;
-    if (const char* dbg = getenv("LPP_DEBUG_GEMV")) a.debug = (int)strtol(dbg, nullptr, 0);
-    if (getenv("LPP_GEMV_TRACE")) {
+    if (const char* dbg = aid_env("LPP_DEBUG_GEMV")) a.debug = (int)strtol(dbg, nullptr, 0);
+    if (aid_env("LPP_GEMV_TRACE")) {
         if (e->gtrace && R.kernels < 256) a.trace = e->gtrace + (size_t)R.kernels * e->num_sms * 8;
     }
     a.vocab = e->c.vocab_size;
@@ -476,8 +393,7 @@ static void record_gemv(Recorder& R, int kind, int epi, GemvArgs a) {
 
 static void record_allreduce(Recorder& R, float* buf, int n) {
     lpp_engine* e = R.e;
-    flush_phases(R);
-    if (R.collect || kind_skipped(e, kAllReduce)) return;
+    if (kind_skipped(e, kAllReduce)) return;
     R.mark(kAllReduce);
     nccl::result_t r = nccl::AllReduce(buf, buf, (size_t)n, nccl::kFloat32, nccl::kSum, e->comm, R.s);
     if (r != 0 && R.err == cudaSuccess) {
@@ -494,7 +410,7 @@ static unsigned int* tp_epoch_word(const lpp_engine* e);
 
 // The fused sampler: exact-order kernel by default, tree kernel when asked for or when the vocabulary
 // needs more blocks than can be co-resident.
-static cudaError_t launch_sampler(lpp_engine* e, cudaStream_t s, bool pdl, bool zero_gbar, bool end_of_step = false) {
+static cudaError_t launch_sampler(lpp_engine* e, cudaStream_t s, bool pdl, bool end_of_step = false) {
     SampleArgs a = {};
     a.logits = e->logits;
     a.vocab = e->c.vocab_size;
@@ -505,8 +421,6 @@ static cudaError_t launch_sampler(lpp_engine* e, cudaStream_t s, bool pdl, bool 
     a.counter = e->samp_counter;
     a.r_values = e->r_values;
     a.out_tokens = e->out_tokens;
-    a.zero = zero_gbar ? e->gbar : nullptr;
-    a.zero_n = zero_gbar ? e->n_gbar : 0;
     a.bump = (end_of_step && tp_peer_path(e)) ? tp_epoch_word(e) : nullptr;
     if (e->exact_sampler) {
         SampleExactArgs ea = {};
@@ -553,7 +467,7 @@ static void set_prefetch(const lpp_engine* e, GemvArgs& a, int kind, int l) {
         default: nk = kQkv; nl = 0; break;
     }
     size_t cap = 8;
-    if (const char* v = getenv("LPP_PF_MB")) cap = (size_t)std::max(0, atoi(v));
+    if (const char* v = aid_env("LPP_PF_MB")) cap = (size_t)std::max(0, atoi(v));
     const void* p;
     size_t bytes;
     matrix_span(e, nk, nl, &p, &bytes);
@@ -576,7 +490,7 @@ static unsigned int* tp_hint(const lpp_engine* e, int p, int ex) { return reinte
 // three ranks on (LPP_TP_HINT=0/1 overrides).
 static bool tp_use_hint(const lpp_engine* e) {
     if (2 * e->c.n_layers > 192) return false;
-    if (const char* v = getenv("LPP_TP_HINT")) return atoi(v) != 0;
+    if (const char* v = aid_env("LPP_TP_HINT")) return atoi(v) != 0;
     return e->c.tp_size > 2;
 }
 static unsigned int tp_hint_per_step(const lpp_engine* e) {
@@ -585,7 +499,7 @@ static unsigned int tp_hint_per_step(const lpp_engine* e) {
 }
 // (a single-kind timing run must not take part in exchanges: its producers would have no consumers)
 static bool tp_peer_path(const lpp_engine* e) {
-    return e->c.tp_size > 1 && e->peer_ready && !e->persistent && e->only_kind < 0 &&
+    return e->c.tp_size > 1 && e->peer_ready && e->only_kind < 0 &&
            !(e->c.flags & (LPP_FLAG_GEMV_LDG | LPP_FLAG_TP_NCCL));
 }
 // producer side: exchange `ex` takes the rows of this residual GEMV
@@ -613,7 +527,7 @@ static void tp_set_consumer(const lpp_engine* e, GemvArgs& a, int ex, float* x_s
 // vocab/tp logits and stores them, as flagged words, into every rank's logits area (after the
 // exchange areas of the buffer); a small kernel turns the words into the float logits the sampler reads.
 static bool tp_cls_sharded(const lpp_engine* e) {
-    return tp_peer_path(e) && e->c.vocab_size % (kRowsPerGroup * e->c.tp_size) == 0 && !getenv("LPP_TP_FULL_CLS");
+    return tp_peer_path(e) && e->c.vocab_size % (kRowsPerGroup * e->c.tp_size) == 0 && !aid_env("LPP_TP_FULL_CLS");
 }
 static unsigned long long* tp_logits_area(const lpp_engine* e, int p) {
     return reinterpret_cast<unsigned long long*>(e->peer_base[p] + tp_header_bytes() + (size_t)2 * e->c.n_layers * tp_area_bytes(e));
@@ -630,7 +544,7 @@ static __global__ void __launch_bounds__(256) tp_unpack_logits_kernel(const unsi
     const int i = (blockIdx.x * 256 + threadIdx.x) * 4;
     if (i >= n) return;
     unsigned long long w[4];
-    long long t0 = 0;
+    long long t0 = 0, limit = 0;
     while (true) {
         asm volatile("ld.volatile.global.v2.u64 {%0,%1}, [%2];" : "=l"(w[0]), "=l"(w[1]) : "l"(words + i) : "memory");
         asm volatile("ld.volatile.global.v2.u64 {%0,%1}, [%2];" : "=l"(w[2]), "=l"(w[3]) : "l"(words + i + 2) : "memory");
@@ -639,9 +553,10 @@ static __global__ void __launch_bounds__(256) tp_unpack_logits_kernel(const unsi
         for (int q = 0; q < 4; ++q) pending |= (i + q < n) && (unsigned int)(w[q] >> 32) != flag;
         if (!pending) break;
         if (t0 == 0) {
-            if (*reinterpret_cast<volatile int*>(&st->status) & kStatusBarrierTimeout) break;
+            if (status_timed_out(st)) break;
             t0 = clock64();
-        } else if (clock64() - t0 > kTpWaitCycles) {
+            limit = tp_wait_limit(st);
+        } else if (clock64() - t0 > limit) {
             atomicOr(&st->status, kStatusBarrierTimeout);
             break;
         }
@@ -705,20 +620,15 @@ static void record_step(Recorder& R, bool with_sampler) {
             at.gqa = e->gqa;
             at.n_splits = e->attn_splits;
             at.n_kv_heads = e->KVHl;
-            if (const char* mc = getenv("LPP_ATTN_CHUNK")) at.min_chunk = atoi(mc);  // timing experiments
+            if (const char* mc = aid_env("LPP_ATTN_CHUNK")) at.min_chunk = atoi(mc);  // timing experiments
             {
                 set_prefetch(e, a, kQkv, l);
                 record_gemv(R, kQkv, kEpiQkv, a);
                 dim3 grid(e->attn_splits, e->KVHl, e->attn_z);
-                if (e->persistent) {
-                    StepPhase ph = {};
-                    ph.type = kPhaseAttn;
-                    ph.at = at;
-                    record_phase(R, ph);
-                } else if (!kind_skipped(e, kAttn)) {
+                if (!kind_skipped(e, kAttn)) {
                     if (e->gtrace && R.kernels < 256) at.trace = e->gtrace + (size_t)R.kernels * e->num_sms * 8;
                     R.mark(kAttn);
-                    if (attn_mma_supported(e) && !getenv("LPP_ATTN_CUDA_CORES")) {
+                    if (attn_mma_supported(e) && !aid_env("LPP_ATTN_CUDA_CORES")) {
                         at.n_splits = e->attn_splits_long;
                         R.check(launch_attn_mma(e, at, R.pdl(), R.s), "attention (tensor-core) launch");
                     } else {
@@ -805,13 +715,6 @@ static void record_step(Recorder& R, bool with_sampler) {
             R.kernels++;
         }
     }
-    flush_phases(R);
-    if (R.collect) return;
-    if (e->persistent && !with_sampler && e->n_gbar > 0) {
-        // no sampler in this graph to clear the grid-barrier counters: a memset node does it
-        R.check(cudaMemsetAsync(e->gbar, 0, (size_t)e->n_gbar * sizeof(unsigned int), R.s), "gbar memset");
-        R.prev_kernel = false;
-    }
     if (!with_sampler && tp_peer_path(e)) {
         // no sampler in this graph to end the step: a one-thread kernel bumps the exchange epoch
         R.check(launch_kernel(tp_bump_kernel, dim3(1), dim3(1), 0, R.s, R.pdl(), tp_epoch_word(e)), "epoch bump launch");
@@ -819,7 +722,7 @@ static void record_step(Recorder& R, bool with_sampler) {
     }
     if (with_sampler && !kind_skipped(e, kSampler)) {
         R.mark(kSampler);
-        R.check(launch_sampler(e, R.s, R.pdl(), e->persistent, true), "sampler launch");
+        R.check(launch_sampler(e, R.s, R.pdl(), true), "sampler launch");
         R.mark(-1);
         R.prev_kernel = true;
         R.kernels++;
@@ -890,7 +793,10 @@ extern "C" lpp_status lpp_engine_create(const lpp_config* cfg, const void* nccl_
     const int Dq = c.dim / c.tp_size;
     if (c.dim % vec || Fl % vec || Dq % vec || (c.vocab_size & 1) || (Fl & 1))
         return fail(LPP_ERR_INVALID_ARG, "dim/hidden/vocab not multiples of the vector width");
-    if (c.tp_size > 1 && !nccl_id) return fail(LPP_ERR_INVALID_ARG, "tp_size > 1 needs an nccl id");
+    if (c.tp_size > 1 && !nccl_id && !(c.flags & LPP_FLAG_TP_LOCAL))
+        return fail(LPP_ERR_INVALID_ARG, "tp_size > 1 needs an nccl id (or LPP_FLAG_TP_LOCAL)");
+    if ((c.flags & LPP_FLAG_TP_LOCAL) && c.tp_size > kMaxTp)
+        return fail(LPP_ERR_INVALID_ARG, "LPP_FLAG_TP_LOCAL supports at most %d ranks", kMaxTp);
 
     int ndev = 0;
     if (cudaGetDeviceCount(&ndev) != cudaSuccess || ndev == 0) {
@@ -987,6 +893,12 @@ extern "C" lpp_status lpp_engine_create(const lpp_config* cfg, const void* nccl_
     CUB(cudaMemsetAsync(e->st, 0, sizeof(StepState), e->stream));
     CUB(cudaMallocHost(&e->h_st, sizeof(StepState)));
     memset(e->h_st, 0, sizeof(StepState));
+    {
+        int khz = 0;  // SM clock in kHz = clocks per millisecond
+        CUB(cudaDeviceGetAttribute(&khz, cudaDevAttrClockRate, c.device));
+        e->h_st->wait_cycles = c.wait_ms > 0 ? (long long)c.wait_ms * khz : 0;
+        e->h_st->tp_wait_cycles = c.tp_wait_ms > 0 ? (long long)c.tp_wait_ms * khz : 0;
+    }
     CUB(cudaMallocHost(&e->h_out, 16));
 
     TRACE("create: buffers allocated");
@@ -1009,11 +921,13 @@ extern "C" lpp_status lpp_engine_create(const lpp_config* cfg, const void* nccl_
     }
 
     if (c.tp_size > 1) {
-        if (!nccl::load()) return bail(fail(LPP_ERR_NCCL, "cannot load libnccl.so.2: %s", dlerror()));
-        nccl::unique_id id;
-        memcpy(&id, nccl_id, sizeof id);
-        nccl::result_t r = nccl::CommInitRank(&e->comm, c.tp_size, id, c.tp_rank);
-        if (r != 0) return bail(fail(LPP_ERR_NCCL, "ncclCommInitRank: %s", nccl::GetErrorString(r)));
+        if (!(c.flags & LPP_FLAG_TP_LOCAL)) {
+            if (!nccl::load()) return bail(fail(LPP_ERR_NCCL, "cannot load libnccl.so.2: %s", dlerror()));
+            nccl::unique_id id;
+            memcpy(&id, nccl_id, sizeof id);
+            nccl::result_t r = nccl::CommInitRank(&e->comm, c.tp_size, id, c.tp_rank);
+            if (r != 0) return bail(fail(LPP_ERR_NCCL, "ncclCommInitRank: %s", nccl::GetErrorString(r)));
+        }
         if (c.tp_size <= kMaxTp) {
             // receive areas and counters of the peer-memory exchange (used once lpp_tp_connect has mapped the peers)
             e->tp_buf_bytes = tp_header_bytes() + (size_t)2 * c.n_layers * tp_area_bytes(e) +
@@ -1040,12 +954,13 @@ extern "C" lpp_status lpp_engine_destroy(lpp_engine* e) {
     }
     if (e->comm) nccl::CommDestroy(e->comm);
     for (int p = 0; p < kMaxTp; ++p)
-        if (e->peer_base[p] && p != e->c.tp_rank) cudaIpcCloseMemHandle(e->peer_base[p]);
+        if (e->peer_base[p] && p != e->c.tp_rank && e->peer_base[p] != e->absent_peer) cudaIpcCloseMemHandle(e->peer_base[p]);
+    if (e->absent_peer) cudaFree(e->absent_peer);
     if (e->tp_buf) cudaFree(e->tp_buf);
     void* bufs[] = {e->wqkv, e->wo, e->w13, e->w2, e->emb, e->wcls_owned ? e->wcls : nullptr, e->rms_att, e->rms_ffn,
                     e->rms_final, e->kcache, e->vcache, e->xa, e->xb, e->q, e->att_out, e->hb, e->logits,
                     e->attn_part, e->attn_counters, e->samp_max, e->samp_sum, e->samp_idx, e->samp_counter,
-                    e->r_values, e->out_tokens, e->st, e->rope, e->stage, e->d_phases, e->gbar, e->trace, e->ex_sync, e->ex_block_sum, e->ex_entry_count, e->ex_entries, e->ex_scalars};
+                    e->r_values, e->out_tokens, e->st, e->rope, e->stage, e->gtrace, e->ex_sync, e->ex_block_sum, e->ex_entry_count, e->ex_entries, e->ex_scalars};
     for (void* p : bufs)
         if (p) cudaFree(p);
     if (e->h_st) cudaFreeHost(e->h_st);
@@ -1188,6 +1103,8 @@ extern "C" lpp_status lpp_finalize(lpp_engine* e) {
             if (!e->got[(size_t)t * c.n_layers + l])
                 return fail(LPP_ERR_NOT_READY, "tensor %s (layer %d) was never uploaded", names[t], l);
     }
+    if (c.tp_size > 1 && !e->comm && !tp_peer_path(e))
+        return fail(LPP_ERR_NOT_READY, "a tensor-parallel engine without NCCL (LPP_FLAG_TP_LOCAL) needs lpp_tp_connect");
     if (!e->wcls_owned) e->wcls = e->emb;  // tied classifier (src/loader.cpp:66, 471)
     if (e->stage) {
         cudaFree(e->stage);
@@ -1199,40 +1116,9 @@ extern "C" lpp_status lpp_finalize(lpp_engine* e) {
         if (e->g_logits[v]) cudaGraphExecDestroy(e->g_logits[v]), e->g_logits[v] = nullptr;
     }
     TRACE("finalize: weights complete");
-    // ---- persistent step kernel: phase table, ring/scratch geometry, grid-barrier counters
-    e->persistent = (c.flags & LPP_FLAG_PERSISTENT) && !(c.flags & LPP_FLAG_GEMV_LDG) && step_kernel_supported(e);
-    if (e->persistent) {
-        int maxK = std::max(c.dim, std::max(e->Fl, e->Dq));
-        const size_t attn_scratch = 2ull * (kAttnThreads / 32) * e->attn_gb * (e->hs + 2) * sizeof(float);
-        e->step_xs_bytes = (int)align_up(std::max((size_t)maxK * 4, attn_scratch), 128);
-        const size_t fixed = kGemvBarrierBytes + 128 + e->step_xs_bytes;
-        size_t ring = (size_t)(c.ring_kb > 0 ? c.ring_kb : 128) * 1024;
-        if (fixed + ring > e->smem_optin) ring = e->smem_optin - fixed;
-        e->step_slots = std::max(2, std::min((int)(ring / ((size_t)kGemvConsumerWarps * kStageTarget)), kGemvMaxStages));
-        e->step_smem = fixed + (size_t)kGemvConsumerWarps * e->step_slots * kStageTarget;
-        if (e->step_smem > e->smem_optin) e->persistent = false;
-    }
-    if (getenv("LPP_GEMV_TRACE") && !e->gtrace) {
+    if (aid_env("LPP_GEMV_TRACE") && !e->gtrace) {
         CU(cudaMalloc(&e->gtrace, (size_t)256 * e->num_sms * 8 * sizeof(unsigned long long)));
         CU(cudaMemset(e->gtrace, 0, (size_t)256 * e->num_sms * 8 * sizeof(unsigned long long)));
-    }
-    if (e->persistent) {
-        e->h_phases.clear();
-        Recorder R{e, e->stream};
-        R.collect = true;
-        record_step(R, true);
-        if (e->d_phases) cudaFree(e->d_phases);
-        CU(cudaMalloc(&e->d_phases, e->h_phases.size() * sizeof(StepPhase)));
-        CU(cudaMemcpy(e->d_phases, e->h_phases.data(), e->h_phases.size() * sizeof(StepPhase), cudaMemcpyHostToDevice));
-        e->n_gbar = c.tp_size > 1 ? 2 * c.n_layers + 1 : 1;
-        if (e->gbar) cudaFree(e->gbar);
-        CU(cudaMalloc(&e->gbar, (size_t)e->n_gbar * sizeof(unsigned int)));
-        CU(cudaMemset(e->gbar, 0, (size_t)e->n_gbar * sizeof(unsigned int)));
-        if (getenv("LPP_STEP_TRACE") && !e->trace) {
-            CU(cudaMalloc(&e->trace, (size_t)e->num_sms * e->h_phases.size() * 4 * sizeof(unsigned long long)));
-            CU(cudaMemset(e->trace, 0, (size_t)e->num_sms * e->h_phases.size() * 4 * sizeof(unsigned long long)));
-        }
-        TRACE("finalize: persistent step kernel, %zu phases, %d slots/warp, %zu B smem", e->h_phases.size(), e->step_slots, e->step_smem);
     }
     if (!(c.flags & LPP_FLAG_NO_GRAPH)) {
         for (int v = 0; v < 1; ++v) {
@@ -1241,7 +1127,7 @@ extern "C" lpp_status lpp_finalize(lpp_engine* e) {
         }
         TRACE("finalize: graphs captured (%d kernels per long-context step)", e->kernels_full);
     } else {
-        e->kernels_full = e->persistent ? (c.tp_size > 1 ? 2 * c.n_layers + 2 : 2) : 5 * c.n_layers + 2 + (tp_cls_sharded(e) ? 1 : 0);
+        e->kernels_full = 5 * c.n_layers + 2 + (tp_cls_sharded(e) ? 1 : 0);
     }
     e->finalized = true;
     return LPP_OK;
@@ -1336,7 +1222,7 @@ extern "C" lpp_status lpp_sample_logits(lpp_engine* e, const float* h_logits, co
     if (!h_logits || !sp || !token) return fail(LPP_ERR_INVALID_ARG, "null argument");
     TRY(push_state(e, 0, 0, sp, h_history, history_len, r, 0, 0));
     CU(cudaMemcpyAsync(e->logits, h_logits, (size_t)e->c.vocab_size * 4, cudaMemcpyHostToDevice, e->stream));
-    CU(launch_sampler(e, e->stream, false, false));
+    CU(launch_sampler(e, e->stream, false));
     return pull_result(e, token);
 }
 
@@ -1397,8 +1283,6 @@ extern "C" lpp_status lpp_kv_read(lpp_engine* e, int layer, int kv_head, int pos
 
 // ------------------------------------------------------------------ introspection
 
-// Timing aid (not part of the public header): copies the time stamps the step kernel left when the
-// engine was finalized with LPP_STEP_TRACE set; n_out = ctas * phases * 4 values.
 // ---- tensor-parallel peer mapping ---------------------------------------------------------------
 
 static_assert(sizeof(cudaIpcMemHandle_t) == LPP_TP_HANDLE_BYTES, "IPC handle size");
@@ -1436,6 +1320,46 @@ extern "C" lpp_status lpp_tp_connect(lpp_engine* e, const void* handles, size_t 
     return LPP_OK;
 }
 
+// Test aid (not part of the public header): lets ONE rank of a tensor-parallel group run without its peers.
+// Stores to the other ranks land in a private scratch buffer and nobody ever fills this rank's receive slots,
+// so the first consuming GEMV's wait on its peers runs out after lpp_config.tp_wait_ms and the step ends
+// with LPP_ERR_DEVICE_STATUS: the one way to see that path on a single GPU without a fault or a hang.
+extern "C" lpp_status lpp_debug_tp_absent_peers(lpp_engine* e) {
+    if (!e) return fail(LPP_ERR_INVALID_ARG, "null argument");
+    if (!e->tp_buf) return fail(LPP_ERR_INVALID_ARG, "engine has no tensor-parallel exchange buffer");
+    if (e->finalized) return fail(LPP_ERR_INVALID_ARG, "must precede lpp_finalize");
+    CU(cudaSetDevice(e->c.device));
+    if (!e->absent_peer) {
+        CU(cudaMalloc(&e->absent_peer, e->tp_buf_bytes));
+        CU(cudaMemset(e->absent_peer, 0, e->tp_buf_bytes));
+    }
+    for (int p = 0; p < e->c.tp_size; ++p)
+        if (p != e->c.tp_rank && !e->peer_base[p]) e->peer_base[p] = e->absent_peer;
+    e->peer_ready = true;
+    return LPP_OK;
+}
+
+// Test aid (not part of the public header): one warp waits, with the engine's wait limit, on a shared-memory
+// barrier that nothing ever arrives on.  The wait must run out, the kernel must return normally, and the
+// call must fail with LPP_ERR_DEVICE_STATUS like a step whose copy never completed.
+static __global__ void wait_probe_kernel(StepState* st) {
+    __shared__ uint64_t bar;
+    if (threadIdx.x == 0) {
+        mbar_init(&bar, 1);
+        mbar_fence_init();
+    }
+    __syncthreads();
+    const bool ok = __all_sync(0xffffffffu, mbar_wait_bounded(&bar, 0u, st));
+    if (!ok && threadIdx.x == 0) st->out_token = -2;
+}
+extern "C" lpp_status lpp_debug_wait_probe(lpp_engine* e) {
+    NEED_READY(e);
+    TRY(push_state(e, 0, 0, nullptr, nullptr, 0, 0.f, 0, 0));
+    wait_probe_kernel<<<1, 32, 0, e->stream>>>(e->st);
+    CU(cudaGetLastError());
+    return pull_result(e, nullptr);
+}
+
 // Debugging aid (not part of the public header): per-CTA time stamps of the ring GEMV launches of one step.
 extern "C" int lpp_debug_gemv_trace(lpp_engine* e, unsigned long long* out, int max_values) {
     if (!e || !e->gtrace || !out) return -1;
@@ -1444,17 +1368,6 @@ extern "C" int lpp_debug_gemv_trace(lpp_engine* e, unsigned long long* out, int 
     cudaStreamSynchronize(e->stream);
     if (cudaMemcpy(out, e->gtrace, n * sizeof(unsigned long long), cudaMemcpyDeviceToHost) != cudaSuccess) return -3;
     return e->num_sms;
-}
-
-extern "C" int lpp_debug_step_trace(lpp_engine* e, unsigned long long* out, int max_values, int* ctas, int* phases) {
-    if (!e || !e->trace || !out) return -1;
-    const size_t n = (size_t)e->num_sms * e->h_phases.size() * 4;
-    if ((size_t)max_values < n) return -2;
-    cudaStreamSynchronize(e->stream);
-    if (cudaMemcpy(out, e->trace, n * sizeof(unsigned long long), cudaMemcpyDeviceToHost) != cudaSuccess) return -3;
-    *ctas = e->num_sms;
-    *phases = (int)e->h_phases.size();
-    return (int)n;
 }
 
 // Debugging aid (not part of the public header): the exact sampler's entry lists of its last stage.
@@ -1512,7 +1425,6 @@ extern "C" lpp_status lpp_profile_kind(lpp_engine* e, int pos, int kind, int ite
     NEED_READY(e);
     if (!ms_per_launch || !launches || iters <= 0 || kind < 0 || kind >= kKinds) return fail(LPP_ERR_INVALID_ARG, "bad argument");
     if (pos < 0 || pos >= e->c.seq_len) return fail(LPP_ERR_INVALID_ARG, "pos out of range");
-    if (e->persistent) return fail(LPP_ERR_INVALID_ARG, "not available with the persistent step kernel");
     *ms_per_launch = 0.f;
     *launches = 0;
     lpp_sample_params sp = {0.8f, 1.1f};
@@ -1550,19 +1462,16 @@ extern "C" lpp_status lpp_profile_kind(lpp_engine* e, int pos, int kind, int ite
     return rs;
 }
 
-extern "C" lpp_status lpp_profile_step(lpp_engine* e, int pos, int iters, float* ms, int* launches, int64_t* bytes) {
+extern "C" lpp_status lpp_profile_step(lpp_engine* e, int pos, int iters, const lpp_sample_params* spp, float* ms,
+                                       int* launches, int64_t* bytes) {
     NEED_READY(e);
     if (!ms || !launches || !bytes || iters <= 0) return fail(LPP_ERR_INVALID_ARG, "bad argument");
     if (pos < 0 || pos >= e->c.seq_len) return fail(LPP_ERR_INVALID_ARG, "pos out of range");
     for (int k = 0; k < kKinds; ++k) ms[k] = 0.f, launches[k] = 0;
     kind_bytes(e, pos, bytes);
-    if (e->persistent) {  // one launch covers the GEMV and attention phases
-        for (int k = kQkv; k <= kLmHead; ++k) {
-            bytes[kStepKernel] += bytes[k];
-            bytes[k] = 0;
-        }
-    }
-    lpp_sample_params sp = {0.f, 1.f};
+    // the sampler that is timed is the one the caller's workload runs (argmax and categorical paths differ)
+    const lpp_sample_params sp = spp ? *spp : lpp_sample_params{0.f, 1.f};
+    const int hist[3] = {1, 2, 3};
     // The step is captured once more with an event-record node before and after every kernel and
     // replayed as a graph, so the durations carry no host launch latency.  Event nodes sit between
     // the kernels, hence no programmatic overlap: these are isolated per-kernel times.
@@ -1585,7 +1494,7 @@ extern "C" lpp_status lpp_profile_step(lpp_engine* e, int pos, int iters, float*
         (void)cudaGetLastError();
     }
     for (int it = 0; it < iters + 1 && rs == LPP_OK; ++it) {  // iteration 0 is a warm-up
-        rs = push_state(e, 0, pos, &sp, nullptr, 0, 0.f, 0, 0);
+        rs = push_state(e, 0, pos, &sp, hist, 3, 0.5f, 0, 0);
         if (rs != LPP_OK) break;
         cudaError_t le = cudaGraphLaunch(gx, e->stream);
         cudaError_t se = cudaStreamSynchronize(e->stream);

@@ -12,6 +12,7 @@
 #include "gemv.cuh"
 #include "ops.cuh"
 #include "sampler.cuh"
+#include "sampler_exact.cuh"
 
 using namespace lpp;
 
@@ -48,7 +49,10 @@ template <typename WT>
 lpp_status op_gemv_t(float* out, const float* x, const void* w, int n, int d, cudaStream_t s) {
     const int vec = 16 / (int)sizeof(WT);
     const size_t smem = 128 + (((size_t)d * 4 + 127) & ~(size_t)127);
-    if ((n & 1) || (d % vec) || (((uintptr_t)w) & 15) || smem > 200 * 1024) {
+    // the vector kernel stages x with 16-byte loads, reads the rows with 16-byte loads and stores row pairs
+    // with 8-byte stores: anything else (an offset sub-vector, say) takes the scalar kernel
+    if ((n & 1) || (d % vec) || (((uintptr_t)w) & 15) || (((uintptr_t)x) & 15) || (((uintptr_t)out) & 7) ||
+        smem > 200 * 1024) {
         gemv_generic_kernel<WT><<<blocks(n, 8), 256, 0, s>>>(out, x, (const WT*)w, n, d);
         return chk();
     }
@@ -100,6 +104,8 @@ static __global__ void sample_static_setup_kernel(StepState* st, unsigned int* c
         st->r = r;
         st->out_token = -1;
         st->status = 0;
+        st->wait_cycles = 0;
+        st->tp_wait_cycles = 0;
         *counter = 0u;
     }
     for (int i = threadIdx.x; i < history_len; i += blockDim.x) st->history[i] = history[i];
@@ -215,9 +221,19 @@ lpp_status lpp_op_sample(float* d_logits, int vocab_size, float temperature, flo
     cudaStream_t s = S(stream);
     const int nb = (vocab_size + kSampleChunk - 1) / kSampleChunk;
     if (nb > kSampleMaxBlocks) return LPP_ERR_TOO_LARGE;
-    // stream-ordered scratch: step state + per-block partials + ticket counter
+    int dev = 0, sms = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
+        return LPP_ERR_CUDA;
+    // The exact-order kernel (ids equal to the reference's sequential CPU sample()) needs all its blocks
+    // co-resident; a vocabulary beyond that (more than 2048 logits per SM) takes the tree-sum kernel.
+    const bool exact = nb <= sms;
+    // stream-ordered scratch: step state + per-block partials + ticket counter (+ the exact kernel's lists)
     const size_t st_bytes = (sizeof(StepState) + 255) & ~(size_t)255;
-    const size_t bytes = st_bytes + (size_t)nb * 12 + 256;
+    const size_t part_bytes = ((size_t)nb * 12 + 255) & ~(size_t)255;
+    const size_t sum_bytes = ((size_t)nb * sizeof(double) + 255) & ~(size_t)255;
+    const size_t cnt_bytes = ((size_t)nb * sizeof(int) + 255) & ~(size_t)255;
+    const size_t ent_bytes = (size_t)nb * kExactMaxEntries * sizeof(ExactEntry);
+    const size_t bytes = st_bytes + part_bytes + 256 + (exact ? 256 + sum_bytes + cnt_bytes + 256 + ent_bytes : 0);
     char* scratch = nullptr;
     if (cudaMallocAsync((void**)&scratch, bytes, s) != cudaSuccess) return LPP_ERR_CUDA;
     StepState h = {};
@@ -237,9 +253,21 @@ lpp_status lpp_op_sample(float* d_logits, int vocab_size, float temperature, flo
     a.part_max = (float*)(scratch + st_bytes);
     a.part_idx = (int*)(scratch + st_bytes + (size_t)nb * 4);
     a.part_sum = (float*)(scratch + st_bytes + (size_t)nb * 8);
-    a.counter = (unsigned int*)(scratch + st_bytes + (size_t)nb * 12);
-    cudaMemsetAsync(a.counter, 0, 4, s);
-    sample_kernel<<<nb, kSampleThreads, 0, s>>>(a);
+    a.counter = (unsigned int*)(scratch + st_bytes + part_bytes);
+    cudaMemsetAsync(a.counter, 0, exact ? 512 : 256, s);  // ticket counter (+ the exact kernel's barrier words)
+    if (exact) {
+        char* p = scratch + st_bytes + part_bytes + 256;
+        SampleExactArgs ea = {};
+        ea.base = a;
+        ea.sync = (unsigned int*)p;
+        ea.block_sum = (double*)(p + 256);
+        ea.entry_count = (int*)(p + 256 + sum_bytes);
+        ea.scalars = (float*)(p + 256 + sum_bytes + cnt_bytes);
+        ea.entries = (ExactEntry*)(p + 256 + sum_bytes + cnt_bytes + 256);
+        sample_exact_kernel<<<nb, kSampleThreads, 0, s>>>(ea);
+    } else {
+        sample_kernel<<<nb, kSampleThreads, 0, s>>>(a);
+    }
     cudaMemcpyAsync(d_sampled_token, scratch + offsetof(StepState, out_token), sizeof(int), cudaMemcpyDeviceToDevice, s);
     cudaFreeAsync(scratch, s);
     return chk();

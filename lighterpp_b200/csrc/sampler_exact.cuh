@@ -128,10 +128,11 @@ __device__ __forceinline__ bool sampler_grid_barrier(unsigned int* counter, unsi
         asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(counter) : "memory");
         if (v < target) {
             const long long t0 = clock64();
+            const long long limit = wait_limit(st);
             while (true) {
                 asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(counter) : "memory");
                 if (v >= target) break;
-                if (clock64() - t0 > kWaitCycles) {
+                if (clock64() - t0 > limit) {
                     atomicOr(&st->status, kStatusBarrierTimeout);
                     ok = false;
                     break;
@@ -211,7 +212,7 @@ __device__ __forceinline__ double block_sum_double(double v, double* s_warp, int
 // Stage helper: every thread owns four consecutive values x[0..3] (element indices base+4*tid+k,
 // zero past the end).  Given the approximate prefix `pre` (double, exclusive) before the quad, the
 // block writes its entry list for the sequential sum of these values.
-__device__ __noinline__ void emit_entries(const float (&x)[4], double pre, int first_elem, int n_valid_quads,
+static __device__ __noinline__ void emit_entries(const float (&x)[4], double pre, int first_elem, int n_valid_quads,
                                              ExactEntry* out, int* out_count, Map2* s_wm, int* s_wf, int* s_i,
                                              int tid) {
     const int lane = tid & 31;
@@ -305,7 +306,7 @@ struct WalkState {
 // requested and the crossing was located).  A map moves the sum by an integer number of ulps inside
 // one binade (or exactly onto the next power of two), which on the bit pattern of a positive float
 // is a plain integer addition.
-__device__ __noinline__ bool walk_list(const ExactEntry* list, int count, const float* x, int n_total,
+static __device__ __noinline__ bool walk_list(const ExactEntry* list, int count, const float* x, int n_total,
                                           const bool kStop, float r, int lane, WalkState& w) {
     unsigned int bits = __float_as_uint(w.s);
     int4 nh = *reinterpret_cast<const int4*>(&list[0]);
@@ -373,7 +374,7 @@ __device__ __noinline__ bool walk_list(const ExactEntry* list, int count, const 
 // Whole-block walk.  The blocks' entry lists are concatenated in block order (a prefix sum of the
 // counts gives every entry its place), staged into shared memory kExactListCap at a time, and
 // applied by warp 0.  Returns the final state in *out (shared memory).
-__device__ __noinline__ void walk_all(const ExactEntry* entries, const int* counts, int n_blocks, const float* x,
+static __device__ __noinline__ void walk_all(const ExactEntry* entries, const int* counts, int n_blocks, const float* x,
                                          int n_total, bool stop, float r, ExactEntry* s_list, int* s_pref, int* s_i,
                                          WalkState* out, int tid) {
     static_assert(kSampleMaxBlocks <= kSampleThreads, "one thread per block's count");

@@ -20,14 +20,14 @@ LIB_PATH = os.path.join(_HERE, "liblpp_b200.so")
 
 LPP_F32, LPP_F16 = 0, 1
 MEM_HOST, MEM_DEVICE = 0, 1
-FLAG_GEMV_LDG, FLAG_NO_PDL, FLAG_NO_GRAPH, FLAG_PERSISTENT, FLAG_FAST_SAMPLER = 1, 2, 4, 8, 16
+FLAG_GEMV_LDG, FLAG_NO_PDL, FLAG_NO_GRAPH, FLAG_FAST_SAMPLER = 1, 2, 4, 16
 TENSOR_IDS = {"tok_emb": 0, "rms_att": 1, "wq": 2, "wk": 3, "wv": 4, "wo": 5, "rms_ffn": 6, "w1": 7, "w2": 8,
               "w3": 9, "rms_final": 10, "w_cls": 11}
 _UNSTACKED = ("tok_emb", "rms_final", "w_cls")
 TP_HANDLE_BYTES = 64
-FLAG_TP_NCCL = 32
+FLAG_TP_NCCL, FLAG_TP_LOCAL = 32, 64
 KINDS = ["qkv_gemv", "attention", "oproj_gemv", "gateup_gemv", "down_gemv", "lmhead_gemv", "sampler", "allreduce",
-         "step_kernel", "reserved"]
+         "reserved8", "reserved9"]
 
 # every symbol include/lpp_b200.h declares; tests check the built library exports all of them
 EXPORTS = [
@@ -52,7 +52,7 @@ class Config(C.Structure):
                 ("n_kv_heads", C.c_int32), ("vocab_size", C.c_int32), ("seq_len", C.c_int32),
                 ("rope_base", C.c_float), ("weight_dtype", C.c_int32), ("kv_dtype", C.c_int32),
                 ("tp_rank", C.c_int32), ("tp_size", C.c_int32), ("device", C.c_int32), ("flags", C.c_uint32),
-                ("ring_kb", C.c_int32), ("attn_splits", C.c_int32)]
+                ("ring_kb", C.c_int32), ("attn_splits", C.c_int32), ("wait_ms", C.c_int32), ("tp_wait_ms", C.c_int32)]
 
 
 class SampleParams(C.Structure):
@@ -95,7 +95,7 @@ def load_library() -> C.CDLL:
     lib.lpp_kernels_per_step.argtypes = [vp]
     lib.lpp_step_bytes.argtypes = [vp, C.c_int]
     lib.lpp_step_bytes.restype = C.c_int64
-    lib.lpp_profile_step.argtypes = [vp, C.c_int, C.c_int, fp, ip, C.POINTER(C.c_int64)]
+    lib.lpp_profile_step.argtypes = [vp, C.c_int, C.c_int, C.POINTER(SampleParams), fp, ip, C.POINTER(C.c_int64)]
     lib.lpp_profile_kind.argtypes = [vp, C.c_int, C.c_int, C.c_int, fp, ip]
     lib.lpp_tp_export.argtypes = [vp, vp, C.c_size_t]
     lib.lpp_tp_connect.argtypes = [vp, vp, C.c_size_t]
@@ -128,13 +128,13 @@ class Engine:
 
     def __init__(self, cfg: ModelConfig, weight_dtype: str = "f16", kv_dtype: str = "f16", *, device: int = 0,
                  tp_rank: int = 0, tp_size: int = 1, nccl_id: Optional[bytes] = None, flags: int = 0,
-                 ring_kb: int = 0, attn_splits: int = 0):
+                 ring_kb: int = 0, attn_splits: int = 0, wait_ms: int = 0, tp_wait_ms: int = 0):
         self.lib = load_library()
         self.cfg = cfg
         self.weight_dtype = {"f32": LPP_F32, "f16": LPP_F16}[weight_dtype]
         c = Config(cfg.dim, cfg.hidden_dim, cfg.n_layers, cfg.n_heads, cfg.n_kv_heads, cfg.vocab_size, cfg.seq_len,
                    cfg.rope_base, self.weight_dtype, {"f32": LPP_F32, "f16": LPP_F16}[kv_dtype], tp_rank, tp_size,
-                   device, flags, ring_kb, attn_splits)
+                   device, flags, ring_kb, attn_splits, wait_ms, tp_wait_ms)
         self.tp_rank, self.tp_size = tp_rank, tp_size
         h = C.c_void_p()
         idbuf = C.create_string_buffer(nccl_id, 128) if nccl_id is not None else None
@@ -259,11 +259,14 @@ class Engine:
     def step_bytes(self, pos: int) -> int:
         return int(self.lib.lpp_step_bytes(self.h, int(pos)))
 
-    def profile_step(self, pos: int, iters: int = 5) -> Dict[str, Dict[str, float]]:
+    def profile_step(self, pos: int, iters: int = 5, temperature: float = 0.0, penalty: float = 1.0
+                     ) -> Dict[str, Dict[str, float]]:
+        """Isolated per-kernel-kind durations of one step; the sampler runs with the given parameters."""
         ms = (C.c_float * 10)()
         n = (C.c_int * 10)()
         b = (C.c_int64 * 10)()
-        _check(self.lib.lpp_profile_step(self.h, int(pos), int(iters), ms, n, b), "lpp_profile_step")
+        sp = SampleParams(temperature, penalty)
+        _check(self.lib.lpp_profile_step(self.h, int(pos), int(iters), C.byref(sp), ms, n, b), "lpp_profile_step")
         return {KINDS[i]: {"ms": float(ms[i]), "launches": int(n[i]), "bytes": int(b[i])} for i in range(10)}
 
     def tp_export(self) -> bytes:

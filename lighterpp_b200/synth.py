@@ -66,17 +66,34 @@ def iter_tensors(c: ModelConfig, seed: int, dtype: str, tied: bool) -> Iterator[
             yield name, -1, gen_tensor(c, name, seed, dtype)
 
 
-def gen_model(c: ModelConfig, seed: int, dtype: str, tied: bool) -> Dict[str, np.ndarray]:
-    """The whole model as stacked arrays (matrices in ``dtype``, norms FP32)."""
+def gen_model(c: ModelConfig, seed: int, dtype: str, tied: bool, threads: int = 0) -> Dict[str, np.ndarray]:
+    """The whole model as stacked arrays (matrices in ``dtype``, norms FP32).  ``threads`` > 1 draws the
+    tensors of different layers on a thread pool (every tensor has its own generator, so the bytes do not
+    depend on the number of threads); the billion-parameter shapes need it to be generated in seconds."""
     shapes = tensor_shapes(c, tied)
     out: Dict[str, np.ndarray] = {}
-    for name, layer, a in iter_tensors(c, seed, dtype, tied):
-        if layer < 0:
-            out[name] = a
+    jobs = []
+    for name, shape in shapes.items():
+        stacked = len(shape) == 3 or (len(shape) == 2 and name in ("rms_att", "rms_ffn"))
+        dt = np.float32 if name in _NORMS else np_dtype(dtype)
+        out[name] = np.empty(shape, dtype=dt)
+        for l in (range(c.n_layers) if stacked else [-1]):
+            jobs.append((name, l))
+
+    def fill(job):
+        name, l = job
+        if l < 0:
+            out[name][...] = gen_tensor(c, name, seed, dtype)
         else:
-            if name not in out:
-                out[name] = np.empty(shapes[name], dtype=a.dtype)
-            out[name][layer] = a
+            out[name][l] = gen_tensor(c, name, seed, dtype, l)
+
+    if threads > 1:
+        from concurrent.futures import ThreadPoolExecutor
+        with ThreadPoolExecutor(threads) as pool:
+            list(pool.map(fill, jobs))
+    else:
+        for job in jobs:
+            fill(job)
     return out
 
 

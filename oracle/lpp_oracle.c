@@ -24,8 +24,11 @@
 typedef struct {
     int dim, hidden_dim, n_layers, n_heads, n_kv_heads, vocab_size, seq_len;
     float rope_base;
-    /* weights: caller-owned FP32, per-layer tensors stacked [L][rows][cols] (model.h:34-53) */
+    /* weights: caller-owned, per-layer tensors stacked [L][rows][cols] (model.h:34-53).  Matrices and
+     * embedding are FP32, or (w_f16 != 0) IEEE binary16 that is widened exactly on use -- the values the
+     * reference's GGUF loader produces with f16_to_f32 (loader.cpp:346-379) without holding them as FP32. */
     const float *tok_emb, *rms_att, *wq, *wk, *wv, *wo, *rms_ffn, *w1, *w2, *w3, *rms_final, *w_cls;
+    int w_f16;
     /* run state (model.h:78-95) */
     float *x, *xb, *xb2, *hb, *he, *q, *k, *v, *att, *logits;
     float *key_cache, *value_cache; /* [L][KVH][seq_len][head_size] FP32 */
@@ -40,6 +43,49 @@ void oracle_matmul(float* out, const float* x, const float* w, int n, int d) {
         for (int k = 0; k < d; k++) val += x[k] * row[k];
         out[i] = val;
     }
+}
+
+/* Exact binary16 -> binary32 widening (every half is representable as a float). */
+static inline float half_bits_to_float(uint16_t h) {
+    uint32_t s = ((uint32_t)h & 0x8000u) << 16, e = (h >> 10) & 31u, m = h & 1023u, b;
+    if (e == 0) {
+        if (m == 0) {
+            b = s;
+        } else { /* subnormal: m * 2^-24 */
+            int sh = 0;
+            while (!(m & 1024u)) {
+                m <<= 1;
+                sh++;
+            }
+            b = s | ((uint32_t)(113 - sh) << 23) | ((m & 1023u) << 13);
+        }
+    } else if (e == 31) {
+        b = s | 0x7f800000u | (m << 13);
+    } else {
+        b = s | ((e + 112u) << 23) | (m << 13);
+    }
+    float f;
+    memcpy(&f, &b, 4);
+    return f;
+}
+
+/* oracle_matmul on a binary16 matrix: the same sequential FP32 sum over the exactly widened weights. */
+void oracle_matmul_f16(float* out, const float* x, const uint16_t* w, int n, int d) {
+#pragma omp parallel for schedule(static) if (((long)n * d) > 262144)
+    for (int i = 0; i < n; i++) {
+        float val = 0.0f;
+        const uint16_t* row = w + (size_t)i * d;
+        for (int k = 0; k < d; k++) val += x[k] * half_bits_to_float(row[k]);
+        out[i] = val;
+    }
+}
+
+/* Matrix `w` (an oracle_model weight pointer) from element offset `off`, in the model's weight type. */
+static void model_matmul(const oracle_model* m, float* out, const float* x, const float* w, size_t off, int n, int d) {
+    if (m->w_f16)
+        oracle_matmul_f16(out, x, (const uint16_t*)w + off, n, d);
+    else
+        oracle_matmul(out, x, w + off, n, d);
 }
 
 /* ops.cpp:20-32 */
@@ -137,6 +183,7 @@ oracle_model* oracle_create(int dim, int hidden_dim, int n_layers, int n_heads, 
     m->w3 = w3;
     m->rms_final = rms_final;
     m->w_cls = w_cls ? w_cls : tok_emb;
+    m->w_f16 = 0;
     int kv_dim = (dim * n_kv_heads) / n_heads;
     m->x = (float*)calloc(dim, sizeof(float));
     m->xb = (float*)calloc(dim, sizeof(float));
@@ -151,6 +198,20 @@ oracle_model* oracle_create(int dim, int hidden_dim, int n_layers, int n_heads, 
     size_t kv = (size_t)n_layers * seq_len * kv_dim;
     m->key_cache = (float*)calloc(kv, sizeof(float));
     m->value_cache = (float*)calloc(kv, sizeof(float));
+    return m;
+}
+
+/* The same model over binary16 matrices / embedding (norm weights stay FP32). */
+oracle_model* oracle_create_f16(int dim, int hidden_dim, int n_layers, int n_heads, int n_kv_heads, int vocab_size,
+                                int seq_len, float rope_base, const uint16_t* tok_emb, const float* rms_att,
+                                const uint16_t* wq, const uint16_t* wk, const uint16_t* wv, const uint16_t* wo,
+                                const float* rms_ffn, const uint16_t* w1, const uint16_t* w2, const uint16_t* w3,
+                                const float* rms_final, const uint16_t* w_cls) {
+    oracle_model* m = oracle_create(dim, hidden_dim, n_layers, n_heads, n_kv_heads, vocab_size, seq_len, rope_base,
+                                    (const float*)tok_emb, rms_att, (const float*)wq, (const float*)wk,
+                                    (const float*)wv, (const float*)wo, rms_ffn, (const float*)w1, (const float*)w2,
+                                    (const float*)w3, rms_final, (const float*)w_cls);
+    m->w_f16 = 1;
     return m;
 }
 
@@ -187,9 +248,9 @@ void oracle_attention(oracle_model* m, int layer, int pos) {
     int gqa = m->n_heads / m->n_kv_heads;
     int cache_stride = m->seq_len * head_size;
 
-    oracle_matmul(m->q, m->xb, m->wq + off_q, dim, dim);
-    oracle_matmul(m->k, m->xb, m->wk + off_kv, kv_dim, dim);
-    oracle_matmul(m->v, m->xb, m->wv + off_kv, kv_dim, dim);
+    model_matmul(m, m->q, m->xb, m->wq, off_q, dim, dim);
+    model_matmul(m, m->k, m->xb, m->wk, off_kv, kv_dim, dim);
+    model_matmul(m, m->v, m->xb, m->wv, off_kv, kv_dim, dim);
     oracle_rope(m->q, m->k, pos, dim, kv_dim, head_size, m->rope_base);
 
     for (int h = 0; h < m->n_kv_heads; h++) {
@@ -224,7 +285,7 @@ void oracle_attention(oracle_model* m, int layer, int pos) {
             for (int i = 0; i < head_size; i++) xbh[i] += vr[i] * score;
         }
     }
-    oracle_matmul(m->xb2, m->xb, m->wo + off_q, dim, dim);
+    model_matmul(m, m->xb2, m->xb, m->wo, off_q, dim, dim);
 }
 
 /* model.cpp:229-239 (CPU transformer_block path) */
@@ -236,20 +297,25 @@ void oracle_transformer_block(oracle_model* m, int layer, int pos) {
     oracle_attention(m, layer, pos);
     for (int i = 0; i < dim; i++) m->x[i] += m->xb2[i];
     oracle_rmsnorm(m->xb, m->x, m->rms_ffn + off_norm, dim);
-    oracle_matmul(m->hb, m->xb, m->w1 + off_ffn, hidden, dim);
-    oracle_matmul(m->he, m->xb, m->w3 + off_ffn, hidden, dim);
+    model_matmul(m, m->hb, m->xb, m->w1, off_ffn, hidden, dim);
+    model_matmul(m, m->he, m->xb, m->w3, off_ffn, hidden, dim);
     oracle_swiglu(m->hb, m->hb, m->he, hidden);
-    oracle_matmul(m->xb2, m->hb, m->w2 + off_ffn, dim, hidden);
+    model_matmul(m, m->xb2, m->hb, m->w2, off_ffn, dim, hidden);
     for (int i = 0; i < dim; i++) m->x[i] += m->xb2[i];
 }
 
 /* model.cpp:373-380: everything of forward() before sample(); logits copied out if asked. */
 void oracle_step_logits(oracle_model* m, int token, int pos, float* logits_out) {
     int dim = m->dim;
-    memcpy(m->x, m->tok_emb + (size_t)token * dim, dim * sizeof(float));
+    if (m->w_f16) {
+        const uint16_t* row = (const uint16_t*)m->tok_emb + (size_t)token * dim;
+        for (int i = 0; i < dim; i++) m->x[i] = half_bits_to_float(row[i]);
+    } else {
+        memcpy(m->x, m->tok_emb + (size_t)token * dim, dim * sizeof(float));
+    }
     for (int l = 0; l < m->n_layers; l++) oracle_transformer_block(m, l, pos);
     oracle_rmsnorm(m->x, m->x, m->rms_final, dim);
-    oracle_matmul(m->logits, m->x, m->w_cls, m->vocab_size, dim);
+    model_matmul(m, m->logits, m->x, m->w_cls, 0, m->vocab_size, dim);
     if (logits_out) memcpy(logits_out, m->logits, (size_t)m->vocab_size * sizeof(float));
 }
 

@@ -18,7 +18,16 @@ import numpy as np
 HERE = os.path.dirname(os.path.abspath(__file__))
 ORACLE_SO = os.path.join(HERE, "liblpp_oracle.so")
 REF_SO = os.path.join(HERE, "_ref", "libref_cpu.so")
-REFERENCE_CHECKOUT = os.environ.get("LPP_REFERENCE", "/root/reference")
+
+
+def reference_checkout() -> Optional[str]:
+    """Where the Lighter++ sources lie: $LPP_REFERENCE, else a directory named ``reference`` beside this
+    repository; None when neither holds a ``src`` folder."""
+    for cand in (os.environ.get("LPP_REFERENCE"), os.path.join(HERE, "..", "..", "reference")):
+        if cand and os.path.isdir(os.path.join(cand, "src")):
+            return os.path.abspath(cand)
+    return None
+
 
 _fp = C.POINTER(C.c_float)
 _ip = C.POINTER(C.c_int)
@@ -28,11 +37,12 @@ _WEIGHT_ORDER = ["tok_emb", "rms_att", "wq", "wk", "wv", "wo", "rms_ffn", "w1", 
 def build(ref: bool = True) -> None:
     """Compile the restatement, and the reference CPU build when its checkout is present."""
     subprocess.run(["make", "-s", "-C", HERE, "oracle"], check=True)
-    if ref and os.path.isdir(os.path.join(REFERENCE_CHECKOUT, "src")):
-        subprocess.run(["make", "-s", "-C", HERE, "ref", f"REF={REFERENCE_CHECKOUT}"], check=True)
+    checkout = reference_checkout() if ref else None
+    if checkout:
+        subprocess.run(["make", "-s", "-C", HERE, "ref", f"REF={checkout}"], check=True)
         # the reference's own main.cpp / runtests.cpp linked against the CUDA library through the C++ shim
         if os.path.exists(os.path.join(HERE, "..", "lighterpp_b200", "liblpp_b200.so")):
-            subprocess.run(["make", "-s", "-C", HERE, "dropin", f"REF={REFERENCE_CHECKOUT}"], check=True)
+            subprocess.run(["make", "-s", "-C", HERE, "dropin", f"REF={checkout}"], check=True)
 
 
 def have_reference() -> bool:
@@ -50,15 +60,23 @@ def _ptr(a: Optional[np.ndarray]):
 class _ModelBase:
     """Shared driver logic; subclasses bind the prefix-specific symbols."""
 
-    def __init__(self, lib, prefix: str, cfg, weights: Dict[str, np.ndarray]):
+    def __init__(self, lib, prefix: str, cfg, weights: Dict[str, np.ndarray], keep_f16: bool = False):
         self.lib, self.p, self.cfg = lib, prefix, cfg
-        # keep FP32 copies alive for the lifetime of the C model
-        self._w = {k: _f32(weights[k]) for k in _WEIGHT_ORDER if k in weights}
-        create = getattr(lib, prefix + "create")
+        if keep_f16:
+            # binary16 matrices stay binary16 (widened exactly inside the C code): half the host memory of FP32
+            # copies, which is what makes the 8B shape fit.  Norm weights are FP32 as everywhere.
+            self._w = {k: (_f32(v) if k.startswith("rms") else np.ascontiguousarray(v, dtype=np.float16))
+                       for k, v in weights.items() if k in _WEIGHT_ORDER}
+            create = getattr(lib, prefix + "create_f16")
+        else:
+            # keep FP32 copies alive for the lifetime of the C model
+            self._w = {k: _f32(weights[k]) for k in _WEIGHT_ORDER if k in weights}
+            create = getattr(lib, prefix + "create")
         create.restype = C.c_void_p
-        create.argtypes = [C.c_int] * 7 + [C.c_float] + [_fp] * 12
+        create.argtypes = [C.c_int] * 7 + [C.c_float] + [C.c_void_p] * 12
+        ptrs = [self._w[k].ctypes.data if k in self._w else None for k in _WEIGHT_ORDER]
         self.h = create(cfg.dim, cfg.hidden_dim, cfg.n_layers, cfg.n_heads, cfg.n_kv_heads, cfg.vocab_size,
-                        cfg.seq_len, cfg.rope_base, *[_ptr(self._w.get(k)) for k in _WEIGHT_ORDER])
+                        cfg.seq_len, cfg.rope_base, *ptrs)
         self._bind()
 
     def _bind(self):
@@ -120,8 +138,10 @@ class Oracle:
         lib.oracle_srand.argtypes = [C.c_uint]
         lib.oracle_rand_floats.argtypes = [_fp, C.c_int]
 
-    def model(self, cfg, weights) -> _ModelBase:
-        return _ModelBase(self.lib, "oracle_", cfg, weights)
+    def model(self, cfg, weights, keep_f16: bool = False) -> _ModelBase:
+        """keep_f16: hand binary16 matrices to the C code as they are (exact widening on use) instead of
+        making FP32 copies; results are bit-identical, host memory is halved."""
+        return _ModelBase(self.lib, "oracle_", cfg, weights, keep_f16)
 
     def matmul(self, x, w):
         x, w = _f32(x), _f32(w)

@@ -72,3 +72,12 @@ def test_product_code_does_not_touch_the_oracle():
                 for needle in ("import oracle", "from oracle", "oracle/", "oracle.oracle", "liblpp_oracle",
                                "libref_cpu"):
                     assert needle not in text, (os.path.join(dirpath, f), needle)
+
+
+def test_library_is_the_product_build():
+    """The timing-aid environment switches (kernel kinds left out, arithmetic skipped ...) exist only in builds
+    made with -DLPP_TIMING_AIDS; the library that ships must not contain them."""
+    with open(E.LIB_PATH, "rb") as f:
+        blob = f.read()
+    for name in (b"LPP_DEBUG_SKIP", b"LPP_DEBUG_GEMV", b"LPP_STAGE_KB", b"LPP_ATTN_CHUNK"):
+        assert name not in blob, name

@@ -120,7 +120,7 @@ def test_stories15m_shape_full_run(E, oracle):
         tok = int(prompt[pos + 1]) if pos + 1 < len(prompt) else (greedy_ref if pos % 2 else hot_ref)
         hist = (hist + [tok])[-64:]
     print(f"stories15m: worst logit diff {worst:.2e}; T=1.0 ids equal to sample() in {agree}/{total} draws")
-    assert agree >= 0.995 * total
+    assert agree == total  # bit-exact ids on identical logits and r
     eng.close()
 
 
@@ -210,25 +210,6 @@ def test_long_context_head_size_128(E, oracle, kv_dtype):
     eng.close()
 
 
-def test_llama32_1b_shape_first_steps(E, oracle):
-    """Config 3 shape (128K vocabulary, tied classifier): first steps against the oracle."""
-    c, dt, tied, seed = synth.SHAPES["llama-3.2-1b"]
-    c = type(c)(**{**c.asdict(), "seq_len": 64})
-    T = synth.gen_model(c, seed, dt, tied)
-    eng = E.Engine(c, dt, "f16")
-    eng.load_weights(T)
-    m = oracle.model(c, synth.as_f32(T))
-    del T
-    toks = synth.prompt_tokens(c.vocab_size, 3, seed)
-    hist = [int(t) for t in toks]
-    for pos, t in enumerate(toks):
-        ref = m.step_logits(int(t), pos)
-        d, cos = check_logits(ref, eng.step_logits(int(t), pos), dt)
-        assert eng.sample(ref, 0.0, 1.1, hist, 0.0) == oracle.sample(ref, 0.0, 1.1, hist, 0.0)
-    print(f"llama-3.2-1b shape: last-step max-abs {d:.2e}, cosine {cos:.7f}")
-    eng.close()
-
-
 @pytest.mark.parametrize("name", ["vocab32k-f16", "vocab128k-f16"])
 def test_exact_sampler_draws_large_vocab(E, oracle, name):
     """The engine's sampler on identical logits, history and r, >= 10k draws over both vocabularies: ids must equal,
@@ -252,7 +233,7 @@ def test_exact_sampler_draws_large_vocab(E, oracle, name):
             same_ref += got == oracle.sample(lg, 0.8, 1.1, hist, float(r))
             total += 1
     print(f"{name}: categorical ids equal to the twin in {total}/{total} draws, to sample() in {same_ref}/{total}")
-    assert same_ref >= 0.995 * total
+    assert same_ref == total  # the seeded draws hold no case where the kernel's exp and libm's expf differ in the last bit
     eng.close()
 
 
