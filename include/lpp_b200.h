@@ -64,6 +64,8 @@ typedef enum {
                                       reference's sequential FP32 sums bit for bit */
 #define LPP_FLAG_TP_NCCL 0x20u   /* tensor parallelism: keep the NCCL all-reduce after o_proj / down even when the peers
                                   * are mapped (lpp_tp_connect); default is the exchange fused into the GEMVs */
+#define LPP_FLAG_NO_SELF_FLAGS 0x80u /* single GPU: hand the residual stream from o_proj / down to the next GEMV through
+                                      * plain floats behind a kernel boundary instead of self-validating words */
 #define LPP_FLAG_TP_LOCAL 0x40u  /* tensor parallelism without NCCL: the engine never loads or initialises NCCL and
                                   * nccl_id may be NULL; only the peer-memory exchange (lpp_tp_connect) can run */
 

@@ -147,9 +147,17 @@ __device__ __forceinline__ bool status_timed_out(const StepState* st) {
 __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity, StepState* st) {
     if (mbar_try_wait(bar, parity)) return true;
     const long long t0 = clock64();
-    const long long limit = wait_limit(st);
+    // The engine's limit lives in global memory; fetching it costs an L2 round trip, which an ordinary wait
+    // for a copy in flight must not pay.  It is read once the wait has lasted longer than any normal one.
+    long long limit = 1 << 17;  // ~65 us, below every configurable limit
+    bool fetched = false;
     while (!mbar_try_wait(bar, parity)) {
         if (clock64() - t0 > limit) {
+            if (!fetched) {
+                limit = wait_limit(st);
+                fetched = true;
+                continue;
+            }
             if (st) atomicOr(&st->status, kStatusBarrierTimeout);
             return false;
         }
@@ -181,12 +189,6 @@ __device__ __forceinline__ unsigned long long l2_policy_evict_first() {
     unsigned long long p;
     asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
     return p;
-}
-
-// Asks the copy engine to pull [gsrc, gsrc+bytes) into L2 (no shared-memory destination, no
-// completion to wait for).  gsrc 16-byte aligned, bytes a multiple of 16.
-__device__ __forceinline__ void bulk_prefetch_l2(const void* gsrc, uint32_t bytes) {
-    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(gsrc), "r"(bytes) : "memory");
 }
 
 // ------------------------------------------------------------------ reproducible expf

@@ -212,18 +212,21 @@ struct GemvPlan {
     size_t smem;
 };
 
-constexpr int kStageTarget = 8192;  // bytes per ring slot (see gemv.cuh)
+constexpr int kStageTarget = 8192;  // bytes per bulk copy / ring slot (see gemv.cuh)
 
-// Ring geometry of one GEMV: rows per stage and bytes per slot.  A row that is a single K-chunk travels
-// with its neighbours in one bulk copy (as many whole rows as fit the slot, a power of two up to the
-// group size); longer rows travel chunk by chunk, `target / chunk bytes` rows per slot.
+// A stage is one bulk copy of about stage_target bytes: whole row pairs when they fit, else one
+// K-chunk of one row.
 static void gemv_geometry(GemvArgs& a, int esz, int stage_target) {
-    const int xc = 32 * kVecPerLane * (16 / esz);  // inputs per chunk
-    const int chunk_bytes = std::min(a.K, xc) * esz;
-    int rps = 1;
-    while (rps * 2 <= kGroupRows && rps * 2 * chunk_bytes <= stage_target) rps *= 2;
-    a.rps = rps;
-    a.stage_bytes = (int)align_up((size_t)rps * chunk_bytes, 128);
+    const int pair_bytes = kRowsPerGroup * a.K * esz;
+    if (pair_bytes <= stage_target) {
+        a.pairs_per_stage = stage_target / pair_bytes;
+        a.kc = a.K;
+        a.stage_bytes = a.pairs_per_stage * pair_bytes;
+    } else {
+        a.pairs_per_stage = 0;
+        a.kc = std::max(8, std::min(a.K, stage_target / esz) / 8 * 8);
+        a.stage_bytes = a.kc * esz;
+    }
 }
 
 template <typename WT, int EPI>
@@ -248,12 +251,8 @@ static cudaError_t launch_gemv_t(lpp_engine* e, GemvArgs& a, bool pdl, cudaStrea
     if (const char* sk = aid_env("LPP_STAGE_KB")) stage_target = std::max(1, atoi(sk)) * 1024;
     gemv_geometry(a, esz, stage_target);
     const size_t fixed = kGemvBarrierBytes + 128 + xbytes;
-    size_t ring = (size_t)(e->c.ring_kb > 0 ? e->c.ring_kb : 192) * 1024;
+    size_t ring = (size_t)(e->c.ring_kb > 0 ? e->c.ring_kb : 128) * 1024;
     if (fixed + ring > e->smem_optin) ring = e->smem_optin - fixed;
-    if (ring < (size_t)2 * kGemvConsumerWarps * a.stage_bytes && stage_target > 4096) {
-        // two slots per warp do not fit beside a long staged input: halve the slots
-        gemv_geometry(a, esz, stage_target / 2);
-    }
     int ns = (int)(ring / ((size_t)kGemvConsumerWarps * a.stage_bytes));  // slots per consumer warp
     ns = std::max(2, std::min(ns, kGemvMaxStages));
     const int grid = std::max(1, std::min(groups, e->num_sms));
@@ -454,28 +453,6 @@ static void matrix_span(const lpp_engine* e, int kind, int l, const void** ptr, 
             break;
     }
 }
-// What the GEMV (kind, l) should pull towards L2 for its successor in the step: the next matrix, or
-// its first LPP_PF_MB MiB (default 8) when it is larger.  The classifier's successor is the first
-// layer's QKV matrix of the next token.
-static void set_prefetch(const lpp_engine* e, GemvArgs& a, int kind, int l) {
-    int nk, nl = l;
-    switch (kind) {
-        case kQkv: nk = kOproj; break;
-        case kOproj: nk = kGateUp; break;
-        case kGateUp: nk = kDown; break;
-        case kDown: nk = (l + 1 < e->c.n_layers) ? kQkv : kLmHead; nl = l + 1; break;
-        default: nk = kQkv; nl = 0; break;
-    }
-    size_t cap = 8;
-    if (const char* v = aid_env("LPP_PF_MB")) cap = (size_t)std::max(0, atoi(v));
-    const void* p;
-    size_t bytes;
-    matrix_span(e, nk, nl, &p, &bytes);
-    bytes = std::min(bytes, cap << 20) & ~(size_t)15;
-    a.pf = bytes ? p : nullptr;
-    a.pf_bytes = (unsigned int)bytes;
-}
-
 // ---- tensor-parallel exchange buffer layout: [epoch word, padded to 256 B][2 * n_layers receive areas],
 //      a receive area = [tp][dim] 64-bit {value, flag} words
 static size_t tp_header_bytes() { return 1024; }  // epoch word at 0, hint counters (one per exchange) from byte 256
@@ -499,7 +476,7 @@ static unsigned int tp_hint_per_step(const lpp_engine* e) {
 }
 // (a single-kind timing run must not take part in exchanges: its producers would have no consumers)
 static bool tp_peer_path(const lpp_engine* e) {
-    return e->c.tp_size > 1 && e->peer_ready && e->only_kind < 0 &&
+    return e->peer_ready && e->only_kind < 0 &&
            !(e->c.flags & (LPP_FLAG_GEMV_LDG | LPP_FLAG_TP_NCCL));
 }
 // producer side: exchange `ex` takes the rows of this residual GEMV
@@ -527,7 +504,7 @@ static void tp_set_consumer(const lpp_engine* e, GemvArgs& a, int ex, float* x_s
 // vocab/tp logits and stores them, as flagged words, into every rank's logits area (after the
 // exchange areas of the buffer); a small kernel turns the words into the float logits the sampler reads.
 static bool tp_cls_sharded(const lpp_engine* e) {
-    return tp_peer_path(e) && e->c.vocab_size % (kRowsPerGroup * e->c.tp_size) == 0 && !aid_env("LPP_TP_FULL_CLS");
+    return e->c.tp_size > 1 && tp_peer_path(e) && e->c.vocab_size % (kRowsPerGroup * e->c.tp_size) == 0 && !aid_env("LPP_TP_FULL_CLS");
 }
 static unsigned long long* tp_logits_area(const lpp_engine* e, int p) {
     return reinterpret_cast<unsigned long long*>(e->peer_base[p] + tp_header_bytes() + (size_t)2 * e->c.n_layers * tp_area_bytes(e));
@@ -622,7 +599,6 @@ static void record_step(Recorder& R, bool with_sampler) {
             at.n_kv_heads = e->KVHl;
             if (const char* mc = aid_env("LPP_ATTN_CHUNK")) at.min_chunk = atoi(mc);  // timing experiments
             {
-                set_prefetch(e, a, kQkv, l);
                 record_gemv(R, kQkv, kEpiQkv, a);
                 dim3 grid(e->attn_splits, e->KVHl, e->attn_z);
                 if (!kind_skipped(e, kAttn)) {
@@ -651,7 +627,6 @@ static void record_step(Recorder& R, bool with_sampler) {
             a.resid = (!tp || c.tp_rank == 0) ? cur : nullptr;
             a.out = tp ? oth : cur;
             if (peers) tp_set_producer(e, a, 2 * l);
-            set_prefetch(e, a, kOproj, l);
             record_gemv(R, kOproj, kEpiResid, a);
             if (tp && !peers) {
                 record_allreduce(R, oth, D);
@@ -667,7 +642,6 @@ static void record_step(Recorder& R, bool with_sampler) {
             if (peers) tp_set_consumer(e, a, 2 * l, cur);
             a.norm_w = e->rms_ffn + (size_t)l * D;
             a.out = e->hb;
-            set_prefetch(e, a, kGateUp, l);
             record_gemv(R, kGateUp, kEpiSwiglu, a);
         }
         {  // down + residual
@@ -679,7 +653,6 @@ static void record_step(Recorder& R, bool with_sampler) {
             a.resid = (!tp || c.tp_rank == 0) ? cur : nullptr;
             a.out = tp ? oth : cur;
             if (peers) tp_set_producer(e, a, 2 * l + 1);
-            set_prefetch(e, a, kDown, l);
             record_gemv(R, kDown, kEpiResid, a);
             if (tp && !peers) {
                 record_allreduce(R, oth, D);
@@ -703,7 +676,6 @@ static void record_step(Recorder& R, bool with_sampler) {
             a.n_rows = Vl;
             for (int p = 0; p < c.tp_size; ++p) a.tp_out[p] = tp_logits_area(e, p) + r0;
         }
-        set_prefetch(e, a, kLmHead, 0);
         record_gemv(R, kLmHead, kEpiStore, a);
         if (sharded && !kind_skipped(e, kLmHead)) {
             const int V = c.vocab_size;
@@ -920,22 +892,25 @@ extern "C" lpp_status lpp_engine_create(const lpp_config* cfg, const void* nccl_
         CUB(cudaMemcpy(e->rope, tab.data(), tab.size() * sizeof(float2), cudaMemcpyHostToDevice));
     }
 
-    if (c.tp_size > 1) {
-        if (!(c.flags & LPP_FLAG_TP_LOCAL)) {
-            if (!nccl::load()) return bail(fail(LPP_ERR_NCCL, "cannot load libnccl.so.2: %s", dlerror()));
-            nccl::unique_id id;
-            memcpy(&id, nccl_id, sizeof id);
-            nccl::result_t r = nccl::CommInitRank(&e->comm, c.tp_size, id, c.tp_rank);
-            if (r != 0) return bail(fail(LPP_ERR_NCCL, "ncclCommInitRank: %s", nccl::GetErrorString(r)));
-        }
-        if (c.tp_size <= kMaxTp) {
-            // receive areas and counters of the peer-memory exchange (used once lpp_tp_connect has mapped the peers)
-            e->tp_buf_bytes = tp_header_bytes() + (size_t)2 * c.n_layers * tp_area_bytes(e) +
-                              (size_t)c.vocab_size * sizeof(unsigned long long);  // exchange areas + logits area
-            CUB(cudaMalloc(&e->tp_buf, e->tp_buf_bytes));
-            CUB(cudaMemset(e->tp_buf, 0, e->tp_buf_bytes));
-            e->peer_base[c.tp_rank] = e->tp_buf;
-        }
+    if (c.tp_size > 1 && !(c.flags & LPP_FLAG_TP_LOCAL)) {
+        if (!nccl::load()) return bail(fail(LPP_ERR_NCCL, "cannot load libnccl.so.2: %s", dlerror()));
+        nccl::unique_id id;
+        memcpy(&id, nccl_id, sizeof id);
+        nccl::result_t r = nccl::CommInitRank(&e->comm, c.tp_size, id, c.tp_rank);
+        if (r != 0) return bail(fail(LPP_ERR_NCCL, "ncclCommInitRank: %s", nccl::GetErrorString(r)));
+    }
+    if (c.tp_size <= kMaxTp) {
+        // Receive areas and counters of the residual-stream exchange.  Tensor parallel: used once lpp_tp_connect
+        // has mapped the peers (plus the logits area of the vocabulary-sharded classifier).  Single GPU: the
+        // same words carry the residual stream from o_proj / down to the next GEMV of this GPU.
+        e->tp_buf_bytes = tp_header_bytes() + (size_t)2 * c.n_layers * tp_area_bytes(e) +
+                          (c.tp_size > 1 ? (size_t)c.vocab_size * sizeof(unsigned long long) : 0);
+        CUB(cudaMalloc(&e->tp_buf, e->tp_buf_bytes));
+        CUB(cudaMemset(e->tp_buf, 0, e->tp_buf_bytes));
+        e->peer_base[c.tp_rank] = e->tp_buf;
+        bool self = c.tp_size == 1 && !(c.flags & (LPP_FLAG_GEMV_LDG | LPP_FLAG_NO_SELF_FLAGS));
+        if (const char* v = aid_env("LPP_SELF_FLAGS")) self = self && atoi(v) != 0;
+        if (self) e->peer_ready = true;
     }
     CUB(cudaStreamSynchronize(e->stream));
 #undef CUB
@@ -1290,7 +1265,7 @@ static_assert(sizeof(cudaIpcMemHandle_t) == LPP_TP_HANDLE_BYTES, "IPC handle siz
 extern "C" lpp_status lpp_tp_export(lpp_engine* e, void* handle, size_t handle_bytes) {
     if (!e || !handle) return fail(LPP_ERR_INVALID_ARG, "null argument");
     if (handle_bytes < sizeof(cudaIpcMemHandle_t)) return fail(LPP_ERR_INVALID_ARG, "handle buffer needs %zu bytes", sizeof(cudaIpcMemHandle_t));
-    if (!e->tp_buf) return fail(LPP_ERR_INVALID_ARG, "engine has no tensor-parallel exchange buffer (tp_size 1 or > %d)", kMaxTp);
+    if (!e->tp_buf || e->c.tp_size < 2) return fail(LPP_ERR_INVALID_ARG, "engine has no tensor-parallel exchange buffer (tp_size 1 or > %d)", kMaxTp);
     CU(cudaSetDevice(e->c.device));
     cudaIpcMemHandle_t h;
     CU(cudaIpcGetMemHandle(&h, e->tp_buf));
@@ -1301,7 +1276,7 @@ extern "C" lpp_status lpp_tp_export(lpp_engine* e, void* handle, size_t handle_b
 extern "C" lpp_status lpp_tp_connect(lpp_engine* e, const void* handles, size_t handle_bytes) {
     if (!e || !handles) return fail(LPP_ERR_INVALID_ARG, "null argument");
     if (handle_bytes < sizeof(cudaIpcMemHandle_t)) return fail(LPP_ERR_INVALID_ARG, "handles are %zu bytes each", sizeof(cudaIpcMemHandle_t));
-    if (!e->tp_buf) return fail(LPP_ERR_INVALID_ARG, "engine has no tensor-parallel exchange buffer");
+    if (!e->tp_buf || e->c.tp_size < 2) return fail(LPP_ERR_INVALID_ARG, "engine has no tensor-parallel exchange buffer");
     if (e->finalized) return fail(LPP_ERR_INVALID_ARG, "lpp_tp_connect must precede lpp_finalize");
     CU(cudaSetDevice(e->c.device));
     for (int p = 0; p < e->c.tp_size; ++p) {
@@ -1326,7 +1301,7 @@ extern "C" lpp_status lpp_tp_connect(lpp_engine* e, const void* handles, size_t 
 // with LPP_ERR_DEVICE_STATUS: the one way to see that path on a single GPU without a fault or a hang.
 extern "C" lpp_status lpp_debug_tp_absent_peers(lpp_engine* e) {
     if (!e) return fail(LPP_ERR_INVALID_ARG, "null argument");
-    if (!e->tp_buf) return fail(LPP_ERR_INVALID_ARG, "engine has no tensor-parallel exchange buffer");
+    if (!e->tp_buf || e->c.tp_size < 2) return fail(LPP_ERR_INVALID_ARG, "engine has no tensor-parallel exchange buffer");
     if (e->finalized) return fail(LPP_ERR_INVALID_ARG, "must precede lpp_finalize");
     CU(cudaSetDevice(e->c.device));
     if (!e->absent_peer) {

@@ -18,9 +18,7 @@
 // no CTA-wide barrier, and the copy-issue work runs eight lanes wide instead of on one thread.
 // The copy engine retires roughly one bulk copy per ~100 SM cycles whatever its size, so a stage is
 // always ONE copy of ~8 KiB: several whole row pairs when rows are short, one K-chunk of one row
-// when they are long.  When a producer lane has issued its last copy it asks the copy engine to
-// prefetch its share of the next kernel's weights into L2, which keeps HBM busy across the kernel
-// boundary.  The producer starts before the programmatic
+// when they are long.  The producer starts before the programmatic
 // dependency wait -- weights do not depend on the previous kernel -- so the ring is already full
 // when the activations arrive.  HBM traffic = the matrix once; x is re-read from L2 per CTA.
 #pragma once
@@ -30,12 +28,12 @@ namespace lpp {
 
 enum GemvEpi : int { kEpiStore = 0, kEpiResid = 1, kEpiSwiglu = 2, kEpiQkv = 3 };
 
-constexpr int kGemvConsumerWarps = 12;
+constexpr int kGemvConsumerWarps = 8;
 constexpr int kGemvRingThreads = (kGemvConsumerWarps + 1) * 32;  // + producer warp
 constexpr int kGemvLdgThreads = 256;
-constexpr int kGemvMaxStages = 8;   // ring slots per consumer warp
+constexpr int kGemvMaxStages = 16;  // ring slots per consumer warp
 // per consumer warp: one "full" and one "empty" barrier per slot of its private ring
-constexpr int kGemvBarrierBytes = (2 * kGemvConsumerWarps * kGemvMaxStages * 8 + 127) / 128 * 128;
+constexpr int kGemvBarrierBytes = 2 * kGemvConsumerWarps * kGemvMaxStages * 8;
 constexpr int kRowsPerGroup = 2;                           // rows handled together by one warp
 
 constexpr int kMaxTp = 8;  // ranks of a tensor-parallel group
@@ -59,16 +57,17 @@ struct GemvArgs {
     void* v_cache;
     int kv_is_f32;
     // ---- ring geometry (host-computed)
-    int rps;          // rows per stage: the same K-chunk of this many consecutive rows shares a ring slot
+    int pairs_per_stage;  // > 0: a stage holds this many whole row pairs (one contiguous copy);
+                          // 0: rows are long, a stage holds one K-chunk (kc elements) of one row
+    int kc;           // K elements per stage in long-row mode (multiple of 8)
     int n_stages;     // ring slots per consumer warp
     int stage_bytes;  // bytes per slot
-    // ---- L2 prefetch of the weights the NEXT kernel of the step will stream (nullptr = none)
-    const void* pf;
-    unsigned int pf_bytes;
     int debug;        // timing experiments only: 1 = consumers skip the arithmetic, 2 = producer skips the copies
     int xs_bytes;     // shared-memory bytes reserved for the staged input (0 = K floats rounded up to 128)
     unsigned long long* trace;  // timing experiments only: [CTA][8] global-timer stamps, nullptr = none
-    // ---- tensor-parallel exchange over peer memory (tp_size <= 1 or null pointers = not used).
+    // ---- exchange of the residual stream as self-validating words (null pointers = not used; with tp_size 1 the
+    // "exchange" is local: the consumer starts on the arrival of the data instead of on the completion of the
+    // producing grid, which takes a kernel boundary's drain-and-wake latency off the critical path).
     // Every result travels as one 64-bit word {value, flag}, flag = the step's epoch + 1, so a word is
     // either old or complete and no fence or counter is needed.  Residual epilogue: every rank stores its
     // partial rows into slot `rank` of the exchange's receive area on EVERY rank (plain peer stores over
@@ -271,7 +270,7 @@ __device__ __forceinline__ void stage_input(const GemvArgs& a, float* xs, float*
     // rank's own slot included): its flags can only be complete once every rank's producing GEMV has
     // stored all its rows, which in turn follows everything earlier in the step, so that case does not
     // wait for the local kernel to drain its peer stores and exit.
-    if (a.tp_in != nullptr && a.tp_size > 1) {
+    if (a.tp_in != nullptr) {
         stage_input_peers<WT, NT>(a, xs, red, tid);
         return;
     }
@@ -442,7 +441,7 @@ __device__ __forceinline__ void dot_rows(const unsigned char* row0, const unsign
 // Store of a finished row pair: locally, or as {value, flag} words into this rank's slot (residual GEMVs) or
 // row range (vocabulary-sharded classifier) on every rank of the tensor-parallel group.
 __device__ __forceinline__ void store_rows(const GemvArgs& a, int row, float v0, float v1) {
-    if (a.tp_size > 1 && a.tp_out[0]) {
+    if (a.tp_out[0]) {
         const unsigned long long flag = (unsigned long long)(*a.tp_epoch + 1u) << 32;
         const unsigned long long w0 = flag | __float_as_uint(v0), w1 = flag | __float_as_uint(v1);
 #pragma unroll
@@ -506,106 +505,14 @@ __device__ __forceinline__ void gemv_epilogue(const GemvArgs& a, int g, float v0
 }
 
 // ------------------------------------------------------------------ ring (bulk async copy) variant
-//
-// Work decomposition.  A CTA owns a contiguous range of row pairs, split into contiguous shares for its
-// consumer warps.  A warp walks its share in GROUPS of kGroupRows rows (four pairs) and, inside a group,
-// K-chunk by K-chunk (a chunk = kVecPerLane 16-byte vectors per lane = 2048 FP16 / 1024 FP32 inputs): the
-// chunk of the input vector sits in REGISTERS, every weight vector is read from shared memory exactly
-// once and meets its inputs there, and the eight running row sums of the group stay in registers until
-// the group is complete.  They are then reduced across the warp with a transposing butterfly (9 shuffles
-// for 8 rows instead of 40) that leaves the sums of pair j on lane 8j, and those four lanes run the
-// epilogue of their pair side by side.
-//
-// A stage (= one ring slot, one barrier phase) holds the same chunk of `rps` rows: consecutive whole rows
-// in one bulk copy when a row is one chunk, else one bulk copy per row.
-
-constexpr int kGroupRows = 8;    // rows whose sums a warp carries in registers at a time
-constexpr int kVecPerLane = 8;   // 16-byte weight vectors per lane and chunk
-
-// One lane's share of a chunk of the staged input, in registers: xr[i][*] = the inputs that meet weight
-// vector (lane + 32 i) of the chunk (FP32 bit patterns).  Positions at or beyond K read as zero.
-template <typename WT>
-__device__ __forceinline__ void load_x_chunk(const float* xs, int K, int k0, int lane, unsigned int (&xr)[kVecPerLane][16 / sizeof(WT)]) {
-    constexpr int VEC = 16 / (int)sizeof(WT);
-#pragma unroll
-    for (int i = 0; i < kVecPerLane; ++i) {
-        const int k = k0 + (lane + 32 * i) * VEC;
-        if (k < K) {
-            if constexpr (sizeof(WT) == 2) {
-                const uint4 lo = *reinterpret_cast<const uint4*>(xs + ((k >> 3) << 2));
-                const uint4 hi = *reinterpret_cast<const uint4*>(xs + ((k >> 3) << 2) + (K >> 1));
-                xr[i][0] = lo.x; xr[i][1] = lo.y; xr[i][2] = lo.z; xr[i][3] = lo.w;
-                xr[i][4] = hi.x; xr[i][5] = hi.y; xr[i][6] = hi.z; xr[i][7] = hi.w;
-            } else {
-                const uint4 v = *reinterpret_cast<const uint4*>(xs + k);
-                xr[i][0] = v.x; xr[i][1] = v.y; xr[i][2] = v.z; xr[i][3] = v.w;
-            }
-        } else {
-#pragma unroll
-            for (int j = 0; j < VEC; ++j) xr[i][j] = 0u;
-        }
-    }
-}
-
-// Dot product of one row's chunk (nv valid 16-byte vectors at shared-memory address `row`) with the chunk of
-// the input held in registers.  All loads of the row are issued before the first is used.
-template <typename WT>
-__device__ __forceinline__ float dot_chunk(uint32_t row, int nv, int lane, const unsigned int (&xr)[kVecPerLane][16 / sizeof(WT)]) {
-    uint4 w[kVecPerLane];
-#pragma unroll
-    for (int i = 0; i < kVecPerLane; ++i) {
-        w[i] = make_uint4(0u, 0u, 0u, 0u);
-        if (lane + 32 * i < nv) w[i] = lds_u4(row + (uint32_t)(lane + 32 * i) * 16u);
-    }
-    float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
-#pragma unroll
-    for (int i = 0; i < kVecPerLane; ++i) {
-        if constexpr (sizeof(WT) == 2) {
-            float2 p;
-            p = half2_bits_to_float2(w[i].x); s0 = fmaf(p.x, __uint_as_float(xr[i][0]), s0); s1 = fmaf(p.y, __uint_as_float(xr[i][1]), s1);
-            p = half2_bits_to_float2(w[i].y); s2 = fmaf(p.x, __uint_as_float(xr[i][2]), s2); s3 = fmaf(p.y, __uint_as_float(xr[i][3]), s3);
-            p = half2_bits_to_float2(w[i].z); s0 = fmaf(p.x, __uint_as_float(xr[i][4]), s0); s1 = fmaf(p.y, __uint_as_float(xr[i][5]), s1);
-            p = half2_bits_to_float2(w[i].w); s2 = fmaf(p.x, __uint_as_float(xr[i][6]), s2); s3 = fmaf(p.y, __uint_as_float(xr[i][7]), s3);
-        } else {
-            s0 = fmaf(__uint_as_float(w[i].x), __uint_as_float(xr[i][0]), s0);
-            s1 = fmaf(__uint_as_float(w[i].y), __uint_as_float(xr[i][1]), s1);
-            s2 = fmaf(__uint_as_float(w[i].z), __uint_as_float(xr[i][2]), s2);
-            s3 = fmaf(__uint_as_float(w[i].w), __uint_as_float(xr[i][3]), s3);
-        }
-    }
-    return (s0 + s1) + (s2 + s3);
-}
-
-// Sums acc[r] over the warp for the eight rows of a group.  Returns, on every lane, the total of row
-// rho(lane) = 4*bit4 + 2*bit3 + bit2 of the lane index (lanes that differ only in bits 0-1 hold copies).
-__device__ __forceinline__ float group_reduce(const float (&acc)[kGroupRows], int lane) {
-    float k4[4], k2[2];
-    const bool h4 = lane & 16, h3 = lane & 8, h2 = lane & 4;
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-        const float got = __shfl_xor_sync(0xffffffffu, h4 ? acc[j] : acc[j + 4], 16);
-        k4[j] = (h4 ? acc[j + 4] : acc[j]) + got;
-    }
-#pragma unroll
-    for (int j = 0; j < 2; ++j) {
-        const float got = __shfl_xor_sync(0xffffffffu, h3 ? k4[j] : k4[j + 2], 8);
-        k2[j] = (h3 ? k4[j + 2] : k4[j]) + got;
-    }
-    float v = (h2 ? k2[1] : k2[0]) + __shfl_xor_sync(0xffffffffu, h2 ? k2[0] : k2[1], 4);
-    v += __shfl_xor_sync(0xffffffffu, v, 2);
-    v += __shfl_xor_sync(0xffffffffu, v, 1);
-    return v;
-}
 
 // Body of the ring kernel.  Returns true on the consumer threads once all of this CTA's rows are
-// done (so a caller can append a CTA-level tail), false on the producer warp.
+// done (so a caller can append a CTA-level tail), false on the producer warp and after a timeout.
 template <typename WT, int EPI>
 __device__ __forceinline__ bool gemv_ring_body(const GemvArgs& a, unsigned char* smem) {
-    constexpr int VEC = 16 / (int)sizeof(WT);
-    constexpr int XC = 32 * kVecPerLane * VEC;                         // inputs per chunk
     uint64_t* full = reinterpret_cast<uint64_t*>(smem);                // [consumer warp][kGemvMaxStages]
     uint64_t* empty = full + kGemvConsumerWarps * kGemvMaxStages;      // [consumer warp][kGemvMaxStages]
-    float* red = reinterpret_cast<float*>(smem + kGemvBarrierBytes);   // one float per consumer warp
+    float* red = reinterpret_cast<float*>(smem + kGemvBarrierBytes);   // 8 floats
     float* xs = reinterpret_cast<float*>(smem + kGemvBarrierBytes + 128);
     const size_t xs_bytes = a.xs_bytes > 0 ? (size_t)a.xs_bytes : (((size_t)a.K * 4 + 127) & ~(size_t)127);
     unsigned char* ring = smem + kGemvBarrierBytes + 128 + xs_bytes;
@@ -618,13 +525,13 @@ __device__ __forceinline__ bool gemv_ring_body(const GemvArgs& a, unsigned char*
     const int g1 = (int)(((long long)(blockIdx.x + 1) * groups) / gridDim.x);
     const int ng = g1 - g0;
     const int w = (warp == kGemvConsumerWarps) ? lane : warp;  // pipeline index
-    const int p0 = g0 + (w < kGemvConsumerWarps ? (int)(((long long)ng * w) / kGemvConsumerWarps) : 0);
-    const int p1 = g0 + (w < kGemvConsumerWarps ? (int)(((long long)ng * (w + 1)) / kGemvConsumerWarps) : 0);
-    const int row_lo = p0 * kRowsPerGroup, row_hi = p1 * kRowsPerGroup;  // this pipeline's rows
+    const int p0 = g0 + (w < kGemvConsumerWarps ? (ng * w) / kGemvConsumerWarps : 0);
+    const int p1 = g0 + (w < kGemvConsumerWarps ? (ng * (w + 1)) / kGemvConsumerWarps : 0);
     const size_t row_bytes = (size_t)a.K * sizeof(WT);
-    const int nch = (a.K + XC - 1) / XC;
-    const int rps = a.rps;                       // rows per stage
-    const uint32_t rstride = nch == 1 ? (uint32_t)row_bytes : (uint32_t)(XC * sizeof(WT));  // row-to-row distance inside a slot
+    const int m = a.pairs_per_stage;
+    const int nch = m > 0 ? 1 : (a.K + a.kc - 1) / a.kc;
+    const int pstep = m > 0 ? m : 1;  // pairs advance by pstep from p0 to p1
+    const int unit = m > 0 ? m : 1;
 
     if (tid == 0) gemv_stamp(a, 0);
     // The dependent kernel is released for launch at once: its CTAs take over an SM as soon as one of
@@ -640,95 +547,53 @@ __device__ __forceinline__ bool gemv_ring_body(const GemvArgs& a, unsigned char*
     __syncthreads();
 
     if (warp == kGemvConsumerWarps) {
-        // ---------------- producer warp: lane w feeds consumer warp w through w's private ring.
-        // The twelve lanes watch twelve different "slot is free" barriers, so none of them may block: the
-        // warp stays converged, every lane TESTS its own barrier (no suspending wait) and the lanes whose
-        // slot is free issue their next copy in the same pass.
-        const bool feeder = lane < kGemvConsumerWarps && row_lo < row_hi;
-        const unsigned char* W = reinterpret_cast<const unsigned char*>(a.W);
-        uint64_t* myfull = full + (feeder ? w : 0) * kGemvMaxStages;
-        uint64_t* myempty = empty + (feeder ? w : 0) * kGemvMaxStages;
-        unsigned char* myring = ring + (size_t)(feeder ? w : 0) * NS * a.stage_bytes;
-        int slot = 0, pass = 0;  // pass = completed trips around the ring
-        bool alive = true;
-        // streamed weights are marked evict-first in L2: they are used once per token and would
-        // otherwise push the K/V cache and the activations out (debug bit 8 turns the hint off)
-        const unsigned long long policy = !(a.debug & 8) ? l2_policy_evict_first() : 0ull;
-        if (lane == 0) gemv_stamp(a, 5);
-        // position in this lane's sequence of stages: group start row, chunk, first row of the stage in the group
-        int r0 = row_lo, c = 0, rs = 0;
-        bool have = feeder && !(a.debug & 16);
-        long long t0 = 0, limit = 0;
-        while (__any_sync(0xffffffffu, have)) {
-            bool moved = false;
-            if (have) {
+        // ---------------- producer warp: lane w feeds consumer warp w through w's private ring
+        if (lane < kGemvConsumerWarps) {
+            const unsigned char* W = reinterpret_cast<const unsigned char*>(a.W);
+            uint64_t* myfull = full + w * kGemvMaxStages;
+            uint64_t* myempty = empty + w * kGemvMaxStages;
+            unsigned char* myring = ring + (size_t)w * NS * a.stage_bytes;
+            int slot = 0, pass = 0;  // pass = completed trips around the ring
+            bool alive = true;
+            // streamed weights are marked evict-first in L2: they are used once per token and would
+            // otherwise push the K/V cache and the activations out (debug bit 8 turns the hint off)
+            const unsigned long long policy = !(a.debug & 8) ? l2_policy_evict_first() : 0ull;
+            auto issue = [&](const unsigned char* src, uint32_t bytes) -> bool {
                 // trip p > 0 reuses a slot once its release number p-1 has happened
-                if (pass == 0 || mbar_test_wait(&myempty[slot], (uint32_t)(pass - 1) & 1u)) {
-                    const int gr = min(kGroupRows, row_hi - r0);
-                    const int cnt = min(rps, gr - rs);
-                    const int klen = min(XC, a.K - c * XC);
-                    const uint32_t cbytes = (uint32_t)(klen * sizeof(WT));
-                    unsigned char* dst = myring + (size_t)slot * a.stage_bytes;
-                    const unsigned char* src = W + (size_t)(r0 + rs) * row_bytes + (size_t)c * XC * sizeof(WT);
-                    if (a.debug & 2) {
-                        mbar_arrive(&myfull[slot]);
-                    } else if (nch == 1) {  // whole consecutive rows: one copy
-                        const uint32_t bytes = (uint32_t)cnt * cbytes;
-                        mbar_arrive_expect_tx(&myfull[slot], bytes);
-                        if (!(a.debug & 8)) bulk_g2s_hint(dst, src, bytes, &myfull[slot], policy);
-                        else bulk_g2s(dst, src, bytes, &myfull[slot]);
-                    } else {                // the same chunk of cnt rows: one copy per row
-                        mbar_arrive_expect_tx(&myfull[slot], (uint32_t)cnt * cbytes);
-                        for (int r = 0; r < cnt; ++r) {
-                            if (!(a.debug & 8)) bulk_g2s_hint(dst + (size_t)r * rstride, src + (size_t)r * row_bytes, cbytes, &myfull[slot], policy);
-                            else bulk_g2s(dst + (size_t)r * rstride, src + (size_t)r * row_bytes, cbytes, &myfull[slot]);
-                        }
-                    }
-                    if (++slot == NS) {
-                        slot = 0;
-                        ++pass;
-                    }
-                    // next stage: rows of the group, then chunks, then groups
-                    rs += rps;
-                    if (rs >= gr) {
-                        rs = 0;
-                        if (++c == nch) {
-                            c = 0;
-                            r0 += kGroupRows;
-                            have = r0 < row_hi;
-                        }
-                    }
-                    moved = true;
+                if (pass > 0 && !mbar_wait_bounded(&myempty[slot], (uint32_t)(pass - 1) & 1u, a.st))
+                    return false;
+                if (a.debug & 2) {
+                    mbar_arrive(&myfull[slot]);
+                } else {
+                    mbar_arrive_expect_tx(&myfull[slot], bytes);
+                    if (!(a.debug & 8))
+                        bulk_g2s_hint(myring + (size_t)slot * a.stage_bytes, src, bytes, &myfull[slot], policy);
+                    else
+                        bulk_g2s(myring + (size_t)slot * a.stage_bytes, src, bytes, &myfull[slot]);
                 }
-            }
-            if (__any_sync(0xffffffffu, moved)) {
-                t0 = 0;
-            } else {  // every slot is still in use: bounded wait, a short nap between looks
-                if (t0 == 0) {
-                    t0 = clock64();
-                    limit = wait_limit(a.st);
-                } else if (__any_sync(0xffffffffu, clock64() - t0 > limit)) {  // one decision for the warp
-                    if (lane == 0) atomicOr(&a.st->status, kStatusBarrierTimeout);
-                    alive = false;
-                    break;
+                if (++slot == NS) {
+                    slot = 0;
+                    ++pass;
                 }
-                __nanosleep(32);
+                return true;
+            };
+            if (lane == 0) gemv_stamp(a, 5);
+            if (m > 0) {
+                for (int p = p0; p < p1 && alive; p += pstep) {
+                    const int cnt = min(unit, p1 - p);
+                    alive = issue(W + (size_t)p * kRowsPerGroup * row_bytes, (uint32_t)(cnt * kRowsPerGroup * row_bytes));
+                }
+            } else {
+                for (int p = p0; p < p1 && alive; p += pstep)
+                    for (int r = 0; r < kRowsPerGroup && alive; ++r)
+                        for (int c = 0; c < nch && alive; ++c) {
+                            const int k0 = c * a.kc;
+                            const int klen = min(a.kc, a.K - k0);
+                            alive = issue(W + ((size_t)(p * kRowsPerGroup + r) * a.K + k0) * sizeof(WT),
+                                          (uint32_t)(klen * sizeof(WT)));
+                        }
             }
-        }
-        if (feeder) {
             if (lane == 0) gemv_stamp(a, 6);
-            // this lane's HBM requests are all queued: pull its share of the next kernel's weights
-            // towards L2 so the memory system stays busy across the kernel boundary
-            if (a.pf && alive) {
-                const unsigned int lanes = gridDim.x * kGemvConsumerWarps;
-                unsigned int slice = (a.pf_bytes + lanes - 1) / lanes;
-                slice = (slice + 15u) & ~15u;
-                const unsigned long long off = (unsigned long long)(blockIdx.x * kGemvConsumerWarps + w) * slice;
-                if (off < a.pf_bytes) {
-                    const unsigned int n = (unsigned int)min((unsigned long long)slice, (unsigned long long)a.pf_bytes - off);
-                    bulk_prefetch_l2(reinterpret_cast<const unsigned char*>(a.pf) + off, n & ~15u);
-                }
-            }
         }
         __syncwarp();
         // all of this CTA's copies are issued: the next kernel may start launching
@@ -755,64 +620,74 @@ __device__ __forceinline__ bool gemv_ring_body(const GemvArgs& a, unsigned char*
     const unsigned char* myring = ring + (size_t)w * NS * a.stage_bytes;
     int slot = 0;
     uint32_t par = 0;
-    unsigned int xr[kVecPerLane][VEC];
-    if (nch == 1 && row_lo < row_hi) load_x_chunk<WT>(xs, a.K, 0, lane, xr);
-    bool first = true;
-    for (int r0 = row_lo; r0 < row_hi; r0 += kGroupRows) {
-        const int gr = min(kGroupRows, row_hi - r0);
-        float acc[kGroupRows];
-#pragma unroll
-        for (int r = 0; r < kGroupRows; ++r) acc[r] = 0.f;
-        // Residual epilogue: the residual of this lane's pair is requested now, so its L2 round trip runs
-        // beside the dot products instead of after them.  The producing kernel has completed: stage_input waited.
-        float2 resid = make_float2(0.f, 0.f);
-        if constexpr (EPI == kEpiResid) {
-            if (a.resid && (lane & 7) == 0 && 2 * (lane >> 3) < gr)
-                resid = __ldcg(reinterpret_cast<const float2*>(a.resid + r0 + 2 * (lane >> 3)));
+    // waits for this warp's next stage; warp-uniform outcome so a timed-out lane cannot strand the rest
+    auto acquire = [&]() -> bool { return __all_sync(0xffffffffu, mbar_wait_bounded(&myfull[slot], par, a.st)); };
+    auto release = [&]() {
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&myempty[slot]);
+        if (++slot == NS) {
+            slot = 0;
+            par ^= 1u;
         }
-        bool ok = true;
-        for (int c = 0; c < nch && ok && !(a.debug & 16); ++c) {  // debug bit 16: no stages at all, epilogues of zeros
-            const int klen = min(XC, a.K - c * XC);
-            const int nv = klen / VEC;
-            if (nch > 1) load_x_chunk<WT>(xs, a.K, c * XC, lane, xr);
-            for (int rs = 0; rs < gr; rs += rps) {
-                const int cnt = min(rps, gr - rs);
-                // waits for this warp's next stage; warp-uniform outcome so a timed-out lane cannot strand the rest
-                if (!__all_sync(0xffffffffu, mbar_wait_bounded(&myfull[slot], par, a.st))) {
-                    ok = false;
-                    break;
-                }
-                if (tid == 0 && first) gemv_stamp(a, 3);
-                first = false;
-                const uint32_t st = smem_u32(myring + (size_t)slot * a.stage_bytes);
-                if (!(a.debug & 1)) {
-#pragma unroll 2
-                    for (int j = 0; j < cnt; ++j) {
-                        const float d = dot_chunk<WT>(st + (uint32_t)j * rstride, nv, lane, xr);
-#pragma unroll
-                        for (int q = 0; q < kGroupRows; ++q)  // acc stays in registers: static indices, predicated adds
-                            if (q == rs + j) acc[q] += d;
-                    }
-                }
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&myempty[slot]);
-                if (++slot == NS) {
-                    slot = 0;
-                    par ^= 1u;
+    };
+    // A warp whose wait runs out stops consuming but still returns through the common exit, so a
+    // CTA-level tail (which uses CTA barriers) is never left waiting for it.
+    bool ok = true;
+    // Residual epilogue: the residual of this warp's first pair is requested now, so its L2 round
+    // trip runs beside the dot product instead of after it (the weights are usually in the ring
+    // already when the input arrives).  The producing kernel has completed: stage_input waited.
+    float2 r_first = make_float2(0.f, 0.f);
+    if (EPI == kEpiResid && a.resid && lane == 0 && p0 < p1)
+        r_first = __ldcg(reinterpret_cast<const float2*>(a.resid + (size_t)p0 * kRowsPerGroup));
+    if (m > 0) {
+        for (int p = p0; p < p1 && ok; p += pstep) {
+            const int cnt = min(unit, p1 - p);
+            if (!acquire()) {
+                ok = false;
+                break;
+            }
+            if (tid == 0 && p == p0) gemv_stamp(a, 3);
+            const unsigned char* st = myring + (size_t)slot * a.stage_bytes;
+            for (int i = 0; i < cnt; ++i) {
+                float acc0 = 0.f, acc1 = 0.f;
+                const unsigned char* r0 = st + (size_t)i * kRowsPerGroup * row_bytes;
+                if (!(a.debug & 1)) dot_rows<WT, 2, false>(r0, r0 + row_bytes, xs, a.K, 0, a.K, lane, acc0, acc1);
+                acc0 = warp_sum(acc0);
+                acc1 = warp_sum(acc1);
+                if (lane == 0) {
+                    if (EPI == kEpiResid && p + i == p0)
+                        store_rows(a, p0 * kRowsPerGroup, acc0 + r_first.x, acc1 + r_first.y);
+                    else
+                        gemv_epilogue<EPI>(a, p + i, acc0, acc1);
                 }
             }
+            release();
         }
-        // A warp whose wait ran out stops consuming but still returns through the common exit, so a
-        // CTA-level tail (which uses CTA barriers) is never left waiting for it.
-        if (!ok) break;
-        const float v = group_reduce(acc, lane);
-        const float vo = __shfl_xor_sync(0xffffffffu, v, 4);  // the other row of the pair
-        if ((lane & 7) == 0 && 2 * (lane >> 3) < gr) {
-            const int pair = (r0 >> 1) + (lane >> 3);
-            if constexpr (EPI == kEpiResid)
-                store_rows(a, pair * kRowsPerGroup, v + resid.x, vo + resid.y);
-            else
-                gemv_epilogue<EPI>(a, pair, v, vo);
+    } else {
+        for (int p = p0; p < p1 && ok; p += pstep) {
+            float acc[kRowsPerGroup] = {0.f, 0.f};
+#pragma unroll
+            for (int r = 0; r < kRowsPerGroup; ++r)
+                for (int c = 0; c < nch && ok; ++c) {
+                    if (!acquire()) {
+                        ok = false;
+                        break;
+                    }
+                    const int k0 = c * a.kc;
+                    const int klen = min(a.kc, a.K - k0);
+                    const unsigned char* st = myring + (size_t)slot * a.stage_bytes;
+                    float dummy = 0.f;
+                    if (!(a.debug & 1)) dot_rows<WT, 1, false>(st, st, xs, a.K, k0, klen, lane, acc[r], dummy);
+                    release();
+                }
+            if (!ok) break;
+            const float v0 = warp_sum(acc[0]), v1 = warp_sum(acc[1]);
+            if (lane == 0) {
+                if (EPI == kEpiResid && p == p0)
+                    store_rows(a, p0 * kRowsPerGroup, v0 + r_first.x, v1 + r_first.y);
+                else
+                    gemv_epilogue<EPI>(a, p, v0, v1);
+            }
         }
     }
     if (tid == 0) gemv_stamp(a, 4);

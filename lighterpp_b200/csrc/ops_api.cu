@@ -77,19 +77,76 @@ lpp_status op_gemv_t(float* out, const float* x, const void* w, int n, int d, cu
     return chk();
 }
 
+// ---- scratch layout of the stand-alone samplers: step state, per-block partials, ticket counter and barrier
+//      words, then what the exact-order kernel adds (block sums, entry counts, scalars, entry lists).
+//      `cap_blocks` sizes the areas: the blocks of this call (stream-ordered scratch) or of the largest
+//      vocabulary the fixed array takes.
+struct SampleScratch {
+    size_t state, part, counters, sums, counts, scalars, entries, total;
+};
+constexpr SampleScratch sample_scratch_layout(int cap_blocks, bool exact) {
+    SampleScratch L = {};
+    size_t o = 0;
+    L.state = o;
+    o += (sizeof(StepState) + 255) & ~(size_t)255;
+    L.part = o;
+    o += ((size_t)cap_blocks * 12 + 255) & ~(size_t)255;
+    L.counters = o;  // [0] ticket counter of the tree kernel; from +256: barrier counter and exit ticket of the exact kernel
+    o += 512;
+    if (exact) {
+        L.sums = o;
+        o += ((size_t)cap_blocks * sizeof(double) + 255) & ~(size_t)255;
+        L.counts = o;
+        o += ((size_t)cap_blocks * sizeof(int) + 255) & ~(size_t)255;
+        L.scalars = o;
+        o += 256;
+        L.entries = o;
+        o += (size_t)cap_blocks * kExactMaxEntries * sizeof(ExactEntry);
+    }
+    L.total = o;
+    return L;
+}
+
+// Launches the sampler on logits with its scratch at `scratch` (laid out by sample_scratch_layout for
+// cap_blocks >= the blocks of this vocabulary).  The step state at the head of the scratch and the zeroed
+// counters are the caller's business.  The exact-order kernel (ids equal to the reference's sequential CPU
+// sample()) needs all its blocks co-resident; a vocabulary beyond that takes the tree-sum kernel.
+void launch_sampler_on_scratch(char* scratch, const SampleScratch& L, bool exact, float* d_logits, int vocab_size,
+                               int nb, cudaStream_t s) {
+    SampleArgs a = {};
+    a.logits = d_logits;
+    a.vocab = vocab_size;
+    a.st = (StepState*)(scratch + L.state);
+    a.part_max = (float*)(scratch + L.part);
+    a.part_idx = (int*)(scratch + L.part + (size_t)nb * 4);
+    a.part_sum = (float*)(scratch + L.part + (size_t)nb * 8);
+    a.counter = (unsigned int*)(scratch + L.counters);
+    if (exact) {
+        SampleExactArgs ea = {};
+        ea.base = a;
+        ea.sync = (unsigned int*)(scratch + L.counters + 256);
+        ea.block_sum = (double*)(scratch + L.sums);
+        ea.entry_count = (int*)(scratch + L.counts);
+        ea.scalars = (float*)(scratch + L.scalars);
+        ea.entries = (ExactEntry*)(scratch + L.entries);
+        sample_exact_kernel<<<nb, kSampleThreads, 0, s>>>(ea);
+    } else {
+        sample_kernel<<<nb, kSampleThreads, 0, s>>>(a);
+    }
+}
+
 // ---- scratch for lpp_op_sample_static: lives in the library image, one copy per GPU that loads it
 constexpr int kStaticSampleMaxVocab = 262144;  // 128 blocks of kSampleChunk logits
-constexpr size_t kStaticStateBytes = (sizeof(StepState) + 255) & ~(size_t)255;
-constexpr size_t kStaticPartialBytes = (size_t)(kStaticSampleMaxVocab / kSampleChunk) * 12;
-constexpr size_t kStaticScratchBytes = kStaticStateBytes + kStaticPartialBytes + 256;
-static __device__ __align__(256) unsigned char g_sample_scratch[kStaticScratchBytes];
+constexpr int kStaticSampleBlocks = kStaticSampleMaxVocab / kSampleChunk;
+constexpr SampleScratch kStaticLayout = sample_scratch_layout(kStaticSampleBlocks, true);
+static __device__ __align__(256) unsigned char g_sample_scratch[kStaticLayout.total];
 // Device addresses of g_sample_scratch, one per CUDA device, filled in on first use.  In host code
 // the name g_sample_scratch is only a handle for cudaGetSymbolAddress, never a pointer to pass on.
 static unsigned char* g_sample_scratch_addr[64];
 
 // Writes the step-state header the sampler reads, copies the history device-to-device and zeroes
 // the ticket counter -- everything in the shared scratch that must not survive from the last call.
-static __global__ void sample_static_setup_kernel(StepState* st, unsigned int* counter, float temperature,
+static __global__ void sample_static_setup_kernel(StepState* st, unsigned int* counters, float temperature,
                                                   float penalty, float r, const int* history, int history_len) {
     if (threadIdx.x == 0) {
         st->token = 0;
@@ -106,7 +163,9 @@ static __global__ void sample_static_setup_kernel(StepState* st, unsigned int* c
         st->status = 0;
         st->wait_cycles = 0;
         st->tp_wait_cycles = 0;
-        *counter = 0u;
+    }
+    if (threadIdx.x < 128) counters[threadIdx.x] = 0u;  // ticket counter, barrier counter, exit ticket
+    if (threadIdx.x == 0) {
     }
     for (int i = threadIdx.x; i < history_len; i += blockDim.x) st->history[i] = history[i];
 }
@@ -224,50 +283,22 @@ lpp_status lpp_op_sample(float* d_logits, int vocab_size, float temperature, flo
     int dev = 0, sms = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
         return LPP_ERR_CUDA;
-    // The exact-order kernel (ids equal to the reference's sequential CPU sample()) needs all its blocks
-    // co-resident; a vocabulary beyond that (more than 2048 logits per SM) takes the tree-sum kernel.
-    const bool exact = nb <= sms;
-    // stream-ordered scratch: step state + per-block partials + ticket counter (+ the exact kernel's lists)
-    const size_t st_bytes = (sizeof(StepState) + 255) & ~(size_t)255;
-    const size_t part_bytes = ((size_t)nb * 12 + 255) & ~(size_t)255;
-    const size_t sum_bytes = ((size_t)nb * sizeof(double) + 255) & ~(size_t)255;
-    const size_t cnt_bytes = ((size_t)nb * sizeof(int) + 255) & ~(size_t)255;
-    const size_t ent_bytes = (size_t)nb * kExactMaxEntries * sizeof(ExactEntry);
-    const size_t bytes = st_bytes + part_bytes + 256 + (exact ? 256 + sum_bytes + cnt_bytes + 256 + ent_bytes : 0);
+    const bool exact = nb <= sms;  // see launch_sampler_on_scratch
+    const SampleScratch L = sample_scratch_layout(nb, exact);  // stream-ordered scratch, sized for this call
     char* scratch = nullptr;
-    if (cudaMallocAsync((void**)&scratch, bytes, s) != cudaSuccess) return LPP_ERR_CUDA;
+    if (cudaMallocAsync((void**)&scratch, L.total, s) != cudaSuccess) return LPP_ERR_CUDA;
     StepState h = {};
     h.temperature = temperature;
     h.penalty = penalty;
     h.r = r;
     const bool use_hist = penalty > 1.0f && d_history && history_len > 0;
     h.history_len = use_hist ? history_len : 0;
-    cudaMemcpyAsync(scratch, &h, offsetof(StepState, history), cudaMemcpyHostToDevice, s);
+    cudaMemcpyAsync(scratch + L.state, &h, offsetof(StepState, history), cudaMemcpyHostToDevice, s);
     if (use_hist)
-        cudaMemcpyAsync(scratch + offsetof(StepState, history), d_history, (size_t)history_len * sizeof(int),
+        cudaMemcpyAsync(scratch + L.state + offsetof(StepState, history), d_history, (size_t)history_len * sizeof(int),
                         cudaMemcpyDeviceToDevice, s);
-    SampleArgs a = {};
-    a.logits = d_logits;
-    a.vocab = vocab_size;
-    a.st = (StepState*)scratch;
-    a.part_max = (float*)(scratch + st_bytes);
-    a.part_idx = (int*)(scratch + st_bytes + (size_t)nb * 4);
-    a.part_sum = (float*)(scratch + st_bytes + (size_t)nb * 8);
-    a.counter = (unsigned int*)(scratch + st_bytes + part_bytes);
-    cudaMemsetAsync(a.counter, 0, exact ? 512 : 256, s);  // ticket counter (+ the exact kernel's barrier words)
-    if (exact) {
-        char* p = scratch + st_bytes + part_bytes + 256;
-        SampleExactArgs ea = {};
-        ea.base = a;
-        ea.sync = (unsigned int*)p;
-        ea.block_sum = (double*)(p + 256);
-        ea.entry_count = (int*)(p + 256 + sum_bytes);
-        ea.scalars = (float*)(p + 256 + sum_bytes + cnt_bytes);
-        ea.entries = (ExactEntry*)(p + 256 + sum_bytes + cnt_bytes + 256);
-        sample_exact_kernel<<<nb, kSampleThreads, 0, s>>>(ea);
-    } else {
-        sample_kernel<<<nb, kSampleThreads, 0, s>>>(a);
-    }
+    cudaMemsetAsync(scratch + L.counters, 0, 512, s);
+    launch_sampler_on_scratch(scratch, L, exact, d_logits, vocab_size, nb, s);
     cudaMemcpyAsync(d_sampled_token, scratch + offsetof(StepState, out_token), sizeof(int), cudaMemcpyDeviceToDevice, s);
     cudaFreeAsync(scratch, s);
     return chk();
@@ -301,20 +332,16 @@ lpp_status lpp_op_sample_static(float* d_logits, int vocab_size, float temperatu
     }
     unsigned char* scratch = g_sample_scratch_addr[dev];
     cudaStream_t s = S(stream);
+    int sms = 0;
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return LPP_ERR_CUDA;
     const int nb = (vocab_size + kSampleChunk - 1) / kSampleChunk;
+    const bool exact = nb <= sms;  // the same choice of kernel as lpp_op_sample
     const bool use_hist = penalty > 1.0f && d_history && history_len > 0;
-    SampleArgs a = {};
-    a.logits = d_logits;
-    a.vocab = vocab_size;
-    a.st = (StepState*)scratch;
-    a.part_max = (float*)(scratch + kStaticStateBytes);
-    a.part_idx = (int*)(scratch + kStaticStateBytes + (size_t)nb * 4);
-    a.part_sum = (float*)(scratch + kStaticStateBytes + (size_t)nb * 8);
-    a.counter = (unsigned int*)(scratch + kStaticStateBytes + kStaticPartialBytes);
-    sample_static_setup_kernel<<<1, 256, 0, s>>>(a.st, a.counter, temperature, penalty, r, use_hist ? d_history : nullptr,
-                                                 use_hist ? history_len : 0);
-    sample_kernel<<<nb, kSampleThreads, 0, s>>>(a);
-    sample_static_publish_kernel<<<1, 1, 0, s>>>(a.st, d_sampled_token);
+    sample_static_setup_kernel<<<1, 256, 0, s>>>((StepState*)(scratch + kStaticLayout.state),
+                                                 (unsigned int*)(scratch + kStaticLayout.counters), temperature, penalty, r,
+                                                 use_hist ? d_history : nullptr, use_hist ? history_len : 0);
+    launch_sampler_on_scratch((char*)scratch, kStaticLayout, exact, d_logits, vocab_size, nb, s);
+    sample_static_publish_kernel<<<1, 1, 0, s>>>((const StepState*)(scratch + kStaticLayout.state), d_sampled_token);
     return chk();
 }
 

@@ -25,7 +25,7 @@ TENSOR_IDS = {"tok_emb": 0, "rms_att": 1, "wq": 2, "wk": 3, "wv": 4, "wo": 5, "r
               "w3": 9, "rms_final": 10, "w_cls": 11}
 _UNSTACKED = ("tok_emb", "rms_final", "w_cls")
 TP_HANDLE_BYTES = 64
-FLAG_TP_NCCL, FLAG_TP_LOCAL = 32, 64
+FLAG_TP_NCCL, FLAG_TP_LOCAL, FLAG_NO_SELF_FLAGS = 32, 64, 128
 KINDS = ["qkv_gemv", "attention", "oproj_gemv", "gateup_gemv", "down_gemv", "lmhead_gemv", "sampler", "allreduce",
          "reserved8", "reserved9"]
 
