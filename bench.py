@@ -57,7 +57,7 @@ class ClockSampler:
     def __enter__(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.Q}",
-                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                          "--format=csv,noheader,nounits", "-lms", "25"],
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.t = threading.Thread(target=self._read, daemon=True)
             self.t.start()
@@ -104,8 +104,16 @@ def gen_device_weights(cfg, dtype, tied, seed, layers=None):
             yield name, l, t
 
 
-def tp1_same_workload(args, cfg, dtype, tied, seed, local, n_prompt, temp, pen):
-    """tok/s of the N>1 workload on one GPU: same prompt handling, a shorter timed region."""
+CHECK_TOKENS = (11, 4242)  # tp_check: two steps at positions 0 and 1 (they depend on no earlier cache content)
+
+
+def check_logits(eng):
+    return [eng.step_logits(t, pos) for pos, t in enumerate(CHECK_TOKENS)]
+
+
+def tp1_same_workload(args, cfg, dtype, tied, seed, local, n_prompt, temp, pen, tp_logits=None):
+    """tok/s of the N>1 workload on one GPU: same prompt handling, a shorter timed region.  With tp_logits (the
+    tensor-parallel engine's logits of the two check steps) it also reports how far they are from this engine's."""
     import torch
     from lighterpp_b200 import engine as E, synth
     steps = max(16, min(args.steps, 64))
@@ -130,10 +138,16 @@ def tp1_same_workload(args, cfg, dtype, tied, seed, local, n_prompt, temp, pen):
     out, dev_ms = eng.decode(tok, pos, steps, temp, pen, hist, 64, rs[8:8 + steps])
     torch.cuda.synchronize()
     bytes_per_step = float(np.mean([eng.step_bytes(p) for p in range(pos, pos + steps)]))
+    check = None
+    if tp_logits is not None:
+        mine = check_logits(eng)
+        check = {"max_abs": max(float(np.abs(a - b).max()) for a, b in zip(mine, tp_logits)),
+                 "min_cosine": min(float(np.dot(a, b) / (np.linalg.norm(a) * np.linalg.norm(b))) for a, b in zip(mine, tp_logits))}
     eng.close()
     us = dev_ms * 1e3 / steps
-    return {"value": round(steps / (dev_ms / 1e3), 2), "unit": "tok/s", "n_gpus": 1, "steps": steps,
-            "ms_per_step": round(dev_ms / steps, 5), "achieved_gbs": round(bytes_per_step / us / 1e3, 1)}
+    out = {"value": round(steps / (dev_ms / 1e3), 2), "unit": "tok/s", "n_gpus": 1, "steps": steps,
+           "ms_per_step": round(dev_ms / steps, 5), "achieved_gbs": round(bytes_per_step / us / 1e3, 1)}
+    return out, check
 
 
 def run_ours(args, rank, world):
@@ -216,16 +230,23 @@ def run_ours(args, rank, world):
         eng.forward(int(t), prefill + i, temp, 1.1, hist, 0.5)
     tok, pos = int(prompt[-1]), prefill + n_prompt - 1
     hist = (hist + [tok])[-64:]
-    # warm-up (untimed), device-resident loop
-    if args.warmup > 0:
-        out, _ = eng.decode(tok, pos, args.warmup, temp, pen, hist, 64, rs[:args.warmup])
-        hist = (hist + [int(x) for x in out])[-64:]
-        tok, pos = int(out[-1]), pos + args.warmup
-    # ---- timed region 1: K steps, inputs resident in HBM, CUDA events on the engine's stream
-    barrier()
+    # the clock sampler starts before the warm-up: nvidia-smi needs a moment to come up, and the short timed region
+    # of the larger rank counts would otherwise pass between two samples (idle samples are filtered out)
     with ClockSampler(local) as clk:
+        # warm-up (untimed), device-resident loop
+        if args.warmup > 0:
+            out, _ = eng.decode(tok, pos, args.warmup, temp, pen, hist, 64, rs[:args.warmup])
+            hist = (hist + [int(x) for x in out])[-64:]
+            tok, pos = int(out[-1]), pos + args.warmup
+        # ---- timed region 1: K steps, inputs resident in HBM, CUDA events on the engine's stream
+        barrier()
         out, dev_ms = eng.decode(tok, pos, args.steps, temp, pen, hist, 64, rs[args.warmup:args.warmup + args.steps])
         barrier()
+    ids_equal = None
+    if world > 1:  # every rank must have sampled the same tokens
+        all_ids = [None] * world
+        dist.all_gather_object(all_ids, [int(x) for x in out])
+        ids_equal = all(a == all_ids[0] for a in all_ids)
     t_dev = torch.tensor([dev_ms], dtype=torch.float64)
     if world > 1:
         dist.all_reduce(t_dev, op=dist.ReduceOp.MAX)
@@ -254,7 +275,7 @@ def run_ours(args, rank, world):
     e2e_s = float(t_e2e.item())
 
     # ---- per-kernel durations (CUDA events inside a replayed graph) for the roofline object
-    prof = eng.profile_step(pos - args.steps // 2, 10)
+    prof = eng.profile_step(pos - args.steps // 2, 10, temp, pen)
     gemv_kinds = {k: v for k, v in prof.items() if (k.endswith("gemv") or k == "step_kernel") and v["launches"]}
     dom = max(gemv_kinds, key=lambda k: gemv_kinds[k]["bytes"])  # the kernel family that moves most bytes per step
     try:
@@ -307,14 +328,25 @@ def run_ours(args, rank, world):
                             "gbs": round(v["bytes"] / v["ms"] / 1e6, 1) if v["ms"] else None}
                         for k, v in prof.items() if v["launches"]},
         }
+    tp_logits = check_logits(eng) if world > 1 else None  # outside every timed region; all ranks take part
     eng.close()
-    if world > 1 and not args.no_tp1 and not prefill:
+    if world > 1 and not args.no_tp1:
         # the same workload on ONE GPU (rank 0 alone, the other ranks wait): the number the sharded run is a
-        # speed-up over.  N=1 of the default run is a different, smaller shape.
+        # speed-up over (N=1 of the default run is a different, smaller shape), and the engine the sharded
+        # logits are checked against
         torch.cuda.empty_cache()
         if rank == 0:
             try:
-                line["tp1_same_workload"] = tp1_same_workload(args, cfg, dtype, tied, seed, local, n_prompt, temp, pen)
+                one, check = tp1_same_workload(args, cfg, dtype, tied, seed, local, n_prompt, temp, pen, tp_logits)
+                line["tp1_same_workload"] = one
+                if prefill:
+                    one["note"] = "this one-GPU run has no pre-filled cache: it serves the logits check only"
+                if not prefill:  # the one-GPU run has no pre-filled cache: its positions are not the same work
+                    line["scaling_vs_tp1"] = {"speedup": round(line["value"] / one["value"], 3),
+                                              "efficiency": round(line["value"] / one["value"] / world, 3)}
+                line["tp_check"] = {**check, "sampled_ids_equal_on_all_ranks": ids_equal,
+                                    "what": "logits of two steps (positions 0, 1) against the same engine on one GPU; "
+                                            "bar: max-abs 2e-2, cosine 0.9999"}
             except Exception as ex:  # e.g. a shape that does not fit one GPU
                 line["tp1_same_workload"] = {"unavailable": str(ex)[:200]}
         dist.barrier()

@@ -64,8 +64,8 @@ typedef enum {
                                       reference's sequential FP32 sums bit for bit */
 #define LPP_FLAG_TP_NCCL 0x20u   /* tensor parallelism: keep the NCCL all-reduce after o_proj / down even when the peers
                                   * are mapped (lpp_tp_connect); default is the exchange fused into the GEMVs */
-#define LPP_FLAG_NO_SELF_FLAGS 0x80u /* single GPU: hand the residual stream from o_proj / down to the next GEMV through
-                                      * plain floats behind a kernel boundary instead of self-validating words */
+#define LPP_FLAG_NO_PREFILL_GEMM 0x80u /* lpp_prefill feeds the prompt token by token (the reference's way) instead of
+                                        * through the batched tensor-core path */
 #define LPP_FLAG_TP_LOCAL 0x40u  /* tensor parallelism without NCCL: the engine never loads or initialises NCCL and
                                   * nccl_id may be NULL; only the peer-memory exchange (lpp_tp_connect) can run */
 
@@ -147,6 +147,15 @@ lpp_status lpp_step_logits(lpp_engine* e, int token, int pos, float* h_logits);
 lpp_status lpp_decode(lpp_engine* e, int first_token, int start_pos, int n, const lpp_sample_params* sp,
                       const int* h_history, int history_len, int history_window, const float* h_r,
                       int* h_out_tokens, float* device_ms);
+
+/* The prompt loop of src/main.cpp:163-179 without its n calls of forward(): fills the K/V cache rows of positions
+ * start_pos .. start_pos + n - 1 for the n prompt tokens and produces no logits (feed the LAST prompt token to
+ * lpp_step / lpp_step_logits as usual, and only the tokens before it to this call).  With FP16 weights, an FP16
+ * cache and one GPU the tokens go through the layers in blocks of 64: every matrix is streamed once per block by a
+ * TMA-fed tensor-core GEMM (activations rounded to FP16 as operands, FP32 accumulation), followed by causal
+ * attention inside the block; other engines (or LPP_FLAG_NO_PREFILL_GEMM) run the step graph once per token.
+ * *device_ms (optional) receives the CUDA-event time. */
+lpp_status lpp_prefill(lpp_engine* e, const int* h_tokens, int n, int start_pos, float* device_ms);
 
 /* cuda_sample (src/kernels.cuh:36, src/sample.cu:210-214) on caller-supplied logits: copies
  * h_logits[vocab_size] to the device and runs the engine's sampler on them. */

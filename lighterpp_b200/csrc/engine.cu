@@ -33,6 +33,7 @@
 #include "common.cuh"
 #include "gemv.cuh"
 #include "ops.cuh"
+#include "prefill.cuh"
 #include "sampler.cuh"
 #include "sampler_exact.cuh"
 
@@ -172,6 +173,13 @@ struct lpp_engine {
     // graphs
     // graph variants by context length; only [0] is used at present
     cudaGraphExec_t g_full[2] = {nullptr, nullptr}, g_logits[2] = {nullptr, nullptr};
+
+    // batched prompt path (allocated by the first lpp_prefill)
+    float *pf_x = nullptr, *pf_q = nullptr;
+    __half *pf_xn = nullptr, *pf_att = nullptr, *pf_hb = nullptr;
+    int* pf_tokens = nullptr;
+    CUtensorMap pf_map_wqkv, pf_map_wo, pf_map_w13, pf_map_w2, pf_map_xn, pf_map_att, pf_map_hb;
+    bool pf_ready = false;
 
     bool finalized = false;
     int kernels_full = 0;
@@ -434,29 +442,15 @@ static cudaError_t launch_sampler(lpp_engine* e, cudaStream_t s, bool pdl, bool 
     return launch_kernel(sample_kernel, dim3(e->sample_blocks), dim3(kSampleThreads), 0, s, pdl, a);
 }
 
-// Start and size of the weight matrix a GEMV kind streams in layer l (this rank's share).
-static void matrix_span(const lpp_engine* e, int kind, int l, const void** ptr, size_t* bytes) {
-    const size_t D = e->c.dim, esz = e->esz;
-    const size_t qkv_rows = e->Dq + 2 * (size_t)e->KVd;
-    switch (kind) {
-        case kQkv: *bytes = qkv_rows * D * esz; *ptr = (const char*)e->wqkv + l * *bytes; break;
-        case kOproj: *bytes = D * e->Dq * esz; *ptr = (const char*)e->wo + l * *bytes; break;
-        case kGateUp: *bytes = 2 * (size_t)e->Fl * D * esz; *ptr = (const char*)e->w13 + l * *bytes; break;
-        case kDown: *bytes = D * e->Fl * esz; *ptr = (const char*)e->w2 + l * *bytes; break;
-        default:
-            *bytes = (size_t)e->c.vocab_size * D * esz;
-            *ptr = e->wcls;
-            if (tp_cls_sharded(e)) {  // this rank's vocabulary rows
-                *bytes /= e->c.tp_size;
-                *ptr = (const char*)e->wcls + (size_t)e->c.tp_rank * *bytes;
-            }
-            break;
-    }
-}
 // ---- tensor-parallel exchange buffer layout: [epoch word, padded to 256 B][2 * n_layers receive areas],
 //      a receive area = [tp][dim] 64-bit {value, flag} words
 static size_t tp_header_bytes() { return 1024; }  // epoch word at 0, hint counters (one per exchange) from byte 256
-static size_t tp_area_bytes(const lpp_engine* e) { return (size_t)e->c.tp_size * e->c.dim * sizeof(unsigned long long); }
+// a receive area = [tp + 1][dim] words: one slot per rank, then the slot for the rank-summed vector (two-level staging)
+static size_t tp_area_bytes(const lpp_engine* e) { return (size_t)(e->c.tp_size + 1) * e->c.dim * sizeof(unsigned long long); }
+static bool tp_two_level(const lpp_engine* e) {
+    if (const char* v = aid_env("LPP_TP_TWO_LEVEL")) return atoi(v) != 0;
+    return e->c.tp_size >= 4;
+}
 static unsigned long long* tp_area(const lpp_engine* e, int p, int ex) {
     return reinterpret_cast<unsigned long long*>(e->peer_base[p] + tp_header_bytes() + (size_t)ex * tp_area_bytes(e));
 }
@@ -476,7 +470,7 @@ static unsigned int tp_hint_per_step(const lpp_engine* e) {
 }
 // (a single-kind timing run must not take part in exchanges: its producers would have no consumers)
 static bool tp_peer_path(const lpp_engine* e) {
-    return e->peer_ready && e->only_kind < 0 &&
+    return e->c.tp_size > 1 && e->peer_ready && e->only_kind < 0 &&
            !(e->c.flags & (LPP_FLAG_GEMV_LDG | LPP_FLAG_TP_NCCL));
 }
 // producer side: exchange `ex` takes the rows of this residual GEMV
@@ -494,6 +488,7 @@ static void tp_set_consumer(const lpp_engine* e, GemvArgs& a, int ex, float* x_s
     a.tp_size = e->c.tp_size;
     a.tp_epoch = tp_epoch_word(e);
     a.tp_in = tp_area(e, e->c.tp_rank, ex);
+    a.tp_reduced = tp_two_level(e) ? tp_area(e, e->c.tp_rank, ex) + (size_t)e->c.tp_size * e->c.dim : nullptr;
     a.tp_hint_in = tp_use_hint(e) ? tp_hint(e, e->c.tp_rank, ex) : nullptr;
     a.tp_hint_per_step = tp_hint_per_step(e);
     a.x = nullptr;
@@ -899,18 +894,14 @@ extern "C" lpp_status lpp_engine_create(const lpp_config* cfg, const void* nccl_
         nccl::result_t r = nccl::CommInitRank(&e->comm, c.tp_size, id, c.tp_rank);
         if (r != 0) return bail(fail(LPP_ERR_NCCL, "ncclCommInitRank: %s", nccl::GetErrorString(r)));
     }
-    if (c.tp_size <= kMaxTp) {
-        // Receive areas and counters of the residual-stream exchange.  Tensor parallel: used once lpp_tp_connect
-        // has mapped the peers (plus the logits area of the vocabulary-sharded classifier).  Single GPU: the
-        // same words carry the residual stream from o_proj / down to the next GEMV of this GPU.
+    if (c.tp_size > 1 && c.tp_size <= kMaxTp) {
+        // receive areas and counters of the peer-memory exchange (used once lpp_tp_connect has mapped the peers)
+        // and the logits area of the vocabulary-sharded classifier
         e->tp_buf_bytes = tp_header_bytes() + (size_t)2 * c.n_layers * tp_area_bytes(e) +
-                          (c.tp_size > 1 ? (size_t)c.vocab_size * sizeof(unsigned long long) : 0);
+                          (size_t)c.vocab_size * sizeof(unsigned long long);
         CUB(cudaMalloc(&e->tp_buf, e->tp_buf_bytes));
         CUB(cudaMemset(e->tp_buf, 0, e->tp_buf_bytes));
         e->peer_base[c.tp_rank] = e->tp_buf;
-        bool self = c.tp_size == 1 && !(c.flags & (LPP_FLAG_GEMV_LDG | LPP_FLAG_NO_SELF_FLAGS));
-        if (const char* v = aid_env("LPP_SELF_FLAGS")) self = self && atoi(v) != 0;
-        if (self) e->peer_ready = true;
     }
     CUB(cudaStreamSynchronize(e->stream));
 #undef CUB
@@ -935,7 +926,8 @@ extern "C" lpp_status lpp_engine_destroy(lpp_engine* e) {
     void* bufs[] = {e->wqkv, e->wo, e->w13, e->w2, e->emb, e->wcls_owned ? e->wcls : nullptr, e->rms_att, e->rms_ffn,
                     e->rms_final, e->kcache, e->vcache, e->xa, e->xb, e->q, e->att_out, e->hb, e->logits,
                     e->attn_part, e->attn_counters, e->samp_max, e->samp_sum, e->samp_idx, e->samp_counter,
-                    e->r_values, e->out_tokens, e->st, e->rope, e->stage, e->gtrace, e->ex_sync, e->ex_block_sum, e->ex_entry_count, e->ex_entries, e->ex_scalars};
+                    e->r_values, e->out_tokens, e->st, e->rope, e->stage, e->gtrace, e->pf_x, e->pf_q, e->pf_xn, e->pf_att, e->pf_hb,
+                    e->pf_tokens, e->ex_sync, e->ex_block_sum, e->ex_entry_count, e->ex_entries, e->ex_scalars};
     for (void* p : bufs)
         if (p) cudaFree(p);
     if (e->h_st) cudaFreeHost(e->h_st);
@@ -1199,6 +1191,167 @@ extern "C" lpp_status lpp_sample_logits(lpp_engine* e, const float* h_logits, co
     CU(cudaMemcpyAsync(e->logits, h_logits, (size_t)e->c.vocab_size * 4, cudaMemcpyHostToDevice, e->stream));
     CU(launch_sampler(e, e->stream, false));
     return pull_result(e, token);
+}
+
+// ------------------------------------------------------------------ batched prompt path
+
+typedef CUresult (*encode_tiled_fn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                    const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                    CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// Tensor map over a row-major FP16 matrix [rows][cols] of THIS GPU's memory, box = box_rows x kPfKc, no swizzle
+// (the kernel reads 16-byte pieces in an order that needs none), out-of-range elements read as zero.
+static lpp_status make_map(CUtensorMap* m, const void* base, size_t rows, size_t cols, int box_rows) {
+    static encode_tiled_fn encode = nullptr;
+    if (!encode) {
+        cudaDriverEntryPointQueryResult qr;
+        void* fn = nullptr;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qr) != cudaSuccess || !fn ||
+            qr != cudaDriverEntryPointSuccess)
+            return fail(LPP_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+        encode = (encode_tiled_fn)fn;
+    }
+    const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
+    const cuuint32_t box[2] = {(cuuint32_t)kPfKc, (cuuint32_t)box_rows};
+    const cuuint32_t estr[2] = {1, 1};
+    const CUresult r = encode(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(LPP_ERR_CUDA, "cuTensorMapEncodeTiled failed (%d) for a %zu x %zu matrix", (int)r, rows, cols);
+    return LPP_OK;
+}
+
+// The tensor-core path takes FP16 weights, an FP16 cache and a single GPU; everything else is fed token by token.
+static bool prefill_batched(const lpp_engine* e) {
+    return e->c.tp_size == 1 && e->c.weight_dtype == LPP_F16 && e->c.kv_dtype == LPP_F16 && e->hs <= 128 && e->gqa <= 8 &&
+           !(e->c.flags & LPP_FLAG_NO_PREFILL_GEMM);
+}
+
+static lpp_status prefill_setup(lpp_engine* e) {
+    if (e->pf_ready) return LPP_OK;
+    const lpp_config& c = e->c;
+    const size_t D = c.dim, L = c.n_layers, T = kPrefillTokens;
+    const size_t qkv_rows = e->Dq + 2 * (size_t)e->KVd;
+    CU(cudaMalloc(&e->pf_x, T * D * 4));
+    CU(cudaMalloc(&e->pf_q, T * e->Dq * 4));
+    CU(cudaMalloc(&e->pf_xn, T * D * 2));
+    CU(cudaMalloc(&e->pf_att, T * e->Dq * 2));
+    CU(cudaMalloc(&e->pf_hb, T * e->Fl * 2));
+    CU(cudaMalloc(&e->pf_tokens, T * sizeof(int)));
+    CU(cudaMemsetAsync(e->pf_x, 0, T * D * 4, e->stream));
+    CU(cudaMemsetAsync(e->pf_xn, 0, T * D * 2, e->stream));
+    CU(cudaMemsetAsync(e->pf_att, 0, T * e->Dq * 2, e->stream));
+    CU(cudaMemsetAsync(e->pf_hb, 0, T * e->Fl * 2, e->stream));
+    CU(cudaMemsetAsync(e->pf_tokens, 0, T * sizeof(int), e->stream));
+    TRY(make_map(&e->pf_map_wqkv, e->wqkv, L * qkv_rows, D, kPfRows));
+    TRY(make_map(&e->pf_map_wo, e->wo, L * D, e->Dq, kPfRows));
+    TRY(make_map(&e->pf_map_w13, e->w13, L * 2 * e->Fl, D, kPfRows));
+    TRY(make_map(&e->pf_map_w2, e->w2, L * D, e->Fl, kPfRows));
+    TRY(make_map(&e->pf_map_xn, e->pf_xn, T, D, kPrefillTokens));
+    TRY(make_map(&e->pf_map_att, e->pf_att, T, e->Dq, kPrefillTokens));
+    TRY(make_map(&e->pf_map_hb, e->pf_hb, T, e->Fl, kPrefillTokens));
+    CU(cudaFuncSetAttribute(prefill_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kPfSmemBytes));
+    e->pf_ready = true;
+    return LPP_OK;
+}
+
+static cudaError_t launch_prefill_gemm(lpp_engine* e, const CUtensorMap& wm, const CUtensorMap& xm, PrefillGemmArgs a) {
+    const int tiles = (a.n_rows + kPfRows - 1) / kPfRows;
+    a.st = e->st;
+    return launch_kernel(prefill_gemm_kernel, dim3(std::min(tiles, e->num_sms)), dim3(kPfThreads), (size_t)kPfSmemBytes,
+                         e->stream, true, wm, xm, a);
+}
+
+// One block of n <= kPrefillTokens prompt tokens at positions start_pos ..: seven kernels per layer.
+static lpp_status prefill_block(lpp_engine* e, const int* h_tokens, int n, int start_pos) {
+    const lpp_config& c = e->c;
+    const int D = c.dim, L = c.n_layers;
+    const int qkv_rows = e->Dq + 2 * e->KVd;
+    CU(cudaMemcpyAsync(e->pf_tokens, h_tokens, (size_t)n * sizeof(int), cudaMemcpyHostToDevice, e->stream));
+    for (int l = 0; l < L; ++l) {
+        CU(launch_kernel(prefill_norm_kernel, dim3(n), dim3(256), 0, e->stream, l > 0, e->pf_x, (const int*)e->pf_tokens,
+                         (const __half*)(l == 0 ? e->emb : nullptr), c.vocab_size, (const float*)(e->rms_att + (size_t)l * D),
+                         e->pf_xn, D, n, e->st));
+        const size_t lofs = (size_t)l * e->KVHl * c.seq_len * e->hs;
+        PrefillGemmArgs g = {};
+        g.n_tokens = n;
+        g.start_pos = start_pos;
+        g.n_rows = qkv_rows;
+        g.K = D;
+        g.row0 = l * qkv_rows;
+        g.epi = kPfQkv;
+        g.q = e->pf_q;
+        g.q_rows = e->Dq;
+        g.kv_rows = e->KVd;
+        g.head_size = e->hs;
+        g.seq_len = c.seq_len;
+        g.rope = e->rope;
+        g.k_cache = (__half*)e->kcache + lofs;
+        g.v_cache = (__half*)e->vcache + lofs;
+        CU(launch_prefill_gemm(e, e->pf_map_wqkv, e->pf_map_xn, g));
+        CU(launch_kernel(prefill_attention_kernel, dim3(n, e->KVHl), dim3(32 * e->gqa), (size_t)e->gqa * e->hs * sizeof(float),
+                         e->stream, true, (const float*)e->pf_q, (const __half*)g.k_cache, (const __half*)g.v_cache, e->pf_att, n,
+                         start_pos, c.seq_len, e->hs, e->gqa, e->Dq));
+        PrefillGemmArgs o = {};
+        o.n_tokens = n;
+        o.start_pos = start_pos;
+        o.n_rows = D;
+        o.K = e->Dq;
+        o.row0 = l * D;
+        o.epi = kPfResid;
+        o.x = e->pf_x;
+        CU(launch_prefill_gemm(e, e->pf_map_wo, e->pf_map_att, o));
+        CU(launch_kernel(prefill_norm_kernel, dim3(n), dim3(256), 0, e->stream, true, e->pf_x, (const int*)e->pf_tokens,
+                         (const __half*)nullptr, c.vocab_size, (const float*)(e->rms_ffn + (size_t)l * D), e->pf_xn, D, n, e->st));
+        PrefillGemmArgs u = {};
+        u.n_tokens = n;
+        u.start_pos = start_pos;
+        u.n_rows = 2 * e->Fl;
+        u.K = D;
+        u.row0 = l * 2 * e->Fl;
+        u.epi = kPfSwiglu;
+        u.hb = e->pf_hb;
+        CU(launch_prefill_gemm(e, e->pf_map_w13, e->pf_map_xn, u));
+        PrefillGemmArgs d = {};
+        d.n_tokens = n;
+        d.start_pos = start_pos;
+        d.n_rows = D;
+        d.K = e->Fl;
+        d.row0 = l * D;
+        d.epi = kPfResid;
+        d.x = e->pf_x;
+        CU(launch_prefill_gemm(e, e->pf_map_w2, e->pf_map_hb, d));
+    }
+    return LPP_OK;
+}
+
+extern "C" lpp_status lpp_prefill(lpp_engine* e, const int* h_tokens, int n, int start_pos, float* device_ms) {
+    NEED_READY(e);
+    if (!h_tokens || n <= 0) return fail(LPP_ERR_INVALID_ARG, "bad argument");
+    if (start_pos < 0 || start_pos + n > e->c.seq_len) return fail(LPP_ERR_INVALID_ARG, "positions %d..%d outside [0, %d)", start_pos, start_pos + n - 1, e->c.seq_len);
+    for (int i = 0; i < n; ++i)
+        if (h_tokens[i] < 0 || h_tokens[i] >= e->c.vocab_size) return fail(LPP_ERR_INVALID_ARG, "token %d outside [0, %d)", h_tokens[i], e->c.vocab_size);
+    TRY(push_state(e, h_tokens[0], start_pos, nullptr, nullptr, 0, 0.f, 0, 0));  // clears the device status
+    if (prefill_batched(e)) {
+        TRY(prefill_setup(e));
+        CU(cudaEventRecord(e->ev0, e->stream));
+        for (int i = 0; i < n; i += kPrefillTokens) TRY(prefill_block(e, h_tokens + i, std::min(kPrefillTokens, n - i), start_pos + i));
+        CU(cudaEventRecord(e->ev1, e->stream));
+    } else {
+        // token by token through the step graph without its sampler, like the reference's prompt loop
+        CU(cudaEventRecord(e->ev0, e->stream));
+        for (int i = 0; i < n; ++i) {
+            TRY(push_state(e, h_tokens[i], start_pos + i, nullptr, nullptr, 0, 0.f, 0, 0));
+            TRY(run_step(e, false, start_pos + i));
+            // the pinned staging block of push_state is rewritten by the next token: the copy must have run
+            if (i + 1 < n) CU(cudaStreamSynchronize(e->stream));
+        }
+        CU(cudaEventRecord(e->ev1, e->stream));
+    }
+    TRY(pull_result(e, nullptr));
+    if (device_ms) CU(cudaEventElapsedTime(device_ms, e->ev0, e->ev1));
+    return LPP_OK;
 }
 
 // ------------------------------------------------------------------ KV cache access

@@ -65,9 +65,9 @@ struct GemvArgs {
     int debug;        // timing experiments only: 1 = consumers skip the arithmetic, 2 = producer skips the copies
     int xs_bytes;     // shared-memory bytes reserved for the staged input (0 = K floats rounded up to 128)
     unsigned long long* trace;  // timing experiments only: [CTA][8] global-timer stamps, nullptr = none
-    // ---- exchange of the residual stream as self-validating words (null pointers = not used; with tp_size 1 the
-    // "exchange" is local: the consumer starts on the arrival of the data instead of on the completion of the
-    // producing grid, which takes a kernel boundary's drain-and-wake latency off the critical path).
+    // ---- tensor-parallel exchange over peer memory (null pointers = not used).  (The same words used on ONE
+    // GPU, so that a consumer starts on the arrival of its input instead of on the completion of the producing
+    // grid, measured 45 us per token SLOWER than the programmatic kernel boundary: 1.4 us per exchange.)
     // Every result travels as one 64-bit word {value, flag}, flag = the step's epoch + 1, so a word is
     // either old or complete and no fence or counter is needed.  Residual epilogue: every rank stores its
     // partial rows into slot `rank` of the exchange's receive area on EVERY rank (plain peer stores over
@@ -76,6 +76,7 @@ struct GemvArgs {
     // activations.  The epoch word is local to each rank and bumped once at the end of every step.
     unsigned long long* tp_out[kMaxTp];  // this rank's slot [n_rows] in rank p's receive area
     const unsigned long long* tp_in;     // local receive area [tp_size][K] of the exchange that produced the input
+    unsigned long long* tp_reduced;      // local area [K] for the rank-summed vector (null = every CTA adds the slots itself)
     const unsigned int* tp_epoch;        // local epoch word
     int tp_size;
     // Arrival hint: every CTA of a producing GEMV bumps (relaxed, unordered with the data) one counter per
@@ -168,10 +169,10 @@ __device__ __forceinline__ void stage_input_peers(const GemvArgs& a, float* xs, 
     if (tid == 0) gemv_stamp(a, 1);
     constexpr int kPer = 4, kRanks = 2;
     const bool store = a.x_store && blockIdx.x == 0;
-    float ss = 0.f;
-    for (int base = 0; base < nv4; base += kPer * NT) {
-        float4 sum[kPer];
-        for (int r0 = 0; r0 < a.tp_size; r0 += kRanks) {
+    // sum[j] = sum over the n_slots slots of `src` (rank order) of the four values at float4 index idx[j];
+    // polls (bounded) until every word carries this step's flag
+    auto gather = [&](const unsigned long long* src, int n_slots, const int (&idx)[kPer], float4 (&sum)[kPer]) {
+        for (int r0 = 0; r0 < n_slots; r0 += kRanks) {
             unsigned long long w[kRanks][kPer][4];
             long long t0 = 0, limit = 0;
             while (true) {
@@ -179,9 +180,8 @@ __device__ __forceinline__ void stage_input_peers(const GemvArgs& a, float* xs, 
                 for (int rr = 0; rr < kRanks; ++rr)
 #pragma unroll
                     for (int j = 0; j < kPer; ++j) {
-                        const int i = base + tid + j * NT;
-                        if (r0 + rr < a.tp_size && i < nv4) {
-                            const unsigned long long* p = a.tp_in + (size_t)(r0 + rr) * K + ((size_t)i << 2);
+                        if (r0 + rr < n_slots && idx[j] >= 0) {
+                            const unsigned long long* p = src + (size_t)(r0 + rr) * K + ((size_t)idx[j] << 2);
                             asm volatile("ld.volatile.global.v2.u64 {%0,%1}, [%2];" : "=l"(w[rr][j][0]), "=l"(w[rr][j][1]) : "l"(p) : "memory");
                             asm volatile("ld.volatile.global.v2.u64 {%0,%1}, [%2];" : "=l"(w[rr][j][2]), "=l"(w[rr][j][3]) : "l"(p + 2) : "memory");
                         }
@@ -191,7 +191,7 @@ __device__ __forceinline__ void stage_input_peers(const GemvArgs& a, float* xs, 
                 for (int rr = 0; rr < kRanks; ++rr)
 #pragma unroll
                     for (int j = 0; j < kPer; ++j)
-                        if (r0 + rr < a.tp_size && base + tid + j * NT < nv4)
+                        if (r0 + rr < n_slots && idx[j] >= 0)
 #pragma unroll
                             for (int q = 0; q < 4; ++q) pending |= (unsigned int)(w[rr][j][q] >> 32) != flag;
                 if (!pending) break;
@@ -209,7 +209,7 @@ __device__ __forceinline__ void stage_input_peers(const GemvArgs& a, float* xs, 
             for (int rr = 0; rr < kRanks; ++rr)
 #pragma unroll
                 for (int j = 0; j < kPer; ++j)
-                    if (r0 + rr < a.tp_size && base + tid + j * NT < nv4) {
+                    if (r0 + rr < n_slots && idx[j] >= 0) {
                         const float4 u = make_float4(__uint_as_float((unsigned int)w[rr][j][0]), __uint_as_float((unsigned int)w[rr][j][1]),
                                                      __uint_as_float((unsigned int)w[rr][j][2]), __uint_as_float((unsigned int)w[rr][j][3]));
                         if (r0 + rr == 0) {
@@ -220,10 +220,44 @@ __device__ __forceinline__ void stage_input_peers(const GemvArgs& a, float* xs, 
                         }
                     }
         }
+    };
+    const unsigned long long* src = a.tp_in;
+    int n_slots = a.tp_size;
+    if (a.tp_reduced) {
+        // Two levels (four ranks and more).  Every CTA of this grid adds the rank slots of ITS slice of the vector
+        // and publishes the sums, again as flagged words, in a local area; then all CTAs read that one area.  A
+        // CTA so pulls K + tp*K/grid words through its L2 port instead of tp*K (262 KB at eight ranks), at the
+        // price of one more store-to-load hop inside this GPU.
+        const int s0 = (int)(((long long)blockIdx.x * nv4) / gridDim.x), s1 = (int)(((long long)(blockIdx.x + 1) * nv4) / gridDim.x);
+        for (int base = s0; base < s1; base += kPer * NT) {
+            int idx[kPer];
+            float4 sum[kPer];
+#pragma unroll
+            for (int j = 0; j < kPer; ++j) idx[j] = (base + tid + j * NT < s1) ? base + tid + j * NT : -1;
+            gather(a.tp_in, a.tp_size, idx, sum);
+            const unsigned long long fl = (unsigned long long)flag << 32;
+#pragma unroll
+            for (int j = 0; j < kPer; ++j)
+                if (idx[j] >= 0) {
+                    unsigned long long* q = a.tp_reduced + ((size_t)idx[j] << 2);
+                    asm volatile("st.volatile.global.v2.u64 [%0], {%1,%2};" ::"l"(q), "l"(fl | __float_as_uint(sum[j].x)), "l"(fl | __float_as_uint(sum[j].y)) : "memory");
+                    asm volatile("st.volatile.global.v2.u64 [%0], {%1,%2};" ::"l"(q + 2), "l"(fl | __float_as_uint(sum[j].z)), "l"(fl | __float_as_uint(sum[j].w)) : "memory");
+                }
+        }
+        src = a.tp_reduced;
+        n_slots = 1;
+    }
+    float ss = 0.f;
+    for (int base = 0; base < nv4; base += kPer * NT) {
+        int idx[kPer];
+        float4 sum[kPer];
+#pragma unroll
+        for (int j = 0; j < kPer; ++j) idx[j] = (base + tid + j * NT < nv4) ? base + tid + j * NT : -1;
+        gather(src, n_slots, idx, sum);
 #pragma unroll
         for (int j = 0; j < kPer; ++j) {
-            const int i = base + tid + j * NT;
-            if (i < nv4) {
+            const int i = idx[j];
+            if (i >= 0) {
                 ss = fmaf(sum[j].x, sum[j].x, fmaf(sum[j].y, sum[j].y, fmaf(sum[j].z, sum[j].z, fmaf(sum[j].w, sum[j].w, ss))));
                 *xs_ptr4<WT>(xs, i << 2, K) = sum[j];
                 if (store) reinterpret_cast<float4*>(a.x_store)[i] = sum[j];  // the residual stream

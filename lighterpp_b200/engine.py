@@ -25,14 +25,14 @@ TENSOR_IDS = {"tok_emb": 0, "rms_att": 1, "wq": 2, "wk": 3, "wv": 4, "wo": 5, "r
               "w3": 9, "rms_final": 10, "w_cls": 11}
 _UNSTACKED = ("tok_emb", "rms_final", "w_cls")
 TP_HANDLE_BYTES = 64
-FLAG_TP_NCCL, FLAG_TP_LOCAL, FLAG_NO_SELF_FLAGS = 32, 64, 128
+FLAG_TP_NCCL, FLAG_TP_LOCAL, FLAG_NO_PREFILL_GEMM = 32, 64, 128
 KINDS = ["qkv_gemv", "attention", "oproj_gemv", "gateup_gemv", "down_gemv", "lmhead_gemv", "sampler", "allreduce",
          "reserved8", "reserved9"]
 
 # every symbol include/lpp_b200.h declares; tests check the built library exports all of them
 EXPORTS = [
     "lpp_engine_create", "lpp_engine_destroy", "lpp_nccl_unique_id", "lpp_upload_tensor", "lpp_finalize",
-    "lpp_step", "lpp_step_logits", "lpp_decode", "lpp_sample_logits", "lpp_kv_prefill", "lpp_kv_read",
+    "lpp_step", "lpp_step_logits", "lpp_decode", "lpp_prefill", "lpp_sample_logits", "lpp_kv_prefill", "lpp_kv_read",
     "lpp_kv_index", "lpp_strerror", "lpp_last_error", "lpp_engine_stream", "lpp_kernels_per_step",
     "lpp_step_bytes", "lpp_profile_step", "lpp_profile_kind", "lpp_tp_export", "lpp_tp_connect", "lpp_op_convert_f32_to_f16", "lpp_op_gemv", "lpp_op_rmsnorm",
     "lpp_op_rope", "lpp_op_swiglu", "lpp_op_softmax_multihead", "lpp_op_scale_multihead",
@@ -83,6 +83,7 @@ def load_library() -> C.CDLL:
     lib.lpp_decode.argtypes = [vp, C.c_int, C.c_int, C.c_int, C.POINTER(SampleParams), ip, C.c_int, C.c_int, fp, ip,
                                fp]
     lib.lpp_sample_logits.argtypes = [vp, fp, C.POINTER(SampleParams), ip, C.c_int, C.c_float, ip]
+    lib.lpp_prefill.argtypes = [vp, ip, C.c_int, C.c_int, fp]
     lib.lpp_kv_prefill.argtypes = [vp, C.c_int, vp, vp, C.c_int, C.c_int, C.c_int]
     lib.lpp_kv_read.argtypes = [vp, C.c_int, C.c_int, C.c_int, fp, fp]
     lib.lpp_kv_index.argtypes = [vp, C.c_int, C.c_int, C.c_int, C.c_int]
@@ -206,6 +207,15 @@ class Engine:
                                    rv.ctypes.data_as(C.POINTER(C.c_float)) if rv is not None else None,
                                    out.ctypes.data_as(C.POINTER(C.c_int)), C.byref(ms)), "lpp_decode")
         return out, ms.value
+
+    def prefill(self, tokens: Sequence[int], start_pos: int = 0) -> float:
+        """The prompt loop of src/main.cpp:163-179 as one batched pass: fills the K/V cache for ``tokens`` at positions
+        ``start_pos ..`` (no logits; the last prompt token still goes through ``forward``).  Returns device ms."""
+        toks = np.ascontiguousarray(tokens, dtype=np.int32)
+        ms = C.c_float(0)
+        _check(self.lib.lpp_prefill(self.h, toks.ctypes.data_as(C.POINTER(C.c_int)), int(toks.size), int(start_pos),
+                                    C.byref(ms)), "lpp_prefill")
+        return ms.value
 
     def sample(self, logits: np.ndarray, temperature: float, penalty: float = 1.0, history: Sequence[int] = (),
                r: float = 0.0) -> int:
