@@ -57,7 +57,7 @@ class ClockSampler:
     def __enter__(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.Q}",
-                                          "--format=csv,noheader,nounits", "-lms", "25"],
+                                          "--format=csv,noheader,nounits", "-lms", os.environ.get("LPP_BENCH_LMS", "25")],
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.t = threading.Thread(target=self._read, daemon=True)
             self.t.start()
@@ -125,12 +125,9 @@ def tp1_same_workload(args, cfg, dtype, tied, seed, local, n_prompt, temp, pen, 
     torch.cuda.empty_cache()
     prompt = synth.prompt_tokens(cfg.vocab_size, n_prompt, seed)
     rs = np.random.default_rng(seed).random(8 + steps).astype(np.float32)
-    hist = []
-    for pos, t in enumerate(prompt[:-1]):
-        hist = (hist + [int(t)])[-64:]
-        eng.forward(int(t), pos, temp, 1.1, hist, 0.5)
+    hist = [int(t) for t in prompt][-64:]
+    eng.prefill(prompt[:-1], 0)
     tok, pos = int(prompt[-1]), n_prompt - 1
-    hist = (hist + [tok])[-64:]
     out, _ = eng.decode(tok, pos, 8, temp, pen, hist, 64, rs[:8])
     hist = (hist + [int(x) for x in out])[-64:]
     tok, pos = int(out[-1]), pos + 8
@@ -223,13 +220,12 @@ def run_ours(args, rank, world):
             v = torch.randn((cfg.n_kv_heads, prefill, cfg.head_size), device="cuda", generator=g).half()
             eng.kv_prefill(l, k, v, prefill)
         del k, v
-    # prompt: token by token through the same step, as the reference does (src/main.cpp:163-179)
-    hist = []
-    for i, t in enumerate(prompt[:-1]):
-        hist = (hist + [int(t)])[-64:]
-        eng.forward(int(t), prefill + i, temp, 1.1, hist, 0.5)
+    # prompt: one batched pass over the weights (lpp_prefill) on a single GPU with FP16 weights; token by token through
+    # the step, as the reference does (src/main.cpp:163-179), on the engines that have no batched path.  Untimed
+    # here; the line reports both ways of feeding the same prompt.
+    hist = [int(t) for t in prompt][-64:]
+    prompt_ms = eng.prefill(prompt[:-1], prefill)
     tok, pos = int(prompt[-1]), prefill + n_prompt - 1
-    hist = (hist + [tok])[-64:]
     # the clock sampler starts before the warm-up: nvidia-smi needs a moment to come up, and the short timed region
     # of the larger rank counts would otherwise pass between two samples (idle samples are filtered out)
     with ClockSampler(local) as clk:
@@ -328,7 +324,23 @@ def run_ours(args, rank, world):
                             "gbs": round(v["bytes"] / v["ms"] / 1e6, 1) if v["ms"] else None}
                         for k, v in prof.items() if v["launches"]},
         }
+    prompt_info = None
+    if world == 1 and not prefill:
+        # the prompt again, both ways, on the finished engine (its cache rows are simply rewritten)
+        loop_ms = 0.0
+        batched = min(eng.prefill(prompt[:-1], 0) for _ in range(3))
+        t0 = time.perf_counter()
+        for i, t in enumerate(prompt[:-1]):
+            eng.step_logits(int(t), i)
+        loop_ms = (time.perf_counter() - t0) * 1e3
+        prompt_info = {"tokens": int(len(prompt) - 1), "batched_ms": round(batched, 3),
+                       "batched_tok_s": round((len(prompt) - 1) / batched * 1e3, 1),
+                       "token_by_token_ms": round(loop_ms, 3),
+                       "token_by_token_tok_s": round((len(prompt) - 1) / loop_ms * 1e3, 1),
+                       "what": "lpp_prefill (device time) against one lpp_step_logits call per prompt token (host time)"}
     tp_logits = check_logits(eng) if world > 1 else None  # outside every timed region; all ranks take part
+    if line is not None and prompt_info is not None:
+        line["prompt"] = prompt_info
     eng.close()
     if world > 1 and not args.no_tp1:
         # the same workload on ONE GPU (rank 0 alone, the other ranks wait): the number the sharded run is a

@@ -224,19 +224,22 @@ lpp_status lpp_op_multihead_gemv(float* d_out, const float* d_q, const void* d_k
 lpp_status lpp_op_rope_scatter(float* d_q, const float* d_k, const float* d_v, void* d_kc_f16, void* d_vc_f16,
                                int layer, int pos, int dim, int n_kv_heads, int head_size, int seq_len,
                                float rope_base, void* stream);
-/* d_logits is modified in place like the reference kernel does (penalty, temperature). */
+/* cuda_sample (src/kernels.cuh:36): d_logits is modified in place like the reference kernel does (penalty,
+ * temperature, probabilities).  Runs the exact-order kernel (ids equal to the reference's CPU sample() on the same
+ * logits and r) whenever vocab_size <= 2048 x the GPU's SM count, the tree-sum kernel beyond that. */
 lpp_status lpp_op_sample(float* d_logits, int vocab_size, float temperature, float penalty, const int* d_history,
                          int history_len, float r, int* d_sampled_token, void* stream);
 
 /* lpp_op_sample for callers that must not allocate.  No counterpart in the reference: its
  * cuda_sample works in place with shared memory only, while this library's multi-block sampler needs
- * a few KiB of global scratch (step state, per-block partials, a ticket counter) that lpp_op_sample
- * takes from the stream-ordered allocator on every call.  Some hosts cannot do that: a serving
- * loop whose device memory was handed out in full at start-up, code that runs while another stream
- * is being captured into a CUDA graph in global capture mode (where allocation calls are refused),
- * or a real-time path that cannot tolerate an allocator's occasional synchronisation.  Here the
- * scratch is a fixed array inside the library image (about 18 KiB per GPU, held from load until
- * the process exits), so this call makes no allocation of any kind.
+ * global scratch (step state, per-block partials, counters, the entry lists of the exact-order kernel)
+ * that lpp_op_sample takes from the stream-ordered allocator on every call.  Some hosts cannot do that: a
+ * serving loop whose device memory was handed out in full at start-up, code that runs while another
+ * stream is being captured into a CUDA graph in global capture mode (where allocation calls are
+ * refused), or a real-time path that cannot tolerate an allocator's occasional synchronisation.  Here
+ * the scratch is a fixed array inside the library image (about 0.4 MiB per GPU, held from load until
+ * the process exits), so this call makes no allocation of any kind.  It runs the same kernels as
+ * lpp_op_sample and returns the same token.
  *
  * Limits and rules: vocab_size <= 262144 and history_len <= 4096, otherwise LPP_ERR_TOO_LARGE
  * (lpp_last_error() says which).  The first call on each device looks up the array's device address

@@ -125,17 +125,14 @@ __device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
 // Limits of device-side waits, in SM clocks.  A wait on this GPU's own work (a bulk copy, a grid barrier)
 // gives up after tens of milliseconds.  The ranks of a tensor-parallel group are separate processes whose
 // launches may be skewed by host-side delays, so the limit of a wait on a peer is seconds.  Both can be
-// shortened per engine (StepState::wait_cycles / tp_wait_cycles, from lpp_config); once a wait has run
-// out the status bit is set and no later wait of the engine spins again.
+// shortened per engine (lpp_config.wait_ms / tp_wait_ms; the first is read from StepState only once a wait
+// has lasted unusually long, the second travels as a kernel argument); once a wait has run out the status
+// bit is set and no later wait of the step spins again.
 constexpr long long kWaitCycles = 100ll * 1000 * 1000;
 constexpr long long kTpWaitCycles = 8ll * 1000 * 1000 * 1000;
 __device__ __forceinline__ long long wait_limit(const StepState* st) {
     const long long v = st ? *reinterpret_cast<const volatile long long*>(&st->wait_cycles) : 0;
     return v > 0 ? v : kWaitCycles;
-}
-__device__ __forceinline__ long long tp_wait_limit(const StepState* st) {
-    const long long v = st ? *reinterpret_cast<const volatile long long*>(&st->tp_wait_cycles) : 0;
-    return v > 0 ? v : kTpWaitCycles;
 }
 __device__ __forceinline__ bool status_timed_out(const StepState* st) {
     return (*reinterpret_cast<const volatile int*>(&st->status) & kStatusBarrierTimeout) != 0;
@@ -189,6 +186,12 @@ __device__ __forceinline__ unsigned long long l2_policy_evict_first() {
     unsigned long long p;
     asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
     return p;
+}
+
+// Asks the copy engine to pull [gsrc, gsrc+bytes) into L2 (no shared-memory destination, no
+// completion to wait for).  gsrc 16-byte aligned, bytes a multiple of 16.
+__device__ __forceinline__ void bulk_prefetch_l2(const void* gsrc, uint32_t bytes) {
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(gsrc), "r"(bytes) : "memory");
 }
 
 // ------------------------------------------------------------------ reproducible expf

@@ -442,15 +442,52 @@ static cudaError_t launch_sampler(lpp_engine* e, cudaStream_t s, bool pdl, bool 
     return launch_kernel(sample_kernel, dim3(e->sample_blocks), dim3(kSampleThreads), 0, s, pdl, a);
 }
 
+// Start and size of the weight matrix a GEMV kind streams in layer l (this rank's share).
+static void matrix_span(const lpp_engine* e, int kind, int l, const void** ptr, size_t* bytes) {
+    const size_t D = e->c.dim, esz = e->esz;
+    const size_t qkv_rows = e->Dq + 2 * (size_t)e->KVd;
+    switch (kind) {
+        case kQkv: *bytes = qkv_rows * D * esz; *ptr = (const char*)e->wqkv + l * *bytes; break;
+        case kOproj: *bytes = D * e->Dq * esz; *ptr = (const char*)e->wo + l * *bytes; break;
+        case kGateUp: *bytes = 2 * (size_t)e->Fl * D * esz; *ptr = (const char*)e->w13 + l * *bytes; break;
+        case kDown: *bytes = D * e->Fl * esz; *ptr = (const char*)e->w2 + l * *bytes; break;
+        default:
+            *bytes = (size_t)e->c.vocab_size * D * esz;
+            *ptr = e->wcls;
+            if (tp_cls_sharded(e)) {  // this rank's vocabulary rows
+                *bytes /= e->c.tp_size;
+                *ptr = (const char*)e->wcls + (size_t)e->c.tp_rank * *bytes;
+            }
+            break;
+    }
+}
+// What the GEMV (kind, l) should pull towards L2 for its successor in the step: the next matrix, or
+// its first LPP_PF_MB MiB (default 8) when it is larger.  The classifier's successor is the first
+// layer's QKV matrix of the next token.
+static void set_prefetch(const lpp_engine* e, GemvArgs& a, int kind, int l) {
+    int nk, nl = l;
+    switch (kind) {
+        case kQkv: nk = kOproj; break;
+        case kOproj: nk = kGateUp; break;
+        case kGateUp: nk = kDown; break;
+        case kDown: nk = (l + 1 < e->c.n_layers) ? kQkv : kLmHead; nl = l + 1; break;
+        default: nk = kQkv; nl = 0; break;
+    }
+    if (e->c.tp_size < 2) return;  // one GPU: no measurable effect, so a launch's DRAM traffic stays its matrix once
+    size_t cap = 8;
+    if (const char* v = aid_env("LPP_PF_MB")) cap = (size_t)std::max(0, atoi(v));
+    const void* p;
+    size_t bytes;
+    matrix_span(e, nk, nl, &p, &bytes);
+    bytes = std::min(bytes, cap << 20) & ~(size_t)15;
+    a.pf = bytes ? p : nullptr;
+    a.pf_bytes = (unsigned int)bytes;
+}
+
 // ---- tensor-parallel exchange buffer layout: [epoch word, padded to 256 B][2 * n_layers receive areas],
 //      a receive area = [tp][dim] 64-bit {value, flag} words
 static size_t tp_header_bytes() { return 1024; }  // epoch word at 0, hint counters (one per exchange) from byte 256
-// a receive area = [tp + 1][dim] words: one slot per rank, then the slot for the rank-summed vector (two-level staging)
-static size_t tp_area_bytes(const lpp_engine* e) { return (size_t)(e->c.tp_size + 1) * e->c.dim * sizeof(unsigned long long); }
-static bool tp_two_level(const lpp_engine* e) {
-    if (const char* v = aid_env("LPP_TP_TWO_LEVEL")) return atoi(v) != 0;
-    return e->c.tp_size >= 4;
-}
+static size_t tp_area_bytes(const lpp_engine* e) { return (size_t)e->c.tp_size * e->c.dim * sizeof(unsigned long long); }
 static unsigned long long* tp_area(const lpp_engine* e, int p, int ex) {
     return reinterpret_cast<unsigned long long*>(e->peer_base[p] + tp_header_bytes() + (size_t)ex * tp_area_bytes(e));
 }
@@ -488,8 +525,8 @@ static void tp_set_consumer(const lpp_engine* e, GemvArgs& a, int ex, float* x_s
     a.tp_size = e->c.tp_size;
     a.tp_epoch = tp_epoch_word(e);
     a.tp_in = tp_area(e, e->c.tp_rank, ex);
-    a.tp_reduced = tp_two_level(e) ? tp_area(e, e->c.tp_rank, ex) + (size_t)e->c.tp_size * e->c.dim : nullptr;
     a.tp_hint_in = tp_use_hint(e) ? tp_hint(e, e->c.tp_rank, ex) : nullptr;
+    a.tp_wait_cycles = e->h_st->tp_wait_cycles > 0 ? e->h_st->tp_wait_cycles : kTpWaitCycles;
     a.tp_hint_per_step = tp_hint_per_step(e);
     a.x = nullptr;
     a.x_store = x_store;
@@ -509,14 +546,14 @@ static unsigned long long* tp_logits_area(const lpp_engine* e, int p) {
 // CTAs would otherwise sit beside, are not slowed by polling), then polls until every word, local or from a
 // peer, carries this step's flag (bounded) and writes the floats.
 static __global__ void __launch_bounds__(256) tp_unpack_logits_kernel(const unsigned long long* words, float* logits, int n,
-                                                                    const unsigned int* epoch, StepState* st) {
+                                                                    const unsigned int* epoch, StepState* st, long long limit) {
     pdl_launch_dependents();
     pdl_wait();
     const unsigned int flag = *epoch + 1u;
     const int i = (blockIdx.x * 256 + threadIdx.x) * 4;
     if (i >= n) return;
     unsigned long long w[4];
-    long long t0 = 0, limit = 0;
+    long long t0 = 0;
     while (true) {
         asm volatile("ld.volatile.global.v2.u64 {%0,%1}, [%2];" : "=l"(w[0]), "=l"(w[1]) : "l"(words + i) : "memory");
         asm volatile("ld.volatile.global.v2.u64 {%0,%1}, [%2];" : "=l"(w[2]), "=l"(w[3]) : "l"(words + i + 2) : "memory");
@@ -527,7 +564,6 @@ static __global__ void __launch_bounds__(256) tp_unpack_logits_kernel(const unsi
         if (t0 == 0) {
             if (status_timed_out(st)) break;
             t0 = clock64();
-            limit = tp_wait_limit(st);
         } else if (clock64() - t0 > limit) {
             atomicOr(&st->status, kStatusBarrierTimeout);
             break;
@@ -594,6 +630,7 @@ static void record_step(Recorder& R, bool with_sampler) {
             at.n_kv_heads = e->KVHl;
             if (const char* mc = aid_env("LPP_ATTN_CHUNK")) at.min_chunk = atoi(mc);  // timing experiments
             {
+                set_prefetch(e, a, kQkv, l);
                 record_gemv(R, kQkv, kEpiQkv, a);
                 dim3 grid(e->attn_splits, e->KVHl, e->attn_z);
                 if (!kind_skipped(e, kAttn)) {
@@ -622,6 +659,7 @@ static void record_step(Recorder& R, bool with_sampler) {
             a.resid = (!tp || c.tp_rank == 0) ? cur : nullptr;
             a.out = tp ? oth : cur;
             if (peers) tp_set_producer(e, a, 2 * l);
+            set_prefetch(e, a, kOproj, l);
             record_gemv(R, kOproj, kEpiResid, a);
             if (tp && !peers) {
                 record_allreduce(R, oth, D);
@@ -637,6 +675,7 @@ static void record_step(Recorder& R, bool with_sampler) {
             if (peers) tp_set_consumer(e, a, 2 * l, cur);
             a.norm_w = e->rms_ffn + (size_t)l * D;
             a.out = e->hb;
+            set_prefetch(e, a, kGateUp, l);
             record_gemv(R, kGateUp, kEpiSwiglu, a);
         }
         {  // down + residual
@@ -648,6 +687,7 @@ static void record_step(Recorder& R, bool with_sampler) {
             a.resid = (!tp || c.tp_rank == 0) ? cur : nullptr;
             a.out = tp ? oth : cur;
             if (peers) tp_set_producer(e, a, 2 * l + 1);
+            set_prefetch(e, a, kDown, l);
             record_gemv(R, kDown, kEpiResid, a);
             if (tp && !peers) {
                 record_allreduce(R, oth, D);
@@ -671,12 +711,14 @@ static void record_step(Recorder& R, bool with_sampler) {
             a.n_rows = Vl;
             for (int p = 0; p < c.tp_size; ++p) a.tp_out[p] = tp_logits_area(e, p) + r0;
         }
+        set_prefetch(e, a, kLmHead, 0);
         record_gemv(R, kLmHead, kEpiStore, a);
         if (sharded && !kind_skipped(e, kLmHead)) {
             const int V = c.vocab_size;
             R.check(launch_kernel(tp_unpack_logits_kernel, dim3((V + 1023) / 1024), dim3(256), 0, R.s, R.pdl(),
                                   (const unsigned long long*)tp_logits_area(e, c.tp_rank), e->logits, V,
-                                  (const unsigned int*)tp_epoch_word(e), e->st),
+                                  (const unsigned int*)tp_epoch_word(e), e->st,
+                                  (long long)(e->h_st->tp_wait_cycles > 0 ? e->h_st->tp_wait_cycles : kTpWaitCycles)),
                     "logits unpack launch");
             R.prev_kernel = true;
             R.kernels++;

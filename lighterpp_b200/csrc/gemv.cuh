@@ -62,6 +62,11 @@ struct GemvArgs {
     int kc;           // K elements per stage in long-row mode (multiple of 8)
     int n_stages;     // ring slots per consumer warp
     int stage_bytes;  // bytes per slot
+    // ---- L2 prefetch of the weights the NEXT kernel of the step will stream (nullptr = none).  Used by tensor-
+    // parallel engines only: there HBM idles while a consumer waits for its peers' rows, and pulling the next
+    // matrix towards L2 in that time measured 45 us per token; on one GPU it made no difference and is off.
+    const void* pf;
+    unsigned int pf_bytes;
     int debug;        // timing experiments only: 1 = consumers skip the arithmetic, 2 = producer skips the copies
     int xs_bytes;     // shared-memory bytes reserved for the staged input (0 = K floats rounded up to 128)
     unsigned long long* trace;  // timing experiments only: [CTA][8] global-timer stamps, nullptr = none
@@ -76,7 +81,6 @@ struct GemvArgs {
     // activations.  The epoch word is local to each rank and bumped once at the end of every step.
     unsigned long long* tp_out[kMaxTp];  // this rank's slot [n_rows] in rank p's receive area
     const unsigned long long* tp_in;     // local receive area [tp_size][K] of the exchange that produced the input
-    unsigned long long* tp_reduced;      // local area [K] for the rank-summed vector (null = every CTA adds the slots itself)
     const unsigned int* tp_epoch;        // local epoch word
     int tp_size;
     // Arrival hint: every CTA of a producing GEMV bumps (relaxed, unordered with the data) one counter per
@@ -86,6 +90,8 @@ struct GemvArgs {
     unsigned int* tp_hint_out[kMaxTp];   // rank p's hint counter of the exchange this GEMV produces
     const unsigned int* tp_hint_in;      // local hint counter of the exchange this GEMV consumes
     unsigned int tp_hint_per_step;       // tp_size * CTAs of the producing GEMV
+    long long tp_wait_cycles;            // limit of a wait on a peer in SM clocks (a kernel argument: the poll loop must
+                                         // not pay a global load for it)
 };
 
 // ------------------------------------------------------------------ x staging layouts
@@ -143,21 +149,24 @@ __device__ __forceinline__ void stage_input_peers(const GemvArgs& a, float* xs, 
     const int K = a.K, nv4 = K >> 2;
     const unsigned int flag = *a.tp_epoch + 1u;
     if (a.tp_hint_in) {
-        // one thread sleeps on the hint counter (bounded, then the data poll decides); a wait that has
-        // already run out on this engine is not repeated, and one that runs out here spares the data poll
-        // below, and every later kernel of the step, a second spin
+        // one thread sleeps on the hint counter (bounded, then the data poll decides).  A wait that has already
+        // run out on this engine is not repeated (the status is looked at once the counter has been slow for a
+        // while, so that the ordinary case pays nothing for it), and one that runs out here sets the status bit,
+        // which spares the data poll below and every later kernel of the step a second spin.
         if (tid == 0) {
             const unsigned int want = flag * a.tp_hint_per_step;
-            long long t0 = 0, limit = 0;
+            const long long t0 = clock64();
+            bool looked = false;
             while (true) {
                 unsigned int v;
                 asm volatile("ld.volatile.global.u32 %0, [%1];" : "=r"(v) : "l"(a.tp_hint_in) : "memory");
                 if ((int)(v - want) >= 0) break;
-                if (t0 == 0) {
+                const long long waited = clock64() - t0;
+                if (!looked && waited > (1 << 17)) {  // ~65 us: far beyond a healthy exchange
+                    looked = true;
                     if (status_timed_out(a.st)) break;
-                    t0 = clock64();
-                    limit = tp_wait_limit(a.st);
-                } else if (clock64() - t0 > limit) {
+                }
+                if (waited > a.tp_wait_cycles) {
                     atomicOr(&a.st->status, kStatusBarrierTimeout);
                     break;
                 }
@@ -169,19 +178,20 @@ __device__ __forceinline__ void stage_input_peers(const GemvArgs& a, float* xs, 
     if (tid == 0) gemv_stamp(a, 1);
     constexpr int kPer = 4, kRanks = 2;
     const bool store = a.x_store && blockIdx.x == 0;
-    // sum[j] = sum over the n_slots slots of `src` (rank order) of the four values at float4 index idx[j];
-    // polls (bounded) until every word carries this step's flag
-    auto gather = [&](const unsigned long long* src, int n_slots, const int (&idx)[kPer], float4 (&sum)[kPer]) {
-        for (int r0 = 0; r0 < n_slots; r0 += kRanks) {
+    float ss = 0.f;
+    for (int base = 0; base < nv4; base += kPer * NT) {
+        float4 sum[kPer];
+        for (int r0 = 0; r0 < a.tp_size; r0 += kRanks) {
             unsigned long long w[kRanks][kPer][4];
-            long long t0 = 0, limit = 0;
+            long long t0 = 0;
             while (true) {
 #pragma unroll
                 for (int rr = 0; rr < kRanks; ++rr)
 #pragma unroll
                     for (int j = 0; j < kPer; ++j) {
-                        if (r0 + rr < n_slots && idx[j] >= 0) {
-                            const unsigned long long* p = src + (size_t)(r0 + rr) * K + ((size_t)idx[j] << 2);
+                        const int i = base + tid + j * NT;
+                        if (r0 + rr < a.tp_size && i < nv4) {
+                            const unsigned long long* p = a.tp_in + (size_t)(r0 + rr) * K + ((size_t)i << 2);
                             asm volatile("ld.volatile.global.v2.u64 {%0,%1}, [%2];" : "=l"(w[rr][j][0]), "=l"(w[rr][j][1]) : "l"(p) : "memory");
                             asm volatile("ld.volatile.global.v2.u64 {%0,%1}, [%2];" : "=l"(w[rr][j][2]), "=l"(w[rr][j][3]) : "l"(p + 2) : "memory");
                         }
@@ -191,15 +201,14 @@ __device__ __forceinline__ void stage_input_peers(const GemvArgs& a, float* xs, 
                 for (int rr = 0; rr < kRanks; ++rr)
 #pragma unroll
                     for (int j = 0; j < kPer; ++j)
-                        if (r0 + rr < n_slots && idx[j] >= 0)
+                        if (r0 + rr < a.tp_size && base + tid + j * NT < nv4)
 #pragma unroll
                             for (int q = 0; q < 4; ++q) pending |= (unsigned int)(w[rr][j][q] >> 32) != flag;
                 if (!pending) break;
                 if (t0 == 0) {
                     if (status_timed_out(a.st)) break;
                     t0 = clock64();
-                    limit = tp_wait_limit(a.st);
-                } else if (clock64() - t0 > limit) {
+                } else if (clock64() - t0 > a.tp_wait_cycles) {
                     atomicOr(&a.st->status, kStatusBarrierTimeout);
                     break;
                 }
@@ -209,7 +218,7 @@ __device__ __forceinline__ void stage_input_peers(const GemvArgs& a, float* xs, 
             for (int rr = 0; rr < kRanks; ++rr)
 #pragma unroll
                 for (int j = 0; j < kPer; ++j)
-                    if (r0 + rr < n_slots && idx[j] >= 0) {
+                    if (r0 + rr < a.tp_size && base + tid + j * NT < nv4) {
                         const float4 u = make_float4(__uint_as_float((unsigned int)w[rr][j][0]), __uint_as_float((unsigned int)w[rr][j][1]),
                                                      __uint_as_float((unsigned int)w[rr][j][2]), __uint_as_float((unsigned int)w[rr][j][3]));
                         if (r0 + rr == 0) {
@@ -220,44 +229,10 @@ __device__ __forceinline__ void stage_input_peers(const GemvArgs& a, float* xs, 
                         }
                     }
         }
-    };
-    const unsigned long long* src = a.tp_in;
-    int n_slots = a.tp_size;
-    if (a.tp_reduced) {
-        // Two levels (four ranks and more).  Every CTA of this grid adds the rank slots of ITS slice of the vector
-        // and publishes the sums, again as flagged words, in a local area; then all CTAs read that one area.  A
-        // CTA so pulls K + tp*K/grid words through its L2 port instead of tp*K (262 KB at eight ranks), at the
-        // price of one more store-to-load hop inside this GPU.
-        const int s0 = (int)(((long long)blockIdx.x * nv4) / gridDim.x), s1 = (int)(((long long)(blockIdx.x + 1) * nv4) / gridDim.x);
-        for (int base = s0; base < s1; base += kPer * NT) {
-            int idx[kPer];
-            float4 sum[kPer];
-#pragma unroll
-            for (int j = 0; j < kPer; ++j) idx[j] = (base + tid + j * NT < s1) ? base + tid + j * NT : -1;
-            gather(a.tp_in, a.tp_size, idx, sum);
-            const unsigned long long fl = (unsigned long long)flag << 32;
-#pragma unroll
-            for (int j = 0; j < kPer; ++j)
-                if (idx[j] >= 0) {
-                    unsigned long long* q = a.tp_reduced + ((size_t)idx[j] << 2);
-                    asm volatile("st.volatile.global.v2.u64 [%0], {%1,%2};" ::"l"(q), "l"(fl | __float_as_uint(sum[j].x)), "l"(fl | __float_as_uint(sum[j].y)) : "memory");
-                    asm volatile("st.volatile.global.v2.u64 [%0], {%1,%2};" ::"l"(q + 2), "l"(fl | __float_as_uint(sum[j].z)), "l"(fl | __float_as_uint(sum[j].w)) : "memory");
-                }
-        }
-        src = a.tp_reduced;
-        n_slots = 1;
-    }
-    float ss = 0.f;
-    for (int base = 0; base < nv4; base += kPer * NT) {
-        int idx[kPer];
-        float4 sum[kPer];
-#pragma unroll
-        for (int j = 0; j < kPer; ++j) idx[j] = (base + tid + j * NT < nv4) ? base + tid + j * NT : -1;
-        gather(src, n_slots, idx, sum);
 #pragma unroll
         for (int j = 0; j < kPer; ++j) {
-            const int i = idx[j];
-            if (i >= 0) {
+            const int i = base + tid + j * NT;
+            if (i < nv4) {
                 ss = fmaf(sum[j].x, sum[j].x, fmaf(sum[j].y, sum[j].y, fmaf(sum[j].z, sum[j].z, fmaf(sum[j].w, sum[j].w, ss))));
                 *xs_ptr4<WT>(xs, i << 2, K) = sum[j];
                 if (store) reinterpret_cast<float4*>(a.x_store)[i] = sum[j];  // the residual stream
@@ -628,6 +603,18 @@ __device__ __forceinline__ bool gemv_ring_body(const GemvArgs& a, unsigned char*
                         }
             }
             if (lane == 0) gemv_stamp(a, 6);
+            // this lane's HBM requests are all queued: pull its share of the next kernel's weights
+            // towards L2 so the memory system stays busy across the kernel boundary
+            if (a.pf && alive) {
+                const unsigned int lanes = gridDim.x * kGemvConsumerWarps;
+                unsigned int slice = (a.pf_bytes + lanes - 1) / lanes;
+                slice = (slice + 15u) & ~15u;
+                const unsigned long long off = (unsigned long long)(blockIdx.x * kGemvConsumerWarps + w) * slice;
+                if (off < a.pf_bytes) {
+                    const unsigned int n = (unsigned int)min((unsigned long long)slice, (unsigned long long)a.pf_bytes - off);
+                    bulk_prefetch_l2(reinterpret_cast<const unsigned char*>(a.pf) + off, n & ~15u);
+                }
+            }
         }
         __syncwarp();
         // all of this CTA's copies are issued: the next kernel may start launching

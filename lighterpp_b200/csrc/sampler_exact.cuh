@@ -128,11 +128,17 @@ __device__ __forceinline__ bool sampler_grid_barrier(unsigned int* counter, unsi
         asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(counter) : "memory");
         if (v < target) {
             const long long t0 = clock64();
-            const long long limit = wait_limit(st);
+            long long limit = 1 << 17;  // the engine's limit is fetched from global memory only after ~65 us
+            bool fetched = false;
             while (true) {
                 asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(counter) : "memory");
                 if (v >= target) break;
                 if (clock64() - t0 > limit) {
+                    if (!fetched) {
+                        limit = wait_limit(st);
+                        fetched = true;
+                        continue;
+                    }
                     atomicOr(&st->status, kStatusBarrierTimeout);
                     ok = false;
                     break;

@@ -161,6 +161,24 @@ static void adopt_weights(RunState* s, transformerWeights* w, Config* p) {
     }
     must(lpp_finalize(e), "lpp_finalize");
     g_shim = {s, w, e};
+#ifndef LPP_SHIM_KEEP_LOADER_WEIGHTS
+    // The engine now holds its own (fused-layout) copy: give the loaders' device tensors back so the model is
+    // resident once, not twice.  The pointers become null, which free_weights_cuda (src/loader.cpp:181-194)
+    // accepts.  A host that also calls attention() / transformer_block() above on these weights after
+    // forward() must be built with -DLPP_SHIM_KEEP_LOADER_WEIGHTS.
+    cudaDeviceSynchronize();
+    void** owned[] = {(void**)&w->d_wq, (void**)&w->d_wk, (void**)&w->d_wv, (void**)&w->d_wo, (void**)&w->d_w1,
+                      (void**)&w->d_w2, (void**)&w->d_w3, (void**)&w->d_rms_att_weight, (void**)&w->d_rms_ffn_weight,
+                      (void**)&w->d_rms_final_weight};
+    for (void** t : owned) {
+        cudaFree(*t);
+        *t = nullptr;
+    }
+    if ((void*)w->d_w_cls != (void*)w->d_token_embedding_table) cudaFree(w->d_w_cls);
+    cudaFree(w->d_token_embedding_table);
+    w->d_w_cls = nullptr;
+    w->d_token_embedding_table = nullptr;
+#endif
 }
 
 // src/model.cpp:342-371: one decode step and the fused sampler; one uniform draw per call like cuda_sample.
