@@ -139,6 +139,7 @@ struct lpp_engine {
     void *wqkv = nullptr, *wo = nullptr, *w13 = nullptr, *w2 = nullptr, *emb = nullptr, *wcls = nullptr;
     float *rms_att = nullptr, *rms_ffn = nullptr, *rms_final = nullptr;
     bool wcls_owned = false;
+    bool wcls_shard_only = false;  // an untied classifier of a tensor-parallel rank holds this rank's vocabulary rows only
     std::vector<unsigned char> got;  // upload bookkeeping: [tensor][layer]
     // state
     void *kcache = nullptr, *vcache = nullptr;
@@ -175,7 +176,7 @@ struct lpp_engine {
     cudaGraphExec_t g_full[2] = {nullptr, nullptr}, g_logits[2] = {nullptr, nullptr};
 
     // batched prompt path (allocated by the first lpp_prefill)
-    float *pf_x = nullptr, *pf_q = nullptr;
+    float *pf_x = nullptr, *pf_q = nullptr, *pf_part = nullptr;
     __half *pf_xn = nullptr, *pf_att = nullptr, *pf_hb = nullptr;
     int* pf_tokens = nullptr;
     CUtensorMap pf_map_wqkv, pf_map_wo, pf_map_w13, pf_map_w2, pf_map_xn, pf_map_att, pf_map_hb;
@@ -456,7 +457,7 @@ static void matrix_span(const lpp_engine* e, int kind, int l, const void** ptr, 
             *ptr = e->wcls;
             if (tp_cls_sharded(e)) {  // this rank's vocabulary rows
                 *bytes /= e->c.tp_size;
-                *ptr = (const char*)e->wcls + (size_t)e->c.tp_rank * *bytes;
+                if (!e->wcls_shard_only) *ptr = (const char*)e->wcls + (size_t)e->c.tp_rank * *bytes;
             }
             break;
     }
@@ -707,7 +708,7 @@ static void record_step(Recorder& R, bool with_sampler) {
         const bool sharded = tp_cls_sharded(e);
         if (sharded) {
             const int Vl = c.vocab_size / c.tp_size, r0 = c.tp_rank * Vl;
-            a.W = (const char*)e->wcls + (size_t)r0 * D * esz;
+            a.W = e->wcls_shard_only ? (const char*)e->wcls : (const char*)e->wcls + (size_t)r0 * D * esz;
             a.n_rows = Vl;
             for (int p = 0; p < c.tp_size; ++p) a.tp_out[p] = tp_logits_area(e, p) + r0;
         }
@@ -968,7 +969,7 @@ extern "C" lpp_status lpp_engine_destroy(lpp_engine* e) {
     void* bufs[] = {e->wqkv, e->wo, e->w13, e->w2, e->emb, e->wcls_owned ? e->wcls : nullptr, e->rms_att, e->rms_ffn,
                     e->rms_final, e->kcache, e->vcache, e->xa, e->xb, e->q, e->att_out, e->hb, e->logits,
                     e->attn_part, e->attn_counters, e->samp_max, e->samp_sum, e->samp_idx, e->samp_counter,
-                    e->r_values, e->out_tokens, e->st, e->rope, e->stage, e->gtrace, e->pf_x, e->pf_q, e->pf_xn, e->pf_att, e->pf_hb,
+                    e->r_values, e->out_tokens, e->st, e->rope, e->stage, e->gtrace, e->pf_x, e->pf_q, e->pf_part, e->pf_xn, e->pf_att, e->pf_hb,
                     e->pf_tokens, e->ex_sync, e->ex_block_sum, e->ex_entry_count, e->ex_entries, e->ex_scalars};
     for (void* p : bufs)
         if (p) cudaFree(p);
@@ -1056,11 +1057,17 @@ extern "C" lpp_status lpp_upload_tensor(lpp_engine* e, int which, int layer, con
             s = put_block(e, e->emb, D, wd, src, D, 0, 0, (int)V, (int)D, src_dtype, memkind);
             break;
         case LPP_T_W_CLS:
+            // With the peers mapped (lpp_tp_connect comes before the uploads in that case) the classifier is
+            // sharded by vocabulary rows and this rank never reads another rank's rows: it keeps V/tp rows.
             if (!e->wcls_owned) {
-                CU(cudaMalloc(&e->wcls, V * D * esz));
+                e->wcls_shard_only = tp_cls_sharded(e);
+                CU(cudaMalloc(&e->wcls, (e->wcls_shard_only ? V / c.tp_size : V) * D * esz));
                 e->wcls_owned = true;
             }
-            s = put_block(e, e->wcls, D, wd, src, D, 0, 0, (int)V, (int)D, src_dtype, memkind);
+            if (e->wcls_shard_only)
+                s = put_block(e, e->wcls, D, wd, src, D, r * (V / c.tp_size), 0, (int)(V / c.tp_size), (int)D, src_dtype, memkind);
+            else
+                s = put_block(e, e->wcls, D, wd, src, D, 0, 0, (int)V, (int)D, src_dtype, memkind);
             break;
         case LPP_T_RMS_ATT:
             s = put_block(e, e->rms_att + l * D, D, LPP_F32, src, D, 0, 0, 1, (int)D, src_dtype, memkind);
@@ -1114,6 +1121,8 @@ extern "C" lpp_status lpp_finalize(lpp_engine* e) {
     }
     if (c.tp_size > 1 && !e->comm && !tp_peer_path(e))
         return fail(LPP_ERR_NOT_READY, "a tensor-parallel engine without NCCL (LPP_FLAG_TP_LOCAL) needs lpp_tp_connect");
+    if (e->wcls_shard_only && !tp_cls_sharded(e))
+        return fail(LPP_ERR_NOT_READY, "the classifier was uploaded as a vocabulary shard but the engine no longer shards it");
     if (!e->wcls_owned) e->wcls = e->emb;  // tied classifier (src/loader.cpp:66, 471)
     if (e->stage) {
         cudaFree(e->stage);
@@ -1241,8 +1250,9 @@ typedef CUresult (*encode_tiled_fn)(CUtensorMap*, CUtensorMapDataType, cuuint32_
                                     const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                                     CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
-// Tensor map over a row-major FP16 matrix [rows][cols] of THIS GPU's memory, box = box_rows x kPfKc, no swizzle
-// (the kernel reads 16-byte pieces in an order that needs none), out-of-range elements read as zero.
+// Tensor map over a row-major FP16 matrix [rows][cols] of THIS GPU's memory: boxes of box_rows x 64 inputs (128
+// bytes) stored with the 128-byte swizzle, which is what makes the kernel's ldmatrix reads bank-conflict free;
+// out-of-range elements read as zero.
 static lpp_status make_map(CUtensorMap* m, const void* base, size_t rows, size_t cols, int box_rows) {
     static encode_tiled_fn encode = nullptr;
     if (!encode) {
@@ -1255,10 +1265,10 @@ static lpp_status make_map(CUtensorMap* m, const void* base, size_t rows, size_t
     }
     const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
     const cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
-    const cuuint32_t box[2] = {(cuuint32_t)kPfKc, (cuuint32_t)box_rows};
+    const cuuint32_t box[2] = {64u, (cuuint32_t)box_rows};
     const cuuint32_t estr[2] = {1, 1};
     const CUresult r = encode(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
-                              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return fail(LPP_ERR_CUDA, "cuTensorMapEncodeTiled failed (%d) for a %zu x %zu matrix", (int)r, rows, cols);
     return LPP_OK;
@@ -1280,41 +1290,58 @@ static lpp_status prefill_setup(lpp_engine* e) {
     CU(cudaMalloc(&e->pf_xn, T * D * 2));
     CU(cudaMalloc(&e->pf_att, T * e->Dq * 2));
     CU(cudaMalloc(&e->pf_hb, T * e->Fl * 2));
+    CU(cudaMalloc(&e->pf_part, (size_t)kPfMaxSplits * T * D * 4));
     CU(cudaMalloc(&e->pf_tokens, T * sizeof(int)));
     CU(cudaMemsetAsync(e->pf_x, 0, T * D * 4, e->stream));
     CU(cudaMemsetAsync(e->pf_xn, 0, T * D * 2, e->stream));
     CU(cudaMemsetAsync(e->pf_att, 0, T * e->Dq * 2, e->stream));
     CU(cudaMemsetAsync(e->pf_hb, 0, T * e->Fl * 2, e->stream));
     CU(cudaMemsetAsync(e->pf_tokens, 0, T * sizeof(int), e->stream));
-    TRY(make_map(&e->pf_map_wqkv, e->wqkv, L * qkv_rows, D, kPfRows));
-    TRY(make_map(&e->pf_map_wo, e->wo, L * D, e->Dq, kPfRows));
-    TRY(make_map(&e->pf_map_w13, e->w13, L * 2 * e->Fl, D, kPfRows));
-    TRY(make_map(&e->pf_map_w2, e->w2, L * D, e->Fl, kPfRows));
+    TRY(make_map(&e->pf_map_wqkv, e->wqkv, L * qkv_rows, D, 32));
+    TRY(make_map(&e->pf_map_wo, e->wo, L * D, e->Dq, 64));
+    TRY(make_map(&e->pf_map_w13, e->w13, L * 2 * e->Fl, D, 64));
+    TRY(make_map(&e->pf_map_w2, e->w2, L * D, e->Fl, 64));
     TRY(make_map(&e->pf_map_xn, e->pf_xn, T, D, kPrefillTokens));
     TRY(make_map(&e->pf_map_att, e->pf_att, T, e->Dq, kPrefillTokens));
     TRY(make_map(&e->pf_map_hb, e->pf_hb, T, e->Fl, kPrefillTokens));
-    CU(cudaFuncSetAttribute(prefill_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kPfSmemBytes));
+    CU(cudaFuncSetAttribute(prefill_gemm_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, kPfSmemBytes));
+    CU(cudaFuncSetAttribute(prefill_gemm_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, kPfSmemBytes));
     e->pf_ready = true;
     return LPP_OK;
 }
 
-static cudaError_t launch_prefill_gemm(lpp_engine* e, const CUtensorMap& wm, const CUtensorMap& xm, PrefillGemmArgs a) {
-    const int tiles = (a.n_rows + kPfRows - 1) / kPfRows;
+// tile_rows: 32 or 64 (must match the weight map's box).  A residual GEMM whose row tiles do not fill the GPU is
+// also cut along K; its partial sums go to pf_part and the next prefill_norm_kernel adds them up.
+static cudaError_t launch_prefill_gemm(lpp_engine* e, const CUtensorMap& wm, const CUtensorMap& xm, PrefillGemmArgs a, int tile_rows) {
+    const int tiles = (a.n_rows + tile_rows - 1) / tile_rows;
+    const int n_kc = (a.K + kPfKc - 1) / kPfKc;
     a.st = e->st;
-    return launch_kernel(prefill_gemm_kernel, dim3(std::min(tiles, e->num_sms)), dim3(kPfThreads), (size_t)kPfSmemBytes,
-                         e->stream, true, wm, xm, a);
+    a.splits = 1;
+    if (a.epi == kPfResid && tiles < e->num_sms) a.splits = std::max(1, std::min({kPfMaxSplits, n_kc, (e->num_sms + tiles - 1) / tiles}));
+    a.part = e->pf_part;
+    const int grid = std::min(tiles * a.splits, e->num_sms);
+    if (tile_rows == 32)
+        return launch_kernel(prefill_gemm_kernel<32>, dim3(grid), dim3(kPfThreads), (size_t)kPfSmemBytes, e->stream, true, wm, xm, a);
+    return launch_kernel(prefill_gemm_kernel<64>, dim3(grid), dim3(kPfThreads), (size_t)kPfSmemBytes, e->stream, true, wm, xm, a);
+}
+static int prefill_splits(const lpp_engine* e, int n_rows, int K) {  // what launch_prefill_gemm chooses for a residual GEMM
+    const int tiles = (n_rows + 63) / 64, n_kc = (K + kPfKc - 1) / kPfKc;
+    return tiles < e->num_sms ? std::max(1, std::min({kPfMaxSplits, n_kc, (e->num_sms + tiles - 1) / tiles})) : 1;
 }
 
-// One block of n <= kPrefillTokens prompt tokens at positions start_pos ..: seven kernels per layer.
+// One block of n <= kPrefillTokens prompt tokens at positions start_pos ..: seven kernels per layer; the last layer
+// stops after its K/V rows are written (nothing downstream of them is needed: the call produces no logits).
 static lpp_status prefill_block(lpp_engine* e, const int* h_tokens, int n, int start_pos) {
     const lpp_config& c = e->c;
     const int D = c.dim, L = c.n_layers;
     const int qkv_rows = e->Dq + 2 * e->KVd;
+    const int s_o = prefill_splits(e, D, e->Dq), s_d = prefill_splits(e, D, e->Fl);
     CU(cudaMemcpyAsync(e->pf_tokens, h_tokens, (size_t)n * sizeof(int), cudaMemcpyHostToDevice, e->stream));
     for (int l = 0; l < L; ++l) {
+        // layer 0 takes the embedding rows; later layers first add the previous down projection's partial sums
         CU(launch_kernel(prefill_norm_kernel, dim3(n), dim3(256), 0, e->stream, l > 0, e->pf_x, (const int*)e->pf_tokens,
                          (const __half*)(l == 0 ? e->emb : nullptr), c.vocab_size, (const float*)(e->rms_att + (size_t)l * D),
-                         e->pf_xn, D, n, e->st));
+                         e->pf_xn, D, n, (const float*)e->pf_part, l == 0 ? 1 : s_d, e->st));
         const size_t lofs = (size_t)l * e->KVHl * c.seq_len * e->hs;
         PrefillGemmArgs g = {};
         g.n_tokens = n;
@@ -1331,7 +1358,8 @@ static lpp_status prefill_block(lpp_engine* e, const int* h_tokens, int n, int s
         g.rope = e->rope;
         g.k_cache = (__half*)e->kcache + lofs;
         g.v_cache = (__half*)e->vcache + lofs;
-        CU(launch_prefill_gemm(e, e->pf_map_wqkv, e->pf_map_xn, g));
+        CU(launch_prefill_gemm(e, e->pf_map_wqkv, e->pf_map_xn, g, 32));
+        if (l == L - 1) break;
         CU(launch_kernel(prefill_attention_kernel, dim3(n, e->KVHl), dim3(32 * e->gqa), (size_t)e->gqa * e->hs * sizeof(float),
                          e->stream, true, (const float*)e->pf_q, (const __half*)g.k_cache, (const __half*)g.v_cache, e->pf_att, n,
                          start_pos, c.seq_len, e->hs, e->gqa, e->Dq));
@@ -1343,9 +1371,10 @@ static lpp_status prefill_block(lpp_engine* e, const int* h_tokens, int n, int s
         o.row0 = l * D;
         o.epi = kPfResid;
         o.x = e->pf_x;
-        CU(launch_prefill_gemm(e, e->pf_map_wo, e->pf_map_att, o));
+        CU(launch_prefill_gemm(e, e->pf_map_wo, e->pf_map_att, o, 64));
         CU(launch_kernel(prefill_norm_kernel, dim3(n), dim3(256), 0, e->stream, true, e->pf_x, (const int*)e->pf_tokens,
-                         (const __half*)nullptr, c.vocab_size, (const float*)(e->rms_ffn + (size_t)l * D), e->pf_xn, D, n, e->st));
+                         (const __half*)nullptr, c.vocab_size, (const float*)(e->rms_ffn + (size_t)l * D), e->pf_xn, D, n,
+                         (const float*)e->pf_part, s_o, e->st));
         PrefillGemmArgs u = {};
         u.n_tokens = n;
         u.start_pos = start_pos;
@@ -1354,7 +1383,7 @@ static lpp_status prefill_block(lpp_engine* e, const int* h_tokens, int n, int s
         u.row0 = l * 2 * e->Fl;
         u.epi = kPfSwiglu;
         u.hb = e->pf_hb;
-        CU(launch_prefill_gemm(e, e->pf_map_w13, e->pf_map_xn, u));
+        CU(launch_prefill_gemm(e, e->pf_map_w13, e->pf_map_xn, u, 64));
         PrefillGemmArgs d = {};
         d.n_tokens = n;
         d.start_pos = start_pos;
@@ -1363,7 +1392,7 @@ static lpp_status prefill_block(lpp_engine* e, const int* h_tokens, int n, int s
         d.row0 = l * D;
         d.epi = kPfResid;
         d.x = e->pf_x;
-        CU(launch_prefill_gemm(e, e->pf_map_w2, e->pf_map_hb, d));
+        CU(launch_prefill_gemm(e, e->pf_map_w2, e->pf_map_hb, d, 64));
     }
     return LPP_OK;
 }

@@ -6,10 +6,12 @@
 // four projections become small GEMMs  C[tokens][rows] = X[tokens][K] . W[rows][K]^T  that are still bound by
 // the weight stream (2 FLOP per weight byte and token: far below the tensor cores' ridge for a few dozen
 // tokens), so the kernel is organised around that stream exactly like the decode GEMV -- a producer warp,
-// a ring of shared-memory stages, mbarrier hand-over -- only that a stage is a 2-D tile fetched by the tensor
-// memory accelerator (cp.async.bulk.tensor.2d: 32 weight rows x 256 inputs, and the matching 64 tokens x 256
-// inputs of the activations) and the arithmetic is warp-level tensor-core MMA (m16n8k16, FP16 operands, FP32
-// accumulation).  Activations are rounded to FP16 as MMA operands; everything between the GEMMs (residual
+// a ring of shared-memory stages, mbarrier hand-over -- only that a stage is a set of 2-D tiles fetched by the
+// tensor memory accelerator (cp.async.bulk.tensor.2d with the 128-byte swizzle: 32 or 64 weight rows x 128 inputs
+// and the matching 64 tokens x 128 inputs of the activations) and the arithmetic is warp-level tensor-core MMA
+// (ldmatrix + m16n8k16, FP16 operands, FP32 accumulation).  The two matrices with few rows and a plain residual
+// epilogue (o_proj, down) are also cut along K so that every SM streams a share; their partial sums are added to
+// the residual stream in a fixed order by the next kernel.  Activations are rounded to FP16 as MMA operands; everything between the GEMMs (residual
 // stream, RMSNorm, RoPE, softmax) stays FP32, following src/ops.cpp like the decode path.
 //
 // Tensor maps cover this GPU's own memory only; no cluster multicast is used anywhere.
@@ -21,13 +23,23 @@
 namespace lpp {
 
 constexpr int kPrefillTokens = 64;   // tokens per pass (rows of the activation tiles)
-constexpr int kPfRows = 32;          // weight rows per CTA tile (two 16-row MMA tiles)
-constexpr int kPfKc = 256;           // inputs per stage
-constexpr int kPfStages = 4;
-constexpr int kPfConsumerWarps = 8;  // 2 row tiles x 4 groups of 16 tokens
+constexpr int kPfKc = 128;           // inputs per stage: two 64-wide (128-byte) swizzled sub-tiles per operand
+constexpr int kPfConsumerWarps = 8;
 constexpr int kPfThreads = (kPfConsumerWarps + 1) * 32;
-constexpr int kPfStageBytes = (kPfRows + kPrefillTokens) * kPfKc * 2;  // 48 KiB: weight tile, then activation tile
-constexpr int kPfSmemBytes = 1024 + kPfStages * kPfStageBytes;
+constexpr int kPfSubBytesX = kPrefillTokens * 128;  // one activation sub-tile: 64 tokens x 64 inputs
+constexpr int kPfMaxSplits = 8;
+constexpr int kPfRingBytes = 192 * 1024;
+constexpr int kPfSmemBytes = 1024 /*barriers*/ + 1024 /*alignment slack*/ + kPfRingBytes;
+template <int M>
+struct PfGeom {
+    static constexpr int kSubW = M * 128;                         // one weight sub-tile: M rows x 64 inputs
+    static constexpr int kStage = 2 * kSubW + 2 * kPfSubBytesX;   // 32 KiB (M = 64) / 24 KiB (M = 32)
+    static constexpr int kStages = kPfRingBytes / kStage;         // 6 / 8
+    static constexpr int kRowTiles = M / 16;                      // 16-row MMA tiles per CTA tile
+    static constexpr int kTokGroups = kPfConsumerWarps / kRowTiles;
+    static constexpr int kTokPerWarp = kPrefillTokens / kTokGroups;  // 32 / 16
+    static constexpr int kNT = kTokPerWarp / 8;                   // 8-token MMA tiles per warp
+};
 
 enum PfEpi : int { kPfQkv = 0, kPfResid = 1, kPfSwiglu = 2 };
 
@@ -37,9 +49,12 @@ struct PrefillGemmArgs {
     int n_tokens;         // valid tokens (<= kPrefillTokens)
     int start_pos;        // position of token 0
     int epi;
+    int splits;           // K is cut into this many ranges (kPfResid only when > 1): work item = (row tile, range)
     StepState* st;
-    // kPfResid: x[t][row] += c        (x: [kPrefillTokens][n_rows] FP32)
+    // kPfResid: x[t][row] += c (x: [kPrefillTokens][n_rows] FP32) when splits == 1; else the partial sums go to
+    // part[split][t][row] and the next kernel (prefill_norm_kernel) adds them to x in split order
     float* x;
+    float* part;
     // kPfSwiglu: hb[t][row/2] = silu(gate) * up   (rows interleaved gate, up; hb: FP16 [kPrefillTokens][n_rows/2])
     __half* hb;
     // kPfQkv: rows are q | k | v; RoPE on q and k, q -> FP32 [kPrefillTokens][q_rows], k/v -> cache at start_pos + t
@@ -50,9 +65,9 @@ struct PrefillGemmArgs {
     __half* v_cache;
 };
 
-__device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+__device__ __forceinline__ void tma_load_2d(uint32_t smem_dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
     asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
-                     smem_u32(smem_dst)),
+                     smem_dst),
                  "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar))
                  : "memory");
 }
@@ -62,13 +77,25 @@ __device__ __forceinline__ void mma_f16_16816(float (&d)[4], uint32_t a0, uint32
                  : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
                  : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
+__device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+// Address of 16-byte chunk `chunk` (0..7) of row `row` in a sub-tile written by the tensor memory accelerator with
+// the 128-byte swizzle (rows of 128 bytes, chunk index XOR row % 8; the sub-tile starts on a 1024-byte boundary).
+__device__ __forceinline__ uint32_t swz(uint32_t base, int row, int chunk) {
+    return base + (uint32_t)row * 128u + (uint32_t)((chunk ^ (row & 7)) << 4);
+}
 
 // One value of the finished tile: row `row` (and its pair partner `other`, the value of row ^ 1), token t.
-__device__ __forceinline__ void pf_epilogue(const PrefillGemmArgs& a, int row, int t, float v, float other) {
+__device__ __forceinline__ void pf_epilogue(const PrefillGemmArgs& a, int split, int row, int t, float v, float other) {
     if (row >= a.n_rows || t >= a.n_tokens) return;
     if (a.epi == kPfResid) {
-        float* p = a.x + (size_t)t * a.n_rows + row;
-        *p = *p + v;  // x += W.xb (src/model.cpp:232, 239)
+        if (a.splits > 1) {
+            a.part[((size_t)split * kPrefillTokens + t) * a.n_rows + row] = v;
+        } else {
+            float* p = a.x + (size_t)t * a.n_rows + row;
+            *p = *p + v;  // x += W.xb (src/model.cpp:232, 239)
+        }
     } else if (a.epi == kPfSwiglu) {
         // rows are interleaved (gate_i, up_i); hb = (h1*sigmoid(h1))*h3 (src/ops.cpp:78-87): the even row writes
         if ((row & 1) == 0) {
@@ -102,20 +129,25 @@ __device__ __forceinline__ void pf_epilogue(const PrefillGemmArgs& a, int row, i
     }
 }
 
-// C[t][row] = sum_k X[t][k] * W[row][k] for t < 64, fused with the epilogue.  grid: min(tiles, SMs) CTAs, every CTA
-// walks 32-row tiles blockIdx.x, + gridDim.x, ...; the ring runs across tile boundaries.
+// C[t][row] = sum_k X[t][k] * W[row][k] for t < 64, fused with the epilogue.  A work item is (tile of M rows, K
+// range); CTA b takes items b, b + grid, ...; the ring runs across item boundaries.  M = 32 for the matrices with
+// few rows per SM and an epilogue that needs the whole sum (QKV), 64 otherwise.
+template <int M>
 static __global__ void __launch_bounds__(kPfThreads) prefill_gemm_kernel(const __grid_constant__ CUtensorMap w_map,
                                                                           const __grid_constant__ CUtensorMap x_map,
                                                                           const PrefillGemmArgs a) {
+    using G = PfGeom<M>;
     extern __shared__ __align__(128) unsigned char smem[];
-    uint64_t* full = reinterpret_cast<uint64_t*>(smem);  // [kPfStages]
-    uint64_t* empty = full + kPfStages;                  // [kPfStages]
-    unsigned char* ring = smem + 1024;
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem);  // [kStages]
+    uint64_t* empty = full + G::kStages;                 // [kStages]
+    const uint32_t ring = (smem_u32(smem) + 1024u + 1023u) & ~1023u;  // swizzled sub-tiles start on 1024-byte boundaries
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int n_tiles = (a.n_rows + kPfRows - 1) / kPfRows;
+    const int n_tiles = (a.n_rows + M - 1) / M;
     const int n_kc = (a.K + kPfKc - 1) / kPfKc;
+    const int S = a.splits;
+    const int n_items = n_tiles * S;
     pdl_launch_dependents();
-    if (tid < kPfStages) {
+    if (tid < G::kStages) {
         mbar_init(&full[tid], 1);
         mbar_init(&empty[tid], kPfConsumerWarps);
         mbar_fence_init();
@@ -123,73 +155,82 @@ static __global__ void __launch_bounds__(kPfThreads) prefill_gemm_kernel(const _
     __syncthreads();
 
     if (warp == kPfConsumerWarps) {
-        // ---------------- producer: one lane issues the two tile copies of every stage
+        // ---------------- producer: one lane issues the four sub-tile copies of every stage
         if (lane == 0) {
             pdl_wait();  // the activation tile comes from the previous kernel (the weights do not, but share the stage)
             int slot = 0, pass = 0;
-            for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x)
-                for (int kc = 0; kc < n_kc; ++kc) {
+            for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
+                const int tile = item / S, split = item - tile * S;
+                const int kc0 = (split * n_kc) / S, kc1 = ((split + 1) * n_kc) / S;
+                for (int kc = kc0; kc < kc1; ++kc) {
                     if (pass > 0 && !mbar_wait_bounded(&empty[slot], (uint32_t)(pass - 1) & 1u, a.st)) return;
-                    unsigned char* dst = ring + (size_t)slot * kPfStageBytes;
-                    mbar_arrive_expect_tx(&full[slot], kPfStageBytes);
-                    tma_load_2d(dst, &w_map, kc * kPfKc, a.row0 + tile * kPfRows, &full[slot]);
-                    tma_load_2d(dst + kPfRows * kPfKc * 2, &x_map, kc * kPfKc, 0, &full[slot]);
-                    if (++slot == kPfStages) {
+                    const uint32_t dst = ring + (uint32_t)slot * G::kStage;
+                    mbar_arrive_expect_tx(&full[slot], G::kStage);
+                    tma_load_2d(dst, &w_map, kc * kPfKc, a.row0 + tile * M, &full[slot]);
+                    tma_load_2d(dst + G::kSubW, &w_map, kc * kPfKc + 64, a.row0 + tile * M, &full[slot]);
+                    tma_load_2d(dst + 2 * G::kSubW, &x_map, kc * kPfKc, 0, &full[slot]);
+                    tma_load_2d(dst + 2 * G::kSubW + kPfSubBytesX, &x_map, kc * kPfKc + 64, 0, &full[slot]);
+                    if (++slot == G::kStages) {
                         slot = 0;
                         ++pass;
                     }
                 }
+            }
         }
         return;
     }
 
-    // ---------------- consumers: warp = (row tile rt of the CTA tile, token group tg of 16 tokens)
-    const int rt = warp & 1, tg = warp >> 1;
+    // ---------------- consumers: warp = (16-row tile rt of the CTA tile, token group tg)
+    const int rt = warp % G::kRowTiles, tg = warp / G::kRowTiles;
     const int g = lane >> 2, j = lane & 3;
+    // ldmatrix source rows of this lane.  A (x4): matrices (rows 0-7, k 0-7), (rows 8-15, k 0-7), (rows 0-7, k 8-15),
+    // (rows 8-15, k 8-15) = a0..a3.  B (x4): (tokens 0-7, k 0-7), (tokens 0-7, k 8-15), (tokens 8-15, k 0-7),
+    // (tokens 8-15, k 8-15) = b0, b1 of two 8-token tiles.
+    const int a_row = rt * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, a_chunk = lane >> 4;
+    const int b_row = tg * G::kTokPerWarp + (lane & 7) + ((lane >> 4) & 1) * 8, b_chunk = (lane >> 3) & 1;
     int slot = 0;
     uint32_t par = 0;
-    for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
-        float acc[2][4];
+    for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
+        const int tile = item / S, split = item - tile * S;
+        const int kc0 = (split * n_kc) / S, kc1 = ((split + 1) * n_kc) / S;
+        float acc[G::kNT][4];
 #pragma unroll
-        for (int nt = 0; nt < 2; ++nt) acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f;
-        for (int kc = 0; kc < n_kc; ++kc) {
+        for (int nt = 0; nt < G::kNT; ++nt) acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f;
+        for (int kc = kc0; kc < kc1; ++kc) {
             if (!__all_sync(0xffffffffu, mbar_wait_bounded(&full[slot], par, a.st))) return;
-            const unsigned char* wt = ring + (size_t)slot * kPfStageBytes;         // [32 rows][256] halves
-            const unsigned char* xt = wt + kPfRows * kPfKc * 2;                    // [64 tokens][256] halves
-            // The sum over k does not care about order, so the k index an operand register stands for is chosen such
-            // that a lane reads whole 16-byte pieces: inside a block of 32 inputs, lane j owns inputs [8j, 8j+8)
-            // of its rows (A) and of its token (B); they feed two k-steps.
-            const unsigned char* a_lo = wt + (size_t)(rt * 16 + g) * (kPfKc * 2) + j * 16;
-            const unsigned char* a_hi = a_lo + 8 * (kPfKc * 2);
-            const unsigned char* b0p = xt + (size_t)(tg * 16 + g) * (kPfKc * 2) + j * 16;
-            const unsigned char* b1p = b0p + 8 * (kPfKc * 2);
+            const uint32_t st = ring + (uint32_t)slot * G::kStage;
 #pragma unroll
-            for (int kb = 0; kb < kPfKc / 32; ++kb) {
-                const uint4 al = *reinterpret_cast<const uint4*>(a_lo + kb * 64);
-                const uint4 ah = *reinterpret_cast<const uint4*>(a_hi + kb * 64);
-                const uint4 b0 = *reinterpret_cast<const uint4*>(b0p + kb * 64);
-                const uint4 b1 = *reinterpret_cast<const uint4*>(b1p + kb * 64);
-                mma_f16_16816(acc[0], al.x, ah.x, al.y, ah.y, b0.x, b0.y);
-                mma_f16_16816(acc[0], al.z, ah.z, al.w, ah.w, b0.z, b0.w);
-                mma_f16_16816(acc[1], al.x, ah.x, al.y, ah.y, b1.x, b1.y);
-                mma_f16_16816(acc[1], al.z, ah.z, al.w, ah.w, b1.z, b1.w);
+            for (int sub = 0; sub < 2; ++sub) {
+                const uint32_t wt = st + sub * G::kSubW, xt = st + 2 * G::kSubW + sub * kPfSubBytesX;
+#pragma unroll
+                for (int ks = 0; ks < 4; ++ks) {  // four 16-input steps per 64-wide sub-tile
+                    uint32_t a0, a1, a2, a3;
+                    ldmatrix_x4(swz(wt, a_row, 2 * ks + a_chunk), a0, a1, a2, a3);
+#pragma unroll
+                    for (int np = 0; np < G::kNT / 2; ++np) {
+                        uint32_t b0, b1, b2, b3;
+                        ldmatrix_x4(swz(xt, b_row + np * 16, 2 * ks + b_chunk), b0, b1, b2, b3);
+                        mma_f16_16816(acc[2 * np], a0, a1, a2, a3, b0, b1);
+                        mma_f16_16816(acc[2 * np + 1], a0, a1, a2, a3, b2, b3);
+                    }
+                }
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(&empty[slot]);
-            if (++slot == kPfStages) {
+            if (++slot == G::kStages) {
                 slot = 0;
                 par ^= 1u;
             }
         }
-        // acc[nt]: rows g (c0, c1) and g + 8 (c2, c3), tokens tg*16 + nt*8 + 2j (c0, c2) and + 1 (c1, c3)
-        const int row_lo = tile * kPfRows + rt * 16 + g;
+        // acc[nt]: rows g (c0, c1) and g + 8 (c2, c3), tokens tg*kTokPerWarp + nt*8 + 2j (c0, c2) and + 1 (c1, c3)
+        const int row_lo = tile * M + rt * 16 + g;
 #pragma unroll
-        for (int nt = 0; nt < 2; ++nt)
+        for (int nt = 0; nt < G::kNT; ++nt)
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
                 const float v = acc[nt][c];
                 const float other = __shfl_xor_sync(0xffffffffu, v, 4);  // the same token, row g ^ 1
-                pf_epilogue(a, row_lo + (c >> 1) * 8, tg * 16 + nt * 8 + 2 * j + (c & 1), v, other);
+                pf_epilogue(a, split, row_lo + (c >> 1) * 8, tg * G::kTokPerWarp + nt * 8 + 2 * j + (c & 1), v, other);
             }
     }
 }
@@ -198,7 +239,7 @@ static __global__ void __launch_bounds__(kPfThreads) prefill_gemm_kernel(const _
 // the prompt tokens and also writes them out as the FP32 residual stream.  grid: tokens.
 static __global__ void __launch_bounds__(256) prefill_norm_kernel(float* x, const int* tokens, const __half* emb, int vocab,
                                                                   const float* norm_w, __half* out, int D, int n_tokens,
-                                                                  StepState* st) {
+                                                                  const float* part, int splits, StepState* st) {
     __shared__ float red[8];
     pdl_launch_dependents();
     pdl_wait();
@@ -212,10 +253,16 @@ static __global__ void __launch_bounds__(256) prefill_norm_kernel(float* x, cons
         }
         const __half* er = emb + (size_t)tok * D;
         for (int i = threadIdx.x; i < D; i += 256) xr[i] = __half2float(er[i]);
-        __syncthreads();
+    } else if (splits > 1) {
+        // the preceding residual GEMM left its K-range partial sums: x += p_0 + p_1 + ... in range order
+        for (int i = threadIdx.x; i < D; i += 256) {
+            float v = xr[i];
+            for (int s = 0; s < splits; ++s) v += part[((size_t)s * kPrefillTokens + t) * D + i];
+            xr[i] = v;
+        }
     }
     float ss = 0.f;
-    for (int i = threadIdx.x; i < D; i += 256) ss = fmaf(xr[i], xr[i], ss);
+    for (int i = threadIdx.x; i < D; i += 256) ss = fmaf(xr[i], xr[i], ss);  // every thread reads back what it wrote
     ss = warp_sum(ss);
     if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
     __syncthreads();
