@@ -1268,7 +1268,7 @@ static lpp_status make_map(CUtensorMap* m, const void* base, size_t rows, size_t
     const cuuint32_t box[2] = {64u, (cuuint32_t)box_rows};
     const cuuint32_t estr[2] = {1, 1};
     const CUresult r = encode(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
-                              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return fail(LPP_ERR_CUDA, "cuTensorMapEncodeTiled failed (%d) for a %zu x %zu matrix", (int)r, rows, cols);
     return LPP_OK;
@@ -1306,6 +1306,8 @@ static lpp_status prefill_setup(lpp_engine* e) {
     TRY(make_map(&e->pf_map_hb, e->pf_hb, T, e->Fl, kPrefillTokens));
     CU(cudaFuncSetAttribute(prefill_gemm_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, kPfSmemBytes));
     CU(cudaFuncSetAttribute(prefill_gemm_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, kPfSmemBytes));
+    CU(cudaFuncSetAttribute(prefill_attention_mma_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, pf_attn_smem<64>()));
+    CU(cudaFuncSetAttribute(prefill_attention_mma_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, pf_attn_smem<128>()));
     e->pf_ready = true;
     return LPP_OK;
 }
@@ -1339,7 +1341,7 @@ static lpp_status prefill_block(lpp_engine* e, const int* h_tokens, int n, int s
     CU(cudaMemcpyAsync(e->pf_tokens, h_tokens, (size_t)n * sizeof(int), cudaMemcpyHostToDevice, e->stream));
     for (int l = 0; l < L; ++l) {
         // layer 0 takes the embedding rows; later layers first add the previous down projection's partial sums
-        CU(launch_kernel(prefill_norm_kernel, dim3(n), dim3(256), 0, e->stream, l > 0, e->pf_x, (const int*)e->pf_tokens,
+        CU(launch_kernel(prefill_norm_kernel, dim3(n), dim3(kPfNormThreads), 0, e->stream, l > 0, e->pf_x, (const int*)e->pf_tokens,
                          (const __half*)(l == 0 ? e->emb : nullptr), c.vocab_size, (const float*)(e->rms_att + (size_t)l * D),
                          e->pf_xn, D, n, (const float*)e->pf_part, l == 0 ? 1 : s_d, e->st));
         const size_t lofs = (size_t)l * e->KVHl * c.seq_len * e->hs;
@@ -1360,9 +1362,21 @@ static lpp_status prefill_block(lpp_engine* e, const int* h_tokens, int n, int s
         g.v_cache = (__half*)e->vcache + lofs;
         CU(launch_prefill_gemm(e, e->pf_map_wqkv, e->pf_map_xn, g, 32));
         if (l == L - 1) break;
-        CU(launch_kernel(prefill_attention_kernel, dim3(n, e->KVHl), dim3(32 * e->gqa), (size_t)e->gqa * e->hs * sizeof(float),
-                         e->stream, true, (const float*)e->pf_q, (const __half*)g.k_cache, (const __half*)g.v_cache, e->pf_att, n,
-                         start_pos, c.seq_len, e->hs, e->gqa, e->Dq));
+        const dim3 agrid((n + kPfAttnRows - 1) / kPfAttnRows, e->KVHl);
+        const bool pf_mma = !aid_env("LPP_ATTN_CUDA_CORES");
+        if (pf_mma && e->hs == 64 && e->gqa <= 8)
+            CU(launch_kernel(prefill_attention_mma_kernel<64>, agrid, dim3(32 * e->gqa), pf_attn_smem<64>(), e->stream, true,
+                             (const float*)e->pf_q, (const __half*)g.k_cache, (const __half*)g.v_cache, e->pf_att, n, start_pos,
+                             c.seq_len, e->gqa, e->Dq));
+        else if (pf_mma && e->hs == 128 && e->gqa <= 8)
+            CU(launch_kernel(prefill_attention_mma_kernel<128>, agrid, dim3(32 * e->gqa), pf_attn_smem<128>(), e->stream, true,
+                             (const float*)e->pf_q, (const __half*)g.k_cache, (const __half*)g.v_cache, e->pf_att, n, start_pos,
+                             c.seq_len, e->gqa, e->Dq));
+        else
+            CU(launch_kernel(prefill_attention_kernel, dim3(n, e->KVHl), dim3(32 * e->gqa),
+                             (size_t)e->gqa * e->hs * sizeof(float), e->stream, true, (const float*)e->pf_q,
+                             (const __half*)g.k_cache, (const __half*)g.v_cache, e->pf_att, n, start_pos, c.seq_len, e->hs,
+                             e->gqa, e->Dq));
         PrefillGemmArgs o = {};
         o.n_tokens = n;
         o.start_pos = start_pos;
@@ -1372,7 +1386,7 @@ static lpp_status prefill_block(lpp_engine* e, const int* h_tokens, int n, int s
         o.epi = kPfResid;
         o.x = e->pf_x;
         CU(launch_prefill_gemm(e, e->pf_map_wo, e->pf_map_att, o, 64));
-        CU(launch_kernel(prefill_norm_kernel, dim3(n), dim3(256), 0, e->stream, true, e->pf_x, (const int*)e->pf_tokens,
+        CU(launch_kernel(prefill_norm_kernel, dim3(n), dim3(kPfNormThreads), 0, e->stream, true, e->pf_x, (const int*)e->pf_tokens,
                          (const __half*)nullptr, c.vocab_size, (const float*)(e->rms_ffn + (size_t)l * D), e->pf_xn, D, n,
                          (const float*)e->pf_part, s_o, e->st));
         PrefillGemmArgs u = {};

@@ -237,39 +237,97 @@ static __global__ void __launch_bounds__(kPfThreads) prefill_gemm_kernel(const _
 
 // Rows of the residual stream -> RMS-normalised FP16 rows (MMA operands).  Layer 0 takes the embedding rows of
 // the prompt tokens and also writes them out as the FP32 residual stream.  grid: tokens.
-static __global__ void __launch_bounds__(256) prefill_norm_kernel(float* x, const int* tokens, const __half* emb, int vocab,
-                                                                  const float* norm_w, __half* out, int D, int n_tokens,
-                                                                  const float* part, int splits, StepState* st) {
-    __shared__ float red[8];
+constexpr int kPfNormThreads = 512;
+// Only the weights (emb, norm_w) are marked read-only: a pointer to data the preceding kernel produced must not be
+// `const __restrict__`, or its loads become invariant loads that the compiler may move above the dependency wait.
+static __global__ void __launch_bounds__(kPfNormThreads) prefill_norm_kernel(float* x, const int* tokens,
+                                                                            const __half* __restrict__ emb, int vocab,
+                                                                            const float* __restrict__ norm_w, __half* out,
+                                                                            int D, int n_tokens, const float* part,
+                                                                            int splits, StepState* st) {
+    __shared__ float red[kPfNormThreads / 32];
     pdl_launch_dependents();
     pdl_wait();
-    const int t = blockIdx.x;
-    float* xr = x + (size_t)t * D;
+    const int t = blockIdx.x, tid = threadIdx.x;
+    float4* xr = reinterpret_cast<float4*>(x + (size_t)t * D);
+    const int nv4 = D >> 2;  // D is a multiple of 8
+    constexpr int kMaxPer = 4;  // float4 per thread held in registers: rows up to 8192 wide in one sweep
+    float4 v[kMaxPer];
+    int tok = 0;
     if (emb) {
-        int tok = tokens[t];
+        tok = tokens[t];
         if (tok < 0 || tok >= vocab) {
-            if (threadIdx.x == 0) atomicOr(&st->status, kStatusBadToken);
+            if (tid == 0) atomicOr(&st->status, kStatusBadToken);
             tok = 0;
-        }
-        const __half* er = emb + (size_t)tok * D;
-        for (int i = threadIdx.x; i < D; i += 256) xr[i] = __half2float(er[i]);
-    } else if (splits > 1) {
-        // the preceding residual GEMM left its K-range partial sums: x += p_0 + p_1 + ... in range order
-        for (int i = threadIdx.x; i < D; i += 256) {
-            float v = xr[i];
-            for (int s = 0; s < splits; ++s) v += part[((size_t)s * kPrefillTokens + t) * D + i];
-            xr[i] = v;
         }
     }
     float ss = 0.f;
-    for (int i = threadIdx.x; i < D; i += 256) ss = fmaf(xr[i], xr[i], ss);  // every thread reads back what it wrote
+    for (int base = 0; base < nv4; base += kMaxPer * kPfNormThreads) {
+        // every load of the sweep is issued before the first is used: one memory round trip, not one per element
+#pragma unroll
+        for (int k = 0; k < kMaxPer; ++k) {
+            const int i = base + tid + k * kPfNormThreads;
+            if (i < nv4) {
+                if (emb) {
+                    const uint2 h = *reinterpret_cast<const uint2*>(emb + (size_t)tok * D + 4 * (size_t)i);
+                    const float2 lo = half2_bits_to_float2(h.x), hi = half2_bits_to_float2(h.y);
+                    v[k] = make_float4(lo.x, lo.y, hi.x, hi.y);
+                } else {
+                    v[k] = xr[i];
+                }
+            }
+        }
+        if (!emb && splits > 1) {
+            // the preceding residual GEMM left its K-range partial sums: x += p_0 + p_1 + ... in range order
+            for (int s0 = 0; s0 < splits; ++s0) {
+                float4 p[kMaxPer];
+#pragma unroll
+                for (int k = 0; k < kMaxPer; ++k) {
+                    const int i = base + tid + k * kPfNormThreads;
+                    if (i < nv4) p[k] = reinterpret_cast<const float4*>(part + ((size_t)s0 * kPrefillTokens + t) * D)[i];
+                }
+#pragma unroll
+                for (int k = 0; k < kMaxPer; ++k) {
+                    const int i = base + tid + k * kPfNormThreads;
+                    if (i < nv4) {
+                        v[k].x += p[k].x; v[k].y += p[k].y; v[k].z += p[k].z; v[k].w += p[k].w;
+                    }
+                }
+            }
+        }
+#pragma unroll
+        for (int k = 0; k < kMaxPer; ++k) {
+            const int i = base + tid + k * kPfNormThreads;
+            if (i < nv4) {
+                if (emb || splits > 1) xr[i] = v[k];  // the residual stream as the next residual GEMM reads it
+                ss = fmaf(v[k].x, v[k].x, fmaf(v[k].y, v[k].y, fmaf(v[k].z, v[k].z, fmaf(v[k].w, v[k].w, ss))));
+            }
+        }
+    }
     ss = warp_sum(ss);
-    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+    if ((tid & 31) == 0) red[tid >> 5] = ss;
     __syncthreads();
     float tot = 0.f;
-    for (int k = 0; k < 8; ++k) tot += red[k];
+#pragma unroll
+    for (int k = 0; k < kPfNormThreads / 32; ++k) tot += red[k];
     const float scale = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(tot, (float)D), 1e-5f)));
-    for (int i = threadIdx.x; i < D; i += 256) out[(size_t)t * D + i] = __float2half_rn(__fmul_rn(__fmul_rn(xr[i], scale), norm_w[i]));
+    const bool one_sweep = nv4 <= kMaxPer * kPfNormThreads;
+    for (int base = 0; base < nv4; base += kMaxPer * kPfNormThreads) {
+#pragma unroll
+        for (int k = 0; k < kMaxPer; ++k) {
+            const int i = base + tid + k * kPfNormThreads;
+            if (i < nv4) {
+                const float4 xv = one_sweep ? v[k] : xr[i];  // wider rows re-read what this thread wrote
+                const float4 w = __ldg(reinterpret_cast<const float4*>(norm_w) + i);
+                const __half2 lo = __floats2half2_rn(__fmul_rn(__fmul_rn(xv.x, scale), w.x), __fmul_rn(__fmul_rn(xv.y, scale), w.y));
+                const __half2 hi = __floats2half2_rn(__fmul_rn(__fmul_rn(xv.z, scale), w.z), __fmul_rn(__fmul_rn(xv.w, scale), w.w));
+                uint2 o;
+                o.x = *reinterpret_cast<const unsigned int*>(&lo);
+                o.y = *reinterpret_cast<const unsigned int*>(&hi);
+                *reinterpret_cast<uint2*>(out + (size_t)t * D + 4 * (size_t)i) = o;
+            }
+        }
+    }
 }
 
 // Causal attention of the prompt block: query token t (position start_pos + t) over cache rows 0..start_pos + t,
@@ -292,49 +350,251 @@ static __global__ void __launch_bounds__(256) prefill_attention_kernel(const flo
     const float scale = __fdiv_rn(1.0f, __fsqrt_rn((float)hs));
     const __half* kb = k_cache + (size_t)kvh * seq_len * hs;
     const __half* vb = v_cache + (size_t)kvh * seq_len * hs;
+    // one position's score: the K row in 16-byte pieces, all requested before the first is used
+    auto score = [&](int p) -> float {
+        const uint4* kr = reinterpret_cast<const uint4*>(kb + (size_t)p * hs);
+        float s = 0.f;
+        for (int d0 = 0; d0 < hs / 8; d0 += 8) {
+            uint4 u[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+                if (d0 + i < hs / 8) u[i] = __ldcg(kr + d0 + i);
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+                if (d0 + i < hs / 8) {
+                    const float* qq = qs + 8 * (d0 + i);
+                    float2 f;
+                    f = half2_bits_to_float2(u[i].x); s = fmaf(qq[0], f.x, s); s = fmaf(qq[1], f.y, s);
+                    f = half2_bits_to_float2(u[i].y); s = fmaf(qq[2], f.x, s); s = fmaf(qq[3], f.y, s);
+                    f = half2_bits_to_float2(u[i].z); s = fmaf(qq[4], f.x, s); s = fmaf(qq[5], f.y, s);
+                    f = half2_bits_to_float2(u[i].w); s = fmaf(qq[6], f.x, s); s = fmaf(qq[7], f.y, s);
+                }
+        }
+        return s * scale;
+    };
     // pass 1: scores of this lane's positions, maximum
     float m = -INFINITY;
-    for (int p = lane; p < T; p += 32) {
-        const __half2* kr = reinterpret_cast<const __half2*>(kb + (size_t)p * hs);
-        float s = 0.f;
-        for (int d = 0; d < hs / 2; ++d) {
-            const float2 kk = __half22float2(kr[d]);
-            s = fmaf(qs[2 * d], kk.x, s);
-            s = fmaf(qs[2 * d + 1], kk.y, s);
-        }
-        m = fmaxf(m, s * scale);
-    }
+    for (int p = lane; p < T; p += 32) m = fmaxf(m, score(p));
     m = warp_max(m);
-    // pass 2: every lane owns head dims lane, lane + 32, ...; positions in order
+    // pass 2: every lane owns head dims lane, lane + 32, ...; positions in order, eight V rows in flight
     float l = 0.f;
     float acc[4] = {0.f, 0.f, 0.f, 0.f};  // head_size <= 128
     for (int p0 = 0; p0 < T; p0 += 32) {
         const int p = p0 + lane;
-        float e = 0.f;
-        if (p < T) {
-            const __half2* kr = reinterpret_cast<const __half2*>(kb + (size_t)p * hs);
-            float s = 0.f;
-            for (int d = 0; d < hs / 2; ++d) {
-                const float2 kk = __half22float2(kr[d]);
-                s = fmaf(qs[2 * d], kk.x, s);
-                s = fmaf(qs[2 * d + 1], kk.y, s);
-            }
-            e = __expf(s * scale - m);
-        }
+        const float e = (p < T) ? __expf(score(p) - m) : 0.f;
         l += e;
         const int cnt = min(32, T - p0);
-        for (int i = 0; i < cnt; ++i) {
-            const float ei = __shfl_sync(0xffffffffu, e, i);
-            const __half* vr = vb + (size_t)(p0 + i) * hs;
+        for (int i0 = 0; i0 < cnt; i0 += 8) {
+            __half vv[8][4];
 #pragma unroll
-            for (int c = 0; c < 4; ++c)
-                if (lane + 32 * c < hs) acc[c] = fmaf(ei, __half2float(vr[lane + 32 * c]), acc[c]);
+            for (int i = 0; i < 8; ++i)
+#pragma unroll
+                for (int c = 0; c < 4; ++c)
+                    if (i0 + i < cnt && lane + 32 * c < hs) vv[i][c] = vb[(size_t)(p0 + i0 + i) * hs + lane + 32 * c];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const float ei = __shfl_sync(0xffffffffu, e, (i0 + i) & 31);
+#pragma unroll
+                for (int c = 0; c < 4; ++c)
+                    if (i0 + i < cnt && lane + 32 * c < hs) acc[c] = fmaf(ei, __half2float(vv[i][c]), acc[c]);
+            }
         }
     }
     l = warp_sum(l);
 #pragma unroll
     for (int c = 0; c < 4; ++c)
         if (lane + 32 * c < hs) out[(size_t)t * q_rows + (size_t)h * hs + lane + 32 * c] = __float2half_rn(__fdiv_rn(acc[c], l));
+}
+
+// Causal attention of the prompt block on the tensor cores: CTA (query tile of 16 tokens, KV head), one warp per
+// query head of the group.  K and V rows stream through shared memory 64 positions at a time (16-byte asynchronous
+// copies, double buffered, rows padded by 16 bytes so that the 8-row matrix loads do not collide on banks); every
+// warp keeps its 16 x head_size query tile as A fragments, forms the 16 x 64 scores with mma.sync m16n8k16, masks
+// them causally, runs the online softmax in FP32 on the accumulator layout, and feeds the probabilities back as A
+// fragments of the P x V product (V read through transposing matrix loads).  Same mathematics as
+// prefill_attention_kernel (src/model.cpp:178-199), FP16 operands with FP32 accumulation.
+constexpr int kPfAttnTile = 64;   // positions per shared-memory tile
+constexpr int kPfAttnRows = 16;   // query tokens per CTA
+template <int HS>
+constexpr int pf_attn_smem() {
+    return 2 /*buffers*/ * 2 /*K, V*/ * kPfAttnTile * (HS * 2 + 16);
+}
+
+__device__ __forceinline__ void cp_async_16(void* dst_smem, const void* src, bool valid) {
+    const uint32_t d = smem_u32(dst_smem);
+    const int n = valid ? 16 : 0;  // 0 source bytes: the 16 destination bytes are filled with zeros
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(src), "r"(n) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(addr));
+}
+template <int HS>
+static __global__ void __launch_bounds__(256) prefill_attention_mma_kernel(const float* q, const __half* k_cache,
+                                                                           const __half* v_cache, __half* out, int n_tokens,
+                                                                           int start_pos, int seq_len, int gqa, int q_rows) {
+    constexpr int kStride = HS * 2 + 16;              // bytes per padded row
+    constexpr int kMat = kPfAttnTile * kStride;       // bytes of one K or V tile
+    constexpr int kChunks = kPfAttnTile * (HS / 8);   // 16-byte pieces of one tile
+    extern __shared__ __align__(128) unsigned char at_smem[];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int t0 = blockIdx.x * kPfAttnRows, kvh = blockIdx.y;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = lane >> 2, tq = lane & 3;
+    const int h = kvh * gqa + warp;
+    const int rows_here = min(kPfAttnRows, n_tokens - t0);
+    const int t_max = start_pos + t0 + rows_here;  // positions 0 .. t_max - 1 are visible to the last token of the tile
+    const int n_tiles = (t_max + kPfAttnTile - 1) / kPfAttnTile;
+    const unsigned char* kb = reinterpret_cast<const unsigned char*>(k_cache + (size_t)kvh * seq_len * HS);
+    const unsigned char* vb = reinterpret_cast<const unsigned char*>(v_cache + (size_t)kvh * seq_len * HS);
+
+    auto load_tile = [&](int tile, int buf) {
+        unsigned char* ks = at_smem + (size_t)buf * 2 * kMat;
+        unsigned char* vs = ks + kMat;
+        const int p0 = tile * kPfAttnTile;
+        for (int c = threadIdx.x; c < kChunks; c += blockDim.x) {
+            const int row = c / (HS / 8), col = c % (HS / 8);
+            const bool ok = p0 + row < t_max;
+            const size_t src = ok ? ((size_t)(p0 + row) * HS * 2 + (size_t)col * 16) : 0;
+            cp_async_16(ks + row * kStride + col * 16, kb + src, ok);
+            cp_async_16(vs + row * kStride + col * 16, vb + src, ok);
+        }
+    };
+
+    // the query tile of this warp's head as A fragments
+    uint32_t qa[HS / 16][4];
+    {
+        const int r0 = t0 + g, r1 = t0 + g + 8;
+        const float* q0 = q + (size_t)r0 * q_rows + (size_t)h * HS;
+        const float* q1 = q + (size_t)r1 * q_rows + (size_t)h * HS;
+#pragma unroll
+        for (int kk = 0; kk < HS / 16; ++kk) {
+            const int c0 = kk * 16 + 2 * tq;
+            const float2 z = make_float2(0.f, 0.f);
+            const float2 a0 = (r0 < n_tokens) ? *reinterpret_cast<const float2*>(q0 + c0) : z;
+            const float2 a1 = (r1 < n_tokens) ? *reinterpret_cast<const float2*>(q1 + c0) : z;
+            const float2 a2 = (r0 < n_tokens) ? *reinterpret_cast<const float2*>(q0 + c0 + 8) : z;
+            const float2 a3 = (r1 < n_tokens) ? *reinterpret_cast<const float2*>(q1 + c0 + 8) : z;
+            qa[kk][0] = pack_half2(a0.x, a0.y);
+            qa[kk][1] = pack_half2(a1.x, a1.y);
+            qa[kk][2] = pack_half2(a2.x, a2.y);
+            qa[kk][3] = pack_half2(a3.x, a3.y);
+        }
+    }
+    const float scale = __fdiv_rn(1.0f, __fsqrt_rn((float)HS));
+    const int lim0 = (t0 + g < n_tokens) ? start_pos + t0 + g : -1;          // last visible position of row g
+    const int lim1 = (t0 + g + 8 < n_tokens) ? start_pos + t0 + g + 8 : -1;  // ... of row g + 8
+    float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+    float o[HS / 8][4];
+#pragma unroll
+    for (int i = 0; i < HS / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+
+    load_tile(0, 0);
+    cp_async_commit();
+    for (int tile = 0; tile < n_tiles; ++tile) {
+        const int buf = tile & 1;
+        if (tile + 1 < n_tiles) {
+            load_tile(tile + 1, buf ^ 1);
+            cp_async_commit();
+            cp_async_wait<1>();
+        } else {
+            cp_async_wait<0>();
+        }
+        __syncthreads();
+        const uint32_t ks = smem_u32(at_smem + (size_t)buf * 2 * kMat);
+        const uint32_t vs = ks + kMat;
+        const int p0 = tile * kPfAttnTile;
+        // scores of 16 rows x 64 positions
+        float c[kPfAttnTile / 8][4];
+#pragma unroll
+        for (int j = 0; j < kPfAttnTile / 8; ++j) c[j][0] = c[j][1] = c[j][2] = c[j][3] = 0.f;
+        const int mi = lane >> 3, mr = lane & 7;
+#pragma unroll
+        for (int jp = 0; jp < kPfAttnTile / 16; ++jp) {
+#pragma unroll
+            for (int kk = 0; kk < HS / 16; ++kk) {
+                uint32_t b[4];
+                ldmatrix_x4(ks + (uint32_t)((jp * 16 + (mi >> 1) * 8 + mr) * kStride + (kk * 16 + (mi & 1) * 8) * 2), b[0], b[1],
+                            b[2], b[3]);
+                mma_f16_16816(c[2 * jp], qa[kk][0], qa[kk][1], qa[kk][2], qa[kk][3], b[0], b[1]);
+                mma_f16_16816(c[2 * jp + 1], qa[kk][0], qa[kk][1], qa[kk][2], qa[kk][3], b[2], b[3]);
+            }
+        }
+        // scale, causal mask, online softmax (rows g and g + 8; a row's 64 scores lie on the four lanes of a quad)
+        float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+        for (int j = 0; j < kPfAttnTile / 8; ++j) {
+            const int p = p0 + 8 * j + 2 * tq;
+            c[j][0] = (p <= lim0) ? c[j][0] * scale : -INFINITY;
+            c[j][1] = (p + 1 <= lim0) ? c[j][1] * scale : -INFINITY;
+            c[j][2] = (p <= lim1) ? c[j][2] * scale : -INFINITY;
+            c[j][3] = (p + 1 <= lim1) ? c[j][3] * scale : -INFINITY;
+            mx0 = fmaxf(mx0, fmaxf(c[j][0], c[j][1]));
+            mx1 = fmaxf(mx1, fmaxf(c[j][2], c[j][3]));
+        }
+        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+        const float n0 = fmaxf(m0, mx0), n1 = fmaxf(m1, mx1);
+        const float u0 = (n0 == -INFINITY) ? 0.f : n0, u1 = (n1 == -INFINITY) ? 0.f : n1;  // nothing visible yet
+        const float f0 = __expf(m0 - u0), f1 = __expf(m1 - u1);  // exp(-inf) = 0 on the first visible tile
+        m0 = n0;
+        m1 = n1;
+        l0 *= f0;
+        l1 *= f1;
+#pragma unroll
+        for (int i = 0; i < HS / 8; ++i) {
+            o[i][0] *= f0;
+            o[i][1] *= f0;
+            o[i][2] *= f1;
+            o[i][3] *= f1;
+        }
+        uint32_t pa[kPfAttnTile / 16][4];
+#pragma unroll
+        for (int j = 0; j < kPfAttnTile / 8; ++j) {
+            const float e0 = __expf(c[j][0] - u0), e1 = __expf(c[j][1] - u0);
+            const float e2 = __expf(c[j][2] - u1), e3 = __expf(c[j][3] - u1);
+            l0 += e0 + e1;
+            l1 += e2 + e3;
+            pa[j >> 1][(j & 1) * 2 + 0] = pack_half2(e0, e1);
+            pa[j >> 1][(j & 1) * 2 + 1] = pack_half2(e2, e3);
+        }
+        // o += P x V
+#pragma unroll
+        for (int kk = 0; kk < kPfAttnTile / 16; ++kk) {
+#pragma unroll
+            for (int dp = 0; dp < HS / 16; ++dp) {
+                uint32_t b[4];
+                ldmatrix_x4_trans(b, vs + (uint32_t)((kk * 16 + (mi & 1) * 8 + mr) * kStride + (dp * 16 + (mi >> 1) * 8) * 2));
+                mma_f16_16816(o[2 * dp], pa[kk][0], pa[kk][1], pa[kk][2], pa[kk][3], b[0], b[1]);
+                mma_f16_16816(o[2 * dp + 1], pa[kk][0], pa[kk][1], pa[kk][2], pa[kk][3], b[2], b[3]);
+            }
+        }
+        __syncthreads();  // the buffer is refilled two iterations from now, by the copy issued in the next one
+    }
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+    const int r0 = t0 + g, r1 = t0 + g + 8;
+#pragma unroll
+    for (int i = 0; i < HS / 8; ++i) {
+        const int d = 8 * i + 2 * tq;
+        if (r0 < n_tokens)
+            *reinterpret_cast<uint32_t*>(out + (size_t)r0 * q_rows + (size_t)h * HS + d) =
+                pack_half2(__fdiv_rn(o[i][0], l0), __fdiv_rn(o[i][1], l0));
+        if (r1 < n_tokens)
+            *reinterpret_cast<uint32_t*>(out + (size_t)r1 * q_rows + (size_t)h * HS + d) =
+                pack_half2(__fdiv_rn(o[i][2], l1), __fdiv_rn(o[i][3], l1));
+    }
 }
 
 }  // namespace lpp

@@ -32,6 +32,8 @@ SHAPES: Dict[str, Tuple[ModelConfig, str, bool, int]] = {
     # full-size vocabularies on a toy body: sampler tests
     "vocab32k-f16": (ModelConfig(64, 128, 1, 2, 2, 32000, 16, 10000.0), "f16", True, 16),
     "vocab128k-f16": (ModelConfig(64, 128, 1, 2, 2, 128256, 16, 500000.0), "f16", True, 17),
+    "vocab256k-f16": (ModelConfig(64, 128, 1, 2, 2, 256008, 16, 10000.0), "f16", True, 18),
+    "vocab50k-f16": (ModelConfig(64, 128, 1, 2, 2, 50264, 16, 10000.0), "f16", True, 19),
     "mini-long-f16": (ModelConfig(512, 1024, 2, 8, 2, 512, 4608, 500000.0), "f16", True, 15),
 }
 

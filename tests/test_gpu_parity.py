@@ -237,6 +237,29 @@ def test_exact_sampler_draws_large_vocab(E, oracle, name):
     eng.close()
 
 
+@pytest.mark.parametrize("name", ["vocab50k-f16", "vocab256k-f16"])
+def test_exact_sampler_ragged_and_widest_vocab(E, oracle, name):
+    """The exact-order sampler where the last block is ragged (50264 logits) and where nearly every SM holds a block
+    (256008 logits: 126 co-resident blocks), with histories from empty to the device capacity: ids equal those of the
+    CPU twin on every draw."""
+    c, dt, T, eng = make(E, name)
+    V = c.vocab_size
+    rng = np.random.default_rng(V + 11)
+    for s in range(6):
+        std = (0.2, 1.0, 4.0)[s % 3]
+        lg = (rng.standard_normal(V) * std).astype(np.float32)
+        hist = rng.integers(0, V, size=(0, 5, 64, 300, 1000, 4096)[s]).astype(np.int32)
+        if hist.size >= 16:
+            hist[:8] = hist[8:16]
+        temp, pen = ((0.8, 1.1), (1.0, 1.0), (0.3, 1.5))[s % 3]
+        assert eng.sample(lg, 0.0, pen, hist, 0.0) == oracle.sample(lg, 0.0, pen, hist, 0.0)
+        rs = rng.random(12).astype(np.float32)
+        rs[:3] = (0.0, 1.0, np.float32(1.0) - np.float32(2 ** -24))
+        for r in rs:
+            assert eng.sample(lg, temp, pen, hist, float(r)) == oracle.sample_twin(lg, temp, pen, hist, float(r)), (s, float(r))
+    eng.close()
+
+
 @pytest.mark.parametrize("V", [32000, 128256])
 def test_tree_sampler_wrapper_large_vocab(E, oracle, V):
     """The stand-alone cuda_sample wrapper (tree-sum sampler): argmax ids are bit-exact; categorical ids are compared

@@ -39,13 +39,15 @@ def _call(torch, fn, logits, temperature, penalty, hist, r):
     return st, int(out.item()), d_logits.cpu().numpy()
 
 
-@pytest.mark.parametrize("V", [1000, 32000, 128256])
+@pytest.mark.parametrize("V", [1000, 32000, 128256, 262144])
 def test_static_scratch_sampler_matches_allocating_one(env, V):
     torch, lib = env
     rng = np.random.default_rng(V + 1)
-    # two calls in a row with different inputs: long history then short, categorical then argmax
+    # two calls in a row with different inputs: long history then short, categorical then argmax; the largest
+    # vocabulary runs at the entry point's built-in capacity (262144 logits, 4096 history entries)
     cases = [
-        (rng.standard_normal(V).astype(np.float32), 0.8, 1.1, rng.integers(0, V, 64).astype(np.int32), 0.37),
+        (rng.standard_normal(V).astype(np.float32), 0.8, 1.1,
+         rng.integers(0, V, 4096 if V == 262144 else 64).astype(np.int32), 0.37),
         (rng.standard_normal(V).astype(np.float32) * 2, 0.0, 1.3, rng.integers(0, V, 5).astype(np.int32), 0.0),
         (rng.standard_normal(V).astype(np.float32), 1.0, 1.0, rng.integers(0, V, 1).astype(np.int32), 0.93),
     ]
