@@ -180,6 +180,7 @@ struct lpp_engine {
     __half *pf_xn = nullptr, *pf_att = nullptr, *pf_hb = nullptr;
     int* pf_tokens = nullptr;
     CUtensorMap pf_map_wqkv, pf_map_wo, pf_map_w13, pf_map_w2, pf_map_xn, pf_map_att, pf_map_hb;
+    int pf_rows_qkv = kUmmaM, pf_rows = kUmmaM;  // weight rows per tile (= box rows of the weight maps)
     bool pf_ready = false;
 
     bool finalized = false;
@@ -1290,44 +1291,71 @@ static lpp_status prefill_setup(lpp_engine* e) {
     CU(cudaMalloc(&e->pf_xn, T * D * 2));
     CU(cudaMalloc(&e->pf_att, T * e->Dq * 2));
     CU(cudaMalloc(&e->pf_hb, T * e->Fl * 2));
-    CU(cudaMalloc(&e->pf_part, (size_t)kPfMaxSplits * T * D * 4));
+    CU(cudaMalloc(&e->pf_part, (size_t)kPfMaxSplits * T * std::max<size_t>(D, qkv_rows) * 4));
     CU(cudaMalloc(&e->pf_tokens, T * sizeof(int)));
     CU(cudaMemsetAsync(e->pf_x, 0, T * D * 4, e->stream));
     CU(cudaMemsetAsync(e->pf_xn, 0, T * D * 2, e->stream));
     CU(cudaMemsetAsync(e->pf_att, 0, T * e->Dq * 2, e->stream));
     CU(cudaMemsetAsync(e->pf_hb, 0, T * e->Fl * 2, e->stream));
     CU(cudaMemsetAsync(e->pf_tokens, 0, T * sizeof(int), e->stream));
-    TRY(make_map(&e->pf_map_wqkv, e->wqkv, L * qkv_rows, D, 32));
-    TRY(make_map(&e->pf_map_wo, e->wo, L * D, e->Dq, 64));
-    TRY(make_map(&e->pf_map_w13, e->w13, L * 2 * e->Fl, D, 64));
-    TRY(make_map(&e->pf_map_w2, e->w2, L * D, e->Fl, 64));
+#ifdef LPP_TIMING_AIDS
+    if (const char* v = aid_env("LPP_PF_UMMA")) {  // comparison kernel (warp-level MMA): bit 0 clear for the residual/SwiGLU GEMMs, bit 1 for QKV
+        const int m = atoi(v);
+        e->pf_rows = (m & 1) ? kUmmaM : 64;
+        e->pf_rows_qkv = (m & 2) ? kUmmaM : 32;
+    }
+#endif
+    TRY(make_map(&e->pf_map_wqkv, e->wqkv, L * qkv_rows, D, e->pf_rows_qkv));
+    TRY(make_map(&e->pf_map_wo, e->wo, L * D, e->Dq, e->pf_rows));
+    TRY(make_map(&e->pf_map_w13, e->w13, L * 2 * e->Fl, D, e->pf_rows));
+    TRY(make_map(&e->pf_map_w2, e->w2, L * D, e->Fl, e->pf_rows));
     TRY(make_map(&e->pf_map_xn, e->pf_xn, T, D, kPrefillTokens));
     TRY(make_map(&e->pf_map_att, e->pf_att, T, e->Dq, kPrefillTokens));
     TRY(make_map(&e->pf_map_hb, e->pf_hb, T, e->Fl, kPrefillTokens));
+#ifdef LPP_TIMING_AIDS
     CU(cudaFuncSetAttribute(prefill_gemm_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, kPfSmemBytes));
     CU(cudaFuncSetAttribute(prefill_gemm_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, kPfSmemBytes));
+#endif
+    CU(cudaFuncSetAttribute(prefill_gemm_umma_kernel<kPfQkv>, cudaFuncAttributeMaxDynamicSharedMemorySize, kPfSmemBytes));
+    CU(cudaFuncSetAttribute(prefill_gemm_umma_kernel<kPfResid>, cudaFuncAttributeMaxDynamicSharedMemorySize, kPfSmemBytes));
+    CU(cudaFuncSetAttribute(prefill_gemm_umma_kernel<kPfSwiglu>, cudaFuncAttributeMaxDynamicSharedMemorySize, kPfSmemBytes));
     CU(cudaFuncSetAttribute(prefill_attention_mma_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, pf_attn_smem<64>()));
     CU(cudaFuncSetAttribute(prefill_attention_mma_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, pf_attn_smem<128>()));
     e->pf_ready = true;
     return LPP_OK;
 }
 
-// tile_rows: 32 or 64 (must match the weight map's box).  A residual GEMM whose row tiles do not fill the GPU is
-// also cut along K; its partial sums go to pf_part and the next prefill_norm_kernel adds them up.
+// tile_rows must match the weight map's box: 128 for the tcgen05 kernel (32 or 64: the comparison kernel of the
+// timing-aids build).  A GEMM whose row tiles do not fill the GPU is also cut along K; its partial sums go to pf_part
+// and are added up by the next prefill_norm_kernel (residual projections) or by prefill_qkv_finish_kernel (QKV).
 static cudaError_t launch_prefill_gemm(lpp_engine* e, const CUtensorMap& wm, const CUtensorMap& xm, PrefillGemmArgs a, int tile_rows) {
     const int tiles = (a.n_rows + tile_rows - 1) / tile_rows;
     const int n_kc = (a.K + kPfKc - 1) / kPfKc;
     a.st = e->st;
     a.splits = 1;
-    if (a.epi == kPfResid && tiles < e->num_sms) a.splits = std::max(1, std::min({kPfMaxSplits, n_kc, (e->num_sms + tiles - 1) / tiles}));
+    // the tcgen05 QKV GEMM is cut too: its partial sums are finished by prefill_qkv_finish_kernel
+    if ((a.epi == kPfResid || (a.epi == kPfQkv && tile_rows == kUmmaM)) && tiles < e->num_sms)
+        a.splits = std::max(1, std::min({kPfMaxSplits, n_kc, (e->num_sms + tiles - 1) / tiles}));
     a.part = e->pf_part;
     const int grid = std::min(tiles * a.splits, e->num_sms);
+    if (tile_rows == kUmmaM) {
+        const dim3 g(grid), b(kUmmaThreads);
+        if (a.epi == kPfResid) return launch_kernel(prefill_gemm_umma_kernel<kPfResid>, g, b, (size_t)kPfSmemBytes, e->stream, true, wm, xm, a);
+        if (a.epi == kPfSwiglu) return launch_kernel(prefill_gemm_umma_kernel<kPfSwiglu>, g, b, (size_t)kPfSmemBytes, e->stream, true, wm, xm, a);
+        const cudaError_t err = launch_kernel(prefill_gemm_umma_kernel<kPfQkv>, g, b, (size_t)kPfSmemBytes, e->stream, true, wm, xm, a);
+        if (err != cudaSuccess || a.splits == 1) return err;
+        return launch_kernel(prefill_qkv_finish_kernel, dim3(a.n_tokens, (a.n_rows / 2 + 255) / 256), dim3(256), 0, e->stream, true, a);
+    }
+#ifdef LPP_TIMING_AIDS
     if (tile_rows == 32)
         return launch_kernel(prefill_gemm_kernel<32>, dim3(grid), dim3(kPfThreads), (size_t)kPfSmemBytes, e->stream, true, wm, xm, a);
     return launch_kernel(prefill_gemm_kernel<64>, dim3(grid), dim3(kPfThreads), (size_t)kPfSmemBytes, e->stream, true, wm, xm, a);
+#else
+    return cudaErrorInvalidValue;
+#endif
 }
 static int prefill_splits(const lpp_engine* e, int n_rows, int K) {  // what launch_prefill_gemm chooses for a residual GEMM
-    const int tiles = (n_rows + 63) / 64, n_kc = (K + kPfKc - 1) / kPfKc;
+    const int tiles = (n_rows + e->pf_rows - 1) / e->pf_rows, n_kc = (K + kPfKc - 1) / kPfKc;
     return tiles < e->num_sms ? std::max(1, std::min({kPfMaxSplits, n_kc, (e->num_sms + tiles - 1) / tiles})) : 1;
 }
 
@@ -1360,7 +1388,7 @@ static lpp_status prefill_block(lpp_engine* e, const int* h_tokens, int n, int s
         g.rope = e->rope;
         g.k_cache = (__half*)e->kcache + lofs;
         g.v_cache = (__half*)e->vcache + lofs;
-        CU(launch_prefill_gemm(e, e->pf_map_wqkv, e->pf_map_xn, g, 32));
+        CU(launch_prefill_gemm(e, e->pf_map_wqkv, e->pf_map_xn, g, e->pf_rows_qkv));
         if (l == L - 1) break;
         const dim3 agrid((n + kPfAttnRows - 1) / kPfAttnRows, e->KVHl);
         const bool pf_mma = !aid_env("LPP_ATTN_CUDA_CORES");
@@ -1385,7 +1413,7 @@ static lpp_status prefill_block(lpp_engine* e, const int* h_tokens, int n, int s
         o.row0 = l * D;
         o.epi = kPfResid;
         o.x = e->pf_x;
-        CU(launch_prefill_gemm(e, e->pf_map_wo, e->pf_map_att, o, 64));
+        CU(launch_prefill_gemm(e, e->pf_map_wo, e->pf_map_att, o, e->pf_rows));
         CU(launch_kernel(prefill_norm_kernel, dim3(n), dim3(kPfNormThreads), 0, e->stream, true, e->pf_x, (const int*)e->pf_tokens,
                          (const __half*)nullptr, c.vocab_size, (const float*)(e->rms_ffn + (size_t)l * D), e->pf_xn, D, n,
                          (const float*)e->pf_part, s_o, e->st));
@@ -1397,7 +1425,7 @@ static lpp_status prefill_block(lpp_engine* e, const int* h_tokens, int n, int s
         u.row0 = l * 2 * e->Fl;
         u.epi = kPfSwiglu;
         u.hb = e->pf_hb;
-        CU(launch_prefill_gemm(e, e->pf_map_w13, e->pf_map_xn, u, 64));
+        CU(launch_prefill_gemm(e, e->pf_map_w13, e->pf_map_xn, u, e->pf_rows));
         PrefillGemmArgs d = {};
         d.n_tokens = n;
         d.start_pos = start_pos;
@@ -1406,7 +1434,7 @@ static lpp_status prefill_block(lpp_engine* e, const int* h_tokens, int n, int s
         d.row0 = l * D;
         d.epi = kPfResid;
         d.x = e->pf_x;
-        CU(launch_prefill_gemm(e, e->pf_map_w2, e->pf_map_hb, d, 64));
+        CU(launch_prefill_gemm(e, e->pf_map_w2, e->pf_map_hb, d, e->pf_rows));
     }
     return LPP_OK;
 }
@@ -1592,6 +1620,14 @@ extern "C" int lpp_debug_sampler_entries(lpp_engine* e, int* counts, void* entri
     cudaMemcpy(scalars, e->ex_scalars, 64 * sizeof(float), cudaMemcpyDeviceToHost);
     return e->sample_blocks;
 }
+
+#ifdef LPP_TIMING_AIDS
+extern "C" int lpp_debug_pf_trace(lpp_engine* e, unsigned long long* out) {
+    if (!e) return -1;
+    cudaStreamSynchronize(e->stream);
+    return (int)cudaMemcpyFromSymbol(out, g_pf_trace, sizeof(unsigned long long) * 160 * 48);
+}
+#endif
 
 extern "C" const char* lpp_strerror(int s) {
     switch (s) {

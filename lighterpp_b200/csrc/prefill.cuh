@@ -4,15 +4,21 @@
 // The reference feeds a prompt through forward() token by token (src/main.cpp:163-179): every prompt token
 // streams all weights once.  Here the layer's matrices are streamed ONCE for the whole block of tokens: the
 // four projections become small GEMMs  C[tokens][rows] = X[tokens][K] . W[rows][K]^T  that are still bound by
-// the weight stream (2 FLOP per weight byte and token: far below the tensor cores' ridge for a few dozen
-// tokens), so the kernel is organised around that stream exactly like the decode GEMV -- a producer warp,
-// a ring of shared-memory stages, mbarrier hand-over -- only that a stage is a set of 2-D tiles fetched by the
-// tensor memory accelerator (cp.async.bulk.tensor.2d with the 128-byte swizzle: 32 or 64 weight rows x 128 inputs
-// and the matching 64 tokens x 128 inputs of the activations) and the arithmetic is warp-level tensor-core MMA
-// (ldmatrix + m16n8k16, FP16 operands, FP32 accumulation).  The two matrices with few rows and a plain residual
-// epilogue (o_proj, down) are also cut along K so that every SM streams a share; their partial sums are added to
-// the residual stream in a fixed order by the next kernel.  Activations are rounded to FP16 as MMA operands; everything between the GEMMs (residual
-// stream, RMSNorm, RoPE, softmax) stays FP32, following src/ops.cpp like the decode path.
+// the weight stream (2 FLOP per weight byte and token: far below the tensor cores' ridge for 64 tokens), so the
+// kernels are organised around that stream like the decode GEMV -- a producer thread, a ring of shared-memory
+// stages, mbarrier hand-over -- only that a stage is a set of 2-D tiles fetched by the tensor memory accelerator
+// (cp.async.bulk.tensor.2d with the 128-byte swizzle: 128 weight rows x 128 inputs and the matching 64 tokens x
+// 128 inputs of the activations, the weight tiles of the first ring pass requested before the dependency wait)
+// and the arithmetic runs on the tensor cores:
+//   * prefill_gemm_umma_kernel: tcgen05.mma reading both operands from shared memory through matrix descriptors,
+//     FP32 accumulators in tensor memory, epilogue warps that read them back with tcgen05.ld (the product path);
+//   * prefill_gemm_kernel: the same ring consumed by eight warps with ldmatrix + mma.sync.m16n8k16 (kept as the
+//     comparison kernel of the timing-aids build).
+// Matrices whose row tiles do not fill the GPU (QKV, o_proj, down) are also cut along K so that every SM streams
+// a share; partial sums are added in a fixed order by the next kernel (the norm kernel for the residual
+// projections, prefill_qkv_finish_kernel for QKV).  Activations are rounded to FP16 as MMA operands; everything
+// between the GEMMs (residual stream, RMSNorm, RoPE, softmax) stays FP32, following src/ops.cpp like the decode path.
+// The causal attention of the block (prefill_attention_mma_kernel) is a tensor-core flash attention over the cache.
 //
 // Tensor maps cover this GPU's own memory only; no cluster multicast is used anywhere.
 #pragma once
@@ -129,6 +135,8 @@ __device__ __forceinline__ void pf_epilogue(const PrefillGemmArgs& a, int split,
     }
 }
 
+#ifdef LPP_TIMING_AIDS
+// Comparison kernel of the timing-aids build (warp-level MMA); the product runs prefill_gemm_umma_kernel below.
 // C[t][row] = sum_k X[t][k] * W[row][k] for t < 64, fused with the epilogue.  A work item is (tile of M rows, K
 // range); CTA b takes items b, b + grid, ...; the ring runs across item boundaries.  M = 32 for the matrices with
 // few rows per SM and an epilogue that needs the whole sum (QKV), 64 otherwise.
@@ -157,17 +165,34 @@ static __global__ void __launch_bounds__(kPfThreads) prefill_gemm_kernel(const _
     if (warp == kPfConsumerWarps) {
         // ---------------- producer: one lane issues the four sub-tile copies of every stage
         if (lane == 0) {
-            pdl_wait();  // the activation tile comes from the previous kernel (the weights do not, but share the stage)
-            int slot = 0, pass = 0;
+            // the weight sub-tiles of the first ring pass are requested before the dependency wait (they do not depend
+            // on the previous kernel), the activation sub-tiles of the same stages right after it
+            int slot = 0, pass = 0, early = 0;
+            bool waited = false;
             for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
                 const int tile = item / S, split = item - tile * S;
                 const int kc0 = (split * n_kc) / S, kc1 = ((split + 1) * n_kc) / S;
+                if (!waited) {
+                    early = min(kc1 - kc0, G::kStages);
+                    for (int i = 0; i < early; ++i) {
+                        const uint32_t dst = ring + (uint32_t)i * G::kStage;
+                        mbar_arrive_expect_tx(&full[i], G::kStage);
+                        tma_load_2d(dst, &w_map, (kc0 + i) * kPfKc, a.row0 + tile * M, &full[i]);
+                        tma_load_2d(dst + G::kSubW, &w_map, (kc0 + i) * kPfKc + 64, a.row0 + tile * M, &full[i]);
+                    }
+                    pdl_wait();
+                    waited = true;
+                }
                 for (int kc = kc0; kc < kc1; ++kc) {
-                    if (pass > 0 && !mbar_wait_bounded(&empty[slot], (uint32_t)(pass - 1) & 1u, a.st)) return;
                     const uint32_t dst = ring + (uint32_t)slot * G::kStage;
-                    mbar_arrive_expect_tx(&full[slot], G::kStage);
-                    tma_load_2d(dst, &w_map, kc * kPfKc, a.row0 + tile * M, &full[slot]);
-                    tma_load_2d(dst + G::kSubW, &w_map, kc * kPfKc + 64, a.row0 + tile * M, &full[slot]);
+                    if (early > 0) {
+                        --early;
+                    } else {
+                        if (pass > 0 && !mbar_wait_bounded(&empty[slot], (uint32_t)(pass - 1) & 1u, a.st)) return;
+                        mbar_arrive_expect_tx(&full[slot], G::kStage);
+                        tma_load_2d(dst, &w_map, kc * kPfKc, a.row0 + tile * M, &full[slot]);
+                        tma_load_2d(dst + G::kSubW, &w_map, kc * kPfKc + 64, a.row0 + tile * M, &full[slot]);
+                    }
                     tma_load_2d(dst + 2 * G::kSubW, &x_map, kc * kPfKc, 0, &full[slot]);
                     tma_load_2d(dst + 2 * G::kSubW + kPfSubBytesX, &x_map, kc * kPfKc + 64, 0, &full[slot]);
                     if (++slot == G::kStages) {
@@ -234,6 +259,348 @@ static __global__ void __launch_bounds__(kPfThreads) prefill_gemm_kernel(const _
             }
     }
 }
+#endif  // LPP_TIMING_AIDS
+
+// ---- the GEMM on the fifth-generation tensor cores (tcgen05), accumulators in tensor memory
+//
+// A work item is (tile of 128 weight rows, K range).  Per stage the tensor memory accelerator delivers two
+// 128-row x 64-input weight sub-tiles and the two matching 64-token activation sub-tiles, all in the 128-byte
+// swizzled K-major layout that the MMA reads straight from shared memory through matrix descriptors: one elected
+// thread issues eight 128 x 64 x 16 MMAs per stage (D[128 rows][64 tokens] += W . X^T) into one of two 64-column
+// accumulators in tensor memory, commits the stage back to the producer, and after the last stage of the item
+// commits the accumulator to the four epilogue warps; these read their 32 lanes (rows) x 64 columns (tokens) with
+// tcgen05.ld, release the accumulator and run the same epilogues as above from registers while the next item's
+// MMAs already fill the other accumulator.  Warp roles: 0 producer, 1 MMA issue and tensor-memory allocation,
+// 2..9 epilogue (a warp may only read the tensor-memory lanes of its quarter, warp index modulo 4; two warps
+// share a quarter and take 32 tokens each).  An epilogue thread owns one weight row and walks its tokens, so
+// everything that depends on the row alone (which of q/k/v, head, rotation-table column) is computed once.
+// Every wait is bounded; every path, also a failed one, reaches the common exit that frees the tensor memory.
+constexpr int kUmmaM = 128;
+constexpr int kUmmaSubW = kUmmaM * 128;                            // 16 KiB
+constexpr int kUmmaStage = 2 * kUmmaSubW + 2 * kPfSubBytesX;       // 48 KiB
+constexpr int kUmmaStages = kPfRingBytes / kUmmaStage;             // 4
+constexpr int kUmmaEpiWarps = 8;                                   // two per tensor-memory lane quarter: 32 tokens each
+constexpr int kUmmaThreads = (2 + kUmmaEpiWarps) * 32;
+constexpr int kUmmaAccCols = kPrefillTokens;                       // FP32 columns of one accumulator
+constexpr int kUmmaTmemCols = 2 * kUmmaAccCols;                    // power of two >= 32
+// Instruction descriptor: D = F32 (bits 4-5 = 1), A = B = F16 (0), both K-major (bits 15, 16 = 0),
+// N / 8 in bits 17-22, M / 16 in bits 24-28.
+constexpr uint32_t kUmmaIdesc = (1u << 4) | ((uint32_t)(kPrefillTokens >> 3) << 17) | ((uint32_t)(kUmmaM >> 4) << 24);
+
+// Shared-memory matrix descriptor of a K-major operand tile with the 128-byte swizzle: start address / 16 in bits
+// 0-13, leading byte offset (unused for swizzled K-major, set to 1) in bits 16-29, stride between 8-row groups
+// (1024 bytes) / 16 in bits 32-45, descriptor version 1 in bits 46-47, layout type 2 (128-byte swizzle) in bits 61-63.
+__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
+    return (uint64_t)((smem_addr & 0x3ffffu) >> 4) | (1ull << 16) | ((uint64_t)(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
+}
+__device__ __forceinline__ void tc_alloc(uint32_t* smem_dst, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_dst)), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc_relinquish() {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tc_dealloc(uint32_t taddr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tc_mma_f16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// 32 lanes x 32 consecutive 32-bit columns: thread i of the warp receives lane (quarter base + i), columns c .. c+31
+__device__ __forceinline__ void tc_ld32(uint32_t taddr, float (&v)[32]) {
+    uint32_t r[32];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+// Epilogue of one thread: weight row `row`, tokens t0 .. t0+31 with the sums v[0..31].  Lanes are consecutive rows,
+// so for a fixed token a warp's stores are contiguous; the partner row (row ^ 1) of the rotation and SwiGLU pairs
+// is the neighbouring lane.  Arithmetic and rounding are those of pf_epilogue.
+template <int EPI>
+__device__ __forceinline__ void umma_epilogue(const PrefillGemmArgs& a, int split, int row, int t0, const float (&v)[32],
+                                              int lane) {
+    const bool row_ok = row < a.n_rows;
+    const int nt = min(32, a.n_tokens - t0);  // valid tokens of this half (may be <= 0)
+    if constexpr (EPI == kPfResid) {
+        if (a.splits > 1) {
+            float* p = a.part + ((size_t)split * kPrefillTokens + t0) * a.n_rows + row;
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+                if (row_ok && i < nt) p[(size_t)i * a.n_rows] = v[i];
+        } else {
+            float* p = a.x + (size_t)t0 * a.n_rows + row;
+            float old[32];
+#pragma unroll
+            for (int i = 0; i < 32; ++i) old[i] = (row_ok && i < nt) ? p[(size_t)i * a.n_rows] : 0.f;
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+                if (row_ok && i < nt) p[(size_t)i * a.n_rows] = old[i] + v[i];  // x += W.xb (src/model.cpp:232, 239)
+        }
+    } else if constexpr (EPI == kPfSwiglu) {
+        // rows interleaved (gate_i, up_i): the even lane finishes tokens 0..15 of the pair, the odd lane tokens 16..31;
+        // each sends the partner the half it does not finish itself.  hb = (h1*sigmoid(h1))*h3 (src/ops.cpp:78-87)
+        // with the fast exponential and division: the result is rounded to FP16 as an MMA operand anyway.
+        const bool even = (lane & 1) == 0;
+        __half* hb = a.hb + (size_t)(t0 + (even ? 0 : 16)) * (a.n_rows >> 1) + (row >> 1);
+        const int nt_mine = nt - (even ? 0 : 16);
+#pragma unroll
+        for (int k = 0; k < 16; ++k) {
+            const float keep = even ? v[k] : v[k + 16], send = even ? v[k + 16] : v[k];
+            const float recv = __shfl_xor_sync(0xffffffffu, send, 1);
+            const float g = even ? keep : recv, u = even ? recv : keep;
+            const float r = __fdividef(g, 1.0f + __expf(-g)) * u;
+            if (row_ok && k < nt_mine) hb[(size_t)k * (a.n_rows >> 1)] = __float2half_rn(r);
+        }
+    } else if (a.splits > 1) {  // kPfQkv cut along K: partial sums, finished by prefill_qkv_finish_kernel
+        float* p = a.part + ((size_t)split * kPrefillTokens + t0) * a.n_rows + row;
+#pragma unroll
+        for (int i = 0; i < 32; ++i)
+            if (row_ok && i < nt) p[(size_t)i * a.n_rows] = v[i];
+    } else {  // kPfQkv
+        const int hs = a.head_size;
+        const bool pos_ok = a.start_pos >= 0 && a.start_pos + a.n_tokens <= a.seq_len;
+        if (!pos_ok && lane == 0) atomicOr(&a.st->status, kStatusBadPos);
+        const bool rot = row < a.q_rows + a.kv_rows;   // q and k rows rotate, v rows do not
+        const bool is_q = row < a.q_rows, is_k = rot && !is_q;
+        const int rr = is_q ? row : row - a.q_rows - (is_k ? 0 : a.kv_rows);
+        const int head = rr / hs, off = rr - head * hs;
+        const float2* rope = a.rope + (off >> 1);       // + pos * (hs / 2)
+        float* qp = a.q + row;                          // + t * q_rows
+        // cache index within the layer: h*(seq_len*hs) + pos*hs + off (src/scatter_kv.cu:15-16)
+        __half* cp = (is_k ? a.k_cache : a.v_cache) + (size_t)head * ((size_t)a.seq_len * hs) + off;
+        const bool odd = row & 1;
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+            const float other = __shfl_xor_sync(0xffffffffu, v[i], 1);
+            if (!(row_ok && pos_ok && i < nt)) continue;
+            const int t = t0 + i, pos = a.start_pos + t;
+            float r = v[i];
+            if (rot) {
+                // adjacent-pair rotation with the table entry for (pos, off/2) (src/ops.cpp:34-54)
+                const float2 cs = __ldg(rope + (size_t)pos * (hs >> 1));
+                r = odd ? __fadd_rn(__fmul_rn(other, cs.y), __fmul_rn(v[i], cs.x))   // v1' = v0*sin + v1*cos
+                        : __fsub_rn(__fmul_rn(v[i], cs.x), __fmul_rn(other, cs.y));  // v0' = v0*cos - v1*sin
+            }
+            if (is_q)
+                qp[(size_t)t * a.q_rows] = r;
+            else
+                cp[(size_t)pos * hs] = __float2half_rn(r);
+        }
+    }
+}
+
+#ifdef LPP_TIMING_AIDS
+// timing aid: global-timer stamps [cta][slot] of the last gate|up launch
+__device__ unsigned long long g_pf_trace[160][48];
+#define PF_STAMP(k)                                                                      \
+    do {                                                                                 \
+        if (EPI == kPfSwiglu && (k) < 48) {                                              \
+            unsigned long long t_;                                                       \
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));                       \
+            g_pf_trace[blockIdx.x][k] = t_;                                              \
+        }                                                                                \
+    } while (0)
+#else
+#define PF_STAMP(k) \
+    do {            \
+    } while (0)
+#endif
+
+template <int EPI>
+static __global__ void __launch_bounds__(kUmmaThreads, 1) prefill_gemm_umma_kernel(const __grid_constant__ CUtensorMap w_map,
+                                                                                   const __grid_constant__ CUtensorMap x_map,
+                                                                                   const PrefillGemmArgs a) {
+    extern __shared__ __align__(128) unsigned char smem[];
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem);  // [kUmmaStages]
+    uint64_t* empty = full + kUmmaStages;                // [kUmmaStages]
+    uint64_t* acc_full = empty + kUmmaStages;            // [2]
+    uint64_t* acc_empty = acc_full + 2;                  // [2]
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+    const uint32_t ring = (smem_u32(smem) + 1024u + 1023u) & ~1023u;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int n_tiles = (a.n_rows + kUmmaM - 1) / kUmmaM;
+    const int n_kc = (a.K + kPfKc - 1) / kPfKc;
+    const int S = a.splits;
+    const int n_items = n_tiles * S;
+    pdl_launch_dependents();
+    if (tid == 0) {
+        for (int i = 0; i < kUmmaStages; ++i) {
+            mbar_init(&full[i], 1);
+            mbar_init(&empty[i], 1);
+        }
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(&acc_full[i], 1);
+            mbar_init(&acc_empty[i], kUmmaEpiWarps);
+        }
+        mbar_fence_init();
+    }
+    if (warp == 1) {
+        tc_alloc(tmem_slot, kUmmaTmemCols);
+        tc_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *reinterpret_cast<volatile uint32_t*>(tmem_slot);
+
+    if (warp == 0) {
+        // ---------------- producer
+        if (lane == 0) {
+            PF_STAMP(0);
+            // The weight sub-tiles of the first ring pass do not depend on the previous kernel: they are requested
+            // before the dependency wait, the activation sub-tiles of the same stages right after it.
+            int slot = 0, pass = 0;
+            bool ok = true, waited = false;
+            int early = 0;  // stages whose weights are already in flight
+            for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
+                const int tile = item / S, split = item - tile * S;
+                const int kc0 = (split * n_kc) / S, kc1 = ((split + 1) * n_kc) / S;
+                if (!waited) {
+                    early = min(kc1 - kc0, kUmmaStages);
+                    for (int i = 0; i < early; ++i) {
+                        const uint32_t dst = ring + (uint32_t)i * kUmmaStage;
+                        mbar_arrive_expect_tx(&full[i], kUmmaStage);
+                        tma_load_2d(dst, &w_map, (kc0 + i) * kPfKc, a.row0 + tile * kUmmaM, &full[i]);
+                        tma_load_2d(dst + kUmmaSubW, &w_map, (kc0 + i) * kPfKc + 64, a.row0 + tile * kUmmaM, &full[i]);
+                    }
+                    pdl_wait();
+                    PF_STAMP(1);
+                    waited = true;
+                }
+                for (int kc = kc0; kc < kc1; ++kc) {
+                    const uint32_t dst = ring + (uint32_t)slot * kUmmaStage;
+                    if (early > 0) {
+                        --early;  // first pass of the first item: only the activations are missing
+                    } else {
+                        if (pass > 0 && !mbar_wait_bounded(&empty[slot], (uint32_t)(pass - 1) & 1u, a.st)) {
+                            ok = false;
+                            break;
+                        }
+                        mbar_arrive_expect_tx(&full[slot], kUmmaStage);
+                        tma_load_2d(dst, &w_map, kc * kPfKc, a.row0 + tile * kUmmaM, &full[slot]);
+                        tma_load_2d(dst + kUmmaSubW, &w_map, kc * kPfKc + 64, a.row0 + tile * kUmmaM, &full[slot]);
+                    }
+                    PF_STAMP(2 + kc - kc0);
+                    tma_load_2d(dst + 2 * kUmmaSubW, &x_map, kc * kPfKc, 0, &full[slot]);
+                    tma_load_2d(dst + 2 * kUmmaSubW + kPfSubBytesX, &x_map, kc * kPfKc + 64, 0, &full[slot]);
+                    if (++slot == kUmmaStages) {
+                        slot = 0;
+                        ++pass;
+                    }
+                }
+            }
+            if (!waited) pdl_wait();
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issue
+        if (lane == 0) {
+            int slot = 0;
+            uint32_t par = 0;
+            bool ok = true;
+            int it = 0;
+            for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x, ++it) {
+                const int tile = item / S, split = item - tile * S;
+                const int kc0 = (split * n_kc) / S, kc1 = ((split + 1) * n_kc) / S;
+                const int b = it & 1, use = it >> 1;
+                (void)tile;
+                if (use > 0 && !mbar_wait_bounded(&acc_empty[b], (uint32_t)(use - 1) & 1u, a.st)) break;
+                tc_fence_after();
+                const uint32_t d_tmem = tmem + (uint32_t)(b * kUmmaAccCols);
+                for (int kc = kc0; kc < kc1; ++kc) {
+                    if (!mbar_wait_bounded(&full[slot], par, a.st)) {
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after();
+                    PF_STAMP(18 + kc - kc0);
+                    const uint32_t st = ring + (uint32_t)slot * kUmmaStage;
+#pragma unroll
+                    for (int sub = 0; sub < 2; ++sub) {
+                        const uint32_t wt = st + sub * kUmmaSubW, xt = st + 2 * kUmmaSubW + sub * kPfSubBytesX;
+#pragma unroll
+                        for (int ks = 0; ks < 4; ++ks)  // 16 inputs = 32 bytes along the swizzled row per step
+                            tc_mma_f16(d_tmem, umma_desc(wt + ks * 32), umma_desc(xt + ks * 32), kUmmaIdesc,
+                                       (kc > kc0 || sub > 0 || ks > 0) ? 1u : 0u);
+                    }
+                    tc_commit(&empty[slot]);  // arrives once the MMAs issued so far have read this stage
+                    if (++slot == kUmmaStages) {
+                        slot = 0;
+                        par ^= 1u;
+                    }
+                }
+                if (ok) tc_commit(&acc_full[b]);
+            }
+        }
+    } else {
+        // ---------------- epilogue: this warp owns tensor-memory lanes 32 * (warp % 4) .. + 31 = rows of the tile,
+        // and the first or second 32 columns (tokens) of the accumulator
+        const int quarter = warp & 3, half = (warp - 2) >> 2;
+        int it = 0;
+        for (int item = blockIdx.x; item < n_items; item += gridDim.x, ++it) {
+            const int tile = item / S, split = item - tile * S;
+            const int b = it & 1, use = it >> 1;
+            if (!__all_sync(0xffffffffu, mbar_wait_bounded(&acc_full[b], (uint32_t)use & 1u, a.st))) break;
+            tc_fence_after();
+            if (tid == 64) PF_STAMP(34);
+            float v[32];
+            tc_ld32(tmem + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(b * kUmmaAccCols + half * 32), v);
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&acc_empty[b]);
+            if (tid == 64) PF_STAMP(35);
+            umma_epilogue<EPI>(a, split, tile * kUmmaM + quarter * 32 + lane, half * 32, v, lane);
+            if (tid == 64) PF_STAMP(36);
+        }
+    }
+    // ---------------- common exit
+    __syncwarp();
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) tc_dealloc(tmem, kUmmaTmemCols);
+}
+
+// Finishes a QKV GEMM that was cut along K: adds the partial sums of a row pair in range order and applies the
+// QKV epilogue (rotation of q and k pairs, q -> FP32 rows, k/v -> cache rows at the reference index).
+// grid: (tokens, ceil(row pairs / 256)).
+static __global__ void __launch_bounds__(256) prefill_qkv_finish_kernel(const PrefillGemmArgs a) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int t = blockIdx.x, pr = blockIdx.y * 256 + threadIdx.x;
+    const int row = 2 * pr;
+    if (row >= a.n_rows) return;
+    float2 v = make_float2(0.f, 0.f);
+    float2 p[kPfMaxSplits];
+#pragma unroll
+    for (int s0 = 0; s0 < kPfMaxSplits; ++s0)
+        if (s0 < a.splits) p[s0] = *reinterpret_cast<const float2*>(a.part + ((size_t)s0 * kPrefillTokens + t) * a.n_rows + row);
+#pragma unroll
+    for (int s0 = 0; s0 < kPfMaxSplits; ++s0)
+        if (s0 < a.splits) {
+            v.x += p[s0].x;
+            v.y += p[s0].y;
+        }
+    pf_epilogue(a, 0, row, t, v.x, v.y);
+    pf_epilogue(a, 0, row + 1, t, v.y, v.x);
+}
 
 // Rows of the residual stream -> RMS-normalised FP16 rows (MMA operands).  Layer 0 takes the embedding rows of
 // the prompt tokens and also writes them out as the FP32 residual stream.  grid: tokens.
@@ -251,7 +618,7 @@ static __global__ void __launch_bounds__(kPfNormThreads) prefill_norm_kernel(flo
     const int t = blockIdx.x, tid = threadIdx.x;
     float4* xr = reinterpret_cast<float4*>(x + (size_t)t * D);
     const int nv4 = D >> 2;  // D is a multiple of 8
-    constexpr int kMaxPer = 4;  // float4 per thread held in registers: rows up to 8192 wide in one sweep
+    constexpr int kMaxPer = 4;  // float4 per thread kept in registers for the second pass: rows up to 8192 wide
     float4 v[kMaxPer];
     int tok = 0;
     if (emb) {
@@ -261,48 +628,53 @@ static __global__ void __launch_bounds__(kPfNormThreads) prefill_norm_kernel(flo
             tok = 0;
         }
     }
+    const bool add_parts = !emb && splits > 1;
     float ss = 0.f;
-    for (int base = 0; base < nv4; base += kMaxPer * kPfNormThreads) {
-        // every load of the sweep is issued before the first is used: one memory round trip, not one per element
 #pragma unroll
-        for (int k = 0; k < kMaxPer; ++k) {
-            const int i = base + tid + k * kPfNormThreads;
-            if (i < nv4) {
-                if (emb) {
-                    const uint2 h = *reinterpret_cast<const uint2*>(emb + (size_t)tok * D + 4 * (size_t)i);
-                    const float2 lo = half2_bits_to_float2(h.x), hi = half2_bits_to_float2(h.y);
-                    v[k] = make_float4(lo.x, lo.y, hi.x, hi.y);
-                } else {
-                    v[k] = xr[i];
-                }
+    for (int k = 0; k < kMaxPer; ++k) {
+        const int i = tid + k * kPfNormThreads;
+        if (i < nv4) {
+            // every load of this piece (the row and all partial sums) is issued before the first is used
+            float4 p[kPfMaxSplits];
+            if (emb) {
+                const uint2 h = *reinterpret_cast<const uint2*>(emb + (size_t)tok * D + 4 * (size_t)i);
+                const float2 lo = half2_bits_to_float2(h.x), hi = half2_bits_to_float2(h.y);
+                v[k] = make_float4(lo.x, lo.y, hi.x, hi.y);
+            } else {
+                v[k] = xr[i];
             }
-        }
-        if (!emb && splits > 1) {
-            // the preceding residual GEMM left its K-range partial sums: x += p_0 + p_1 + ... in range order
-            for (int s0 = 0; s0 < splits; ++s0) {
-                float4 p[kMaxPer];
+            if (add_parts) {
 #pragma unroll
-                for (int k = 0; k < kMaxPer; ++k) {
-                    const int i = base + tid + k * kPfNormThreads;
-                    if (i < nv4) p[k] = reinterpret_cast<const float4*>(part + ((size_t)s0 * kPrefillTokens + t) * D)[i];
-                }
+                for (int s0 = 0; s0 < kPfMaxSplits; ++s0)
+                    if (s0 < splits) p[s0] = reinterpret_cast<const float4*>(part + ((size_t)s0 * kPrefillTokens + t) * D)[i];
+                // x += p_0 + p_1 + ... in range order
 #pragma unroll
-                for (int k = 0; k < kMaxPer; ++k) {
-                    const int i = base + tid + k * kPfNormThreads;
-                    if (i < nv4) {
-                        v[k].x += p[k].x; v[k].y += p[k].y; v[k].z += p[k].z; v[k].w += p[k].w;
+                for (int s0 = 0; s0 < kPfMaxSplits; ++s0)
+                    if (s0 < splits) {
+                        v[k].x += p[s0].x; v[k].y += p[s0].y; v[k].z += p[s0].z; v[k].w += p[s0].w;
                     }
-                }
             }
+            if (emb || add_parts) xr[i] = v[k];  // the residual stream as the next residual GEMM reads it
+            ss = fmaf(v[k].x, v[k].x, fmaf(v[k].y, v[k].y, fmaf(v[k].z, v[k].z, fmaf(v[k].w, v[k].w, ss))));
         }
-#pragma unroll
-        for (int k = 0; k < kMaxPer; ++k) {
-            const int i = base + tid + k * kPfNormThreads;
-            if (i < nv4) {
-                if (emb || splits > 1) xr[i] = v[k];  // the residual stream as the next residual GEMM reads it
-                ss = fmaf(v[k].x, v[k].x, fmaf(v[k].y, v[k].y, fmaf(v[k].z, v[k].z, fmaf(v[k].w, v[k].w, ss))));
+    }
+    // rows wider than kMaxPer * kPfNormThreads * 4: the rest without register caching
+    for (int i = tid + kMaxPer * kPfNormThreads; i < nv4; i += kPfNormThreads) {
+        float4 w;
+        if (emb) {
+            const uint2 h = *reinterpret_cast<const uint2*>(emb + (size_t)tok * D + 4 * (size_t)i);
+            const float2 lo = half2_bits_to_float2(h.x), hi = half2_bits_to_float2(h.y);
+            w = make_float4(lo.x, lo.y, hi.x, hi.y);
+        } else {
+            w = xr[i];
+        }
+        if (add_parts)
+            for (int s0 = 0; s0 < splits; ++s0) {
+                const float4 q = reinterpret_cast<const float4*>(part + ((size_t)s0 * kPrefillTokens + t) * D)[i];
+                w.x += q.x; w.y += q.y; w.z += q.z; w.w += q.w;
             }
-        }
+        if (emb || add_parts) xr[i] = w;
+        ss = fmaf(w.x, w.x, fmaf(w.y, w.y, fmaf(w.z, w.z, fmaf(w.w, w.w, ss))));
     }
     ss = warp_sum(ss);
     if ((tid & 31) == 0) red[tid >> 5] = ss;
@@ -311,23 +683,21 @@ static __global__ void __launch_bounds__(kPfNormThreads) prefill_norm_kernel(flo
 #pragma unroll
     for (int k = 0; k < kPfNormThreads / 32; ++k) tot += red[k];
     const float scale = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(tot, (float)D), 1e-5f)));
-    const bool one_sweep = nv4 <= kMaxPer * kPfNormThreads;
-    for (int base = 0; base < nv4; base += kMaxPer * kPfNormThreads) {
+    auto emit = [&](int i, const float4& xv) {
+        const float4 w = __ldg(reinterpret_cast<const float4*>(norm_w) + i);
+        const __half2 lo = __floats2half2_rn(__fmul_rn(__fmul_rn(xv.x, scale), w.x), __fmul_rn(__fmul_rn(xv.y, scale), w.y));
+        const __half2 hi = __floats2half2_rn(__fmul_rn(__fmul_rn(xv.z, scale), w.z), __fmul_rn(__fmul_rn(xv.w, scale), w.w));
+        uint2 o;
+        o.x = *reinterpret_cast<const unsigned int*>(&lo);
+        o.y = *reinterpret_cast<const unsigned int*>(&hi);
+        *reinterpret_cast<uint2*>(out + (size_t)t * D + 4 * (size_t)i) = o;
+    };
 #pragma unroll
-        for (int k = 0; k < kMaxPer; ++k) {
-            const int i = base + tid + k * kPfNormThreads;
-            if (i < nv4) {
-                const float4 xv = one_sweep ? v[k] : xr[i];  // wider rows re-read what this thread wrote
-                const float4 w = __ldg(reinterpret_cast<const float4*>(norm_w) + i);
-                const __half2 lo = __floats2half2_rn(__fmul_rn(__fmul_rn(xv.x, scale), w.x), __fmul_rn(__fmul_rn(xv.y, scale), w.y));
-                const __half2 hi = __floats2half2_rn(__fmul_rn(__fmul_rn(xv.z, scale), w.z), __fmul_rn(__fmul_rn(xv.w, scale), w.w));
-                uint2 o;
-                o.x = *reinterpret_cast<const unsigned int*>(&lo);
-                o.y = *reinterpret_cast<const unsigned int*>(&hi);
-                *reinterpret_cast<uint2*>(out + (size_t)t * D + 4 * (size_t)i) = o;
-            }
-        }
+    for (int k = 0; k < kMaxPer; ++k) {
+        const int i = tid + k * kPfNormThreads;
+        if (i < nv4) emit(i, v[k]);
     }
+    for (int i = tid + kMaxPer * kPfNormThreads; i < nv4; i += kPfNormThreads) emit(i, xr[i]);  // re-read what this thread wrote
 }
 
 // Causal attention of the prompt block: query token t (position start_pos + t) over cache rows 0..start_pos + t,
