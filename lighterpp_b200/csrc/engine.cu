@@ -1288,15 +1288,15 @@ static lpp_status prefill_setup(lpp_engine* e) {
     const size_t qkv_rows = e->Dq + 2 * (size_t)e->KVd;
     CU(cudaMalloc(&e->pf_x, T * D * 4));
     CU(cudaMalloc(&e->pf_q, T * e->Dq * 4));
-    CU(cudaMalloc(&e->pf_xn, T * D * 2));
-    CU(cudaMalloc(&e->pf_att, T * e->Dq * 2));
-    CU(cudaMalloc(&e->pf_hb, T * e->Fl * 2));
+    CU(cudaMalloc(&e->pf_xn, 2 * T * D * 2));  // hi plane, lo plane
+    CU(cudaMalloc(&e->pf_att, 2 * T * e->Dq * 2));  // hi plane, lo plane
+    CU(cudaMalloc(&e->pf_hb, 2 * T * e->Fl * 2));  // hi plane, lo plane
     CU(cudaMalloc(&e->pf_part, (size_t)kPfMaxSplits * T * std::max<size_t>(D, qkv_rows) * 4));
     CU(cudaMalloc(&e->pf_tokens, T * sizeof(int)));
     CU(cudaMemsetAsync(e->pf_x, 0, T * D * 4, e->stream));
-    CU(cudaMemsetAsync(e->pf_xn, 0, T * D * 2, e->stream));
-    CU(cudaMemsetAsync(e->pf_att, 0, T * e->Dq * 2, e->stream));
-    CU(cudaMemsetAsync(e->pf_hb, 0, T * e->Fl * 2, e->stream));
+    CU(cudaMemsetAsync(e->pf_xn, 0, 2 * T * D * 2, e->stream));
+    CU(cudaMemsetAsync(e->pf_att, 0, 2 * T * e->Dq * 2, e->stream));
+    CU(cudaMemsetAsync(e->pf_hb, 0, 2 * T * e->Fl * 2, e->stream));
     CU(cudaMemsetAsync(e->pf_tokens, 0, T * sizeof(int), e->stream));
 #ifdef LPP_TIMING_AIDS
     if (const char* v = aid_env("LPP_PF_UMMA")) {  // comparison kernel (warp-level MMA): bit 0 clear for the residual/SwiGLU GEMMs, bit 1 for QKV
@@ -1309,9 +1309,9 @@ static lpp_status prefill_setup(lpp_engine* e) {
     TRY(make_map(&e->pf_map_wo, e->wo, L * D, e->Dq, e->pf_rows));
     TRY(make_map(&e->pf_map_w13, e->w13, L * 2 * e->Fl, D, e->pf_rows));
     TRY(make_map(&e->pf_map_w2, e->w2, L * D, e->Fl, e->pf_rows));
-    TRY(make_map(&e->pf_map_xn, e->pf_xn, T, D, kPrefillTokens));
-    TRY(make_map(&e->pf_map_att, e->pf_att, T, e->Dq, kPrefillTokens));
-    TRY(make_map(&e->pf_map_hb, e->pf_hb, T, e->Fl, kPrefillTokens));
+    TRY(make_map(&e->pf_map_xn, e->pf_xn, 2 * T, D, kPrefillTokens));
+    TRY(make_map(&e->pf_map_att, e->pf_att, 2 * T, e->Dq, kPrefillTokens));
+    TRY(make_map(&e->pf_map_hb, e->pf_hb, 2 * T, e->Fl, kPrefillTokens));
 #ifdef LPP_TIMING_AIDS
     CU(cudaFuncSetAttribute(prefill_gemm_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, kPfSmemBytes));
     CU(cudaFuncSetAttribute(prefill_gemm_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, kPfSmemBytes));

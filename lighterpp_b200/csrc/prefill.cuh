@@ -49,6 +49,15 @@ struct PfGeom {
 
 enum PfEpi : int { kPfQkv = 0, kPfResid = 1, kPfSwiglu = 2 };
 
+// An activation x is handed to the tensor cores as two FP16 numbers, hi = fp16(x) and lo = fp16(x - hi): the MMA
+// accumulates W.hi + W.lo in FP32, which keeps about 22 bits of x, so the batched pass carries FP32 activations
+// through FP16-operand MMAs like the token loop carries them through its FP32 arithmetic.  Every activation buffer
+// holds the hi plane [kPrefillTokens][cols] followed by the lo plane; one tensor map covers both (lo tile at row 64).
+__device__ __forceinline__ void split_half(float x, __half& hi, __half& lo) {
+    hi = __float2half_rn(x);
+    lo = __float2half_rn(x - __half2float(hi));
+}
+
 struct PrefillGemmArgs {
     int n_rows, K;        // rows of the weight matrix, inputs per row
     int row0;             // first row of this layer's matrix inside the tensor map (layers are stacked)
@@ -106,7 +115,10 @@ __device__ __forceinline__ void pf_epilogue(const PrefillGemmArgs& a, int split,
         // rows are interleaved (gate_i, up_i); hb = (h1*sigmoid(h1))*h3 (src/ops.cpp:78-87): the even row writes
         if ((row & 1) == 0) {
             const float sig = __fdiv_rn(1.0f, 1.0f + expf(-v));
-            a.hb[(size_t)t * (a.n_rows >> 1) + (row >> 1)] = __float2half_rn(__fmul_rn(__fmul_rn(v, sig), other));
+            __half hi, lo;
+            split_half(__fmul_rn(__fmul_rn(v, sig), other), hi, lo);
+            a.hb[(size_t)t * (a.n_rows >> 1) + (row >> 1)] = hi;
+            a.hb[(size_t)(kPrefillTokens + t) * (a.n_rows >> 1) + (row >> 1)] = lo;
         }
     } else {  // kPfQkv
         const int pos = a.start_pos + t;
@@ -277,8 +289,8 @@ static __global__ void __launch_bounds__(kPfThreads) prefill_gemm_kernel(const _
 // Every wait is bounded; every path, also a failed one, reaches the common exit that frees the tensor memory.
 constexpr int kUmmaM = 128;
 constexpr int kUmmaSubW = kUmmaM * 128;                            // 16 KiB
-constexpr int kUmmaStage = 2 * kUmmaSubW + 2 * kPfSubBytesX;       // 48 KiB
-constexpr int kUmmaStages = kPfRingBytes / kUmmaStage;             // 4
+constexpr int kUmmaStage = 2 * kUmmaSubW + 4 * kPfSubBytesX;       // 64 KiB: weights, activations hi, activations lo
+constexpr int kUmmaStages = kPfRingBytes / kUmmaStage;             // 3
 constexpr int kUmmaEpiWarps = 8;                                   // two per tensor-memory lane quarter: 32 tokens each
 constexpr int kUmmaThreads = (2 + kUmmaEpiWarps) * 32;
 constexpr int kUmmaAccCols = kPrefillTokens;                       // FP32 columns of one accumulator
@@ -358,7 +370,7 @@ __device__ __forceinline__ void umma_epilogue(const PrefillGemmArgs& a, int spli
     } else if constexpr (EPI == kPfSwiglu) {
         // rows interleaved (gate_i, up_i): the even lane finishes tokens 0..15 of the pair, the odd lane tokens 16..31;
         // each sends the partner the half it does not finish itself.  hb = (h1*sigmoid(h1))*h3 (src/ops.cpp:78-87)
-        // with the fast exponential and division: the result is rounded to FP16 as an MMA operand anyway.
+        // with the fast exponential and division (relative error ~1e-6, far below the FP16 weights' own rounding).
         const bool even = (lane & 1) == 0;
         __half* hb = a.hb + (size_t)(t0 + (even ? 0 : 16)) * (a.n_rows >> 1) + (row >> 1);
         const int nt_mine = nt - (even ? 0 : 16);
@@ -368,7 +380,12 @@ __device__ __forceinline__ void umma_epilogue(const PrefillGemmArgs& a, int spli
             const float recv = __shfl_xor_sync(0xffffffffu, send, 1);
             const float g = even ? keep : recv, u = even ? recv : keep;
             const float r = __fdividef(g, 1.0f + __expf(-g)) * u;
-            if (row_ok && k < nt_mine) hb[(size_t)k * (a.n_rows >> 1)] = __float2half_rn(r);
+            __half hi, lo;
+            split_half(r, hi, lo);
+            if (row_ok && k < nt_mine) {
+                hb[(size_t)k * (a.n_rows >> 1)] = hi;
+                hb[(size_t)(kPrefillTokens + k) * (a.n_rows >> 1)] = lo;
+            }
         }
     } else if (a.splits > 1) {  // kPfQkv cut along K: partial sums, finished by prefill_qkv_finish_kernel
         float* p = a.part + ((size_t)split * kPrefillTokens + t0) * a.n_rows + row;
@@ -502,6 +519,8 @@ static __global__ void __launch_bounds__(kUmmaThreads, 1) prefill_gemm_umma_kern
                     PF_STAMP(2 + kc - kc0);
                     tma_load_2d(dst + 2 * kUmmaSubW, &x_map, kc * kPfKc, 0, &full[slot]);
                     tma_load_2d(dst + 2 * kUmmaSubW + kPfSubBytesX, &x_map, kc * kPfKc + 64, 0, &full[slot]);
+                    tma_load_2d(dst + 2 * kUmmaSubW + 2 * kPfSubBytesX, &x_map, kc * kPfKc, kPrefillTokens, &full[slot]);
+                    tma_load_2d(dst + 2 * kUmmaSubW + 3 * kPfSubBytesX, &x_map, kc * kPfKc + 64, kPrefillTokens, &full[slot]);
                     if (++slot == kUmmaStages) {
                         slot = 0;
                         ++pass;
@@ -537,9 +556,11 @@ static __global__ void __launch_bounds__(kUmmaThreads, 1) prefill_gemm_umma_kern
                     for (int sub = 0; sub < 2; ++sub) {
                         const uint32_t wt = st + sub * kUmmaSubW, xt = st + 2 * kUmmaSubW + sub * kPfSubBytesX;
 #pragma unroll
-                        for (int ks = 0; ks < 4; ++ks)  // 16 inputs = 32 bytes along the swizzled row per step
-                            tc_mma_f16(d_tmem, umma_desc(wt + ks * 32), umma_desc(xt + ks * 32), kUmmaIdesc,
-                                       (kc > kc0 || sub > 0 || ks > 0) ? 1u : 0u);
+                        for (int ks = 0; ks < 4; ++ks) {  // 16 inputs = 32 bytes along the swizzled row per step
+                            const uint64_t wd = umma_desc(wt + ks * 32);
+                            tc_mma_f16(d_tmem, wd, umma_desc(xt + ks * 32), kUmmaIdesc, (kc > kc0 || sub > 0 || ks > 0) ? 1u : 0u);
+                            tc_mma_f16(d_tmem, wd, umma_desc(xt + 2 * kPfSubBytesX + ks * 32), kUmmaIdesc, 1u);  // lo plane
+                        }
                     }
                     tc_commit(&empty[slot]);  // arrives once the MMAs issued so far have read this stage
                     if (++slot == kUmmaStages) {
@@ -685,12 +706,13 @@ static __global__ void __launch_bounds__(kPfNormThreads) prefill_norm_kernel(flo
     const float scale = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(tot, (float)D), 1e-5f)));
     auto emit = [&](int i, const float4& xv) {
         const float4 w = __ldg(reinterpret_cast<const float4*>(norm_w) + i);
-        const __half2 lo = __floats2half2_rn(__fmul_rn(__fmul_rn(xv.x, scale), w.x), __fmul_rn(__fmul_rn(xv.y, scale), w.y));
-        const __half2 hi = __floats2half2_rn(__fmul_rn(__fmul_rn(xv.z, scale), w.z), __fmul_rn(__fmul_rn(xv.w, scale), w.w));
-        uint2 o;
-        o.x = *reinterpret_cast<const unsigned int*>(&lo);
-        o.y = *reinterpret_cast<const unsigned int*>(&hi);
-        *reinterpret_cast<uint2*>(out + (size_t)t * D + 4 * (size_t)i) = o;
+        const float y[4] = {__fmul_rn(__fmul_rn(xv.x, scale), w.x), __fmul_rn(__fmul_rn(xv.y, scale), w.y),
+                            __fmul_rn(__fmul_rn(xv.z, scale), w.z), __fmul_rn(__fmul_rn(xv.w, scale), w.w)};
+        __align__(8) __half hi[4], lo[4];
+#pragma unroll
+        for (int c = 0; c < 4; ++c) split_half(y[c], hi[c], lo[c]);
+        *reinterpret_cast<uint2*>(out + (size_t)t * D + 4 * (size_t)i) = *reinterpret_cast<const uint2*>(hi);
+        *reinterpret_cast<uint2*>(out + (size_t)(kPrefillTokens + t) * D + 4 * (size_t)i) = *reinterpret_cast<const uint2*>(lo);
     };
 #pragma unroll
     for (int k = 0; k < kMaxPer; ++k) {
@@ -773,7 +795,12 @@ static __global__ void __launch_bounds__(256) prefill_attention_kernel(const flo
     l = warp_sum(l);
 #pragma unroll
     for (int c = 0; c < 4; ++c)
-        if (lane + 32 * c < hs) out[(size_t)t * q_rows + (size_t)h * hs + lane + 32 * c] = __float2half_rn(__fdiv_rn(acc[c], l));
+        if (lane + 32 * c < hs) {
+            __half hi, lo;
+            split_half(__fdiv_rn(acc[c], l), hi, lo);
+            out[(size_t)t * q_rows + (size_t)h * hs + lane + 32 * c] = hi;
+            out[(size_t)(kPrefillTokens + t) * q_rows + (size_t)h * hs + lane + 32 * c] = lo;
+        }
 }
 
 // Causal attention of the prompt block on the tensor cores: CTA (query tile of 16 tokens, KV head), one warp per
@@ -958,12 +985,16 @@ static __global__ void __launch_bounds__(256) prefill_attention_mma_kernel(const
 #pragma unroll
     for (int i = 0; i < HS / 8; ++i) {
         const int d = 8 * i + 2 * tq;
-        if (r0 < n_tokens)
-            *reinterpret_cast<uint32_t*>(out + (size_t)r0 * q_rows + (size_t)h * HS + d) =
-                pack_half2(__fdiv_rn(o[i][0], l0), __fdiv_rn(o[i][1], l0));
-        if (r1 < n_tokens)
-            *reinterpret_cast<uint32_t*>(out + (size_t)r1 * q_rows + (size_t)h * HS + d) =
-                pack_half2(__fdiv_rn(o[i][2], l1), __fdiv_rn(o[i][3], l1));
+        auto put = [&](int r, float a0, float a1) {
+            __align__(4) __half hi[2], lo[2];
+            split_half(a0, hi[0], lo[0]);
+            split_half(a1, hi[1], lo[1]);
+            *reinterpret_cast<uint32_t*>(out + (size_t)r * q_rows + (size_t)h * HS + d) = *reinterpret_cast<const uint32_t*>(hi);
+            *reinterpret_cast<uint32_t*>(out + (size_t)(kPrefillTokens + r) * q_rows + (size_t)h * HS + d) =
+                *reinterpret_cast<const uint32_t*>(lo);
+        };
+        if (r0 < n_tokens) put(r0, __fdiv_rn(o[i][0], l0), __fdiv_rn(o[i][1], l0));
+        if (r1 < n_tokens) put(r1, __fdiv_rn(o[i][2], l1), __fdiv_rn(o[i][3], l1));
     }
 }
 
