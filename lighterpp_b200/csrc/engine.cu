@@ -180,7 +180,6 @@ struct lpp_engine {
     __half *pf_xn = nullptr, *pf_att = nullptr, *pf_hb = nullptr;
     int* pf_tokens = nullptr;
     CUtensorMap pf_map_wqkv, pf_map_wo, pf_map_w13, pf_map_w2, pf_map_xn, pf_map_att, pf_map_hb;
-    int pf_rows_qkv = kUmmaM, pf_rows = kUmmaM;  // weight rows per tile (= box rows of the weight maps)
     bool pf_ready = false;
 
     bool finalized = false;
@@ -1251,34 +1250,58 @@ typedef CUresult (*encode_tiled_fn)(CUtensorMap*, CUtensorMapDataType, cuuint32_
                                     const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                                     CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
-// Tensor map over a row-major FP16 matrix [rows][cols] of THIS GPU's memory: boxes of box_rows x 64 inputs (128
-// bytes) stored with the 128-byte swizzle, which is what makes the kernel's ldmatrix reads bank-conflict free;
-// out-of-range elements read as zero.
-static lpp_status make_map(CUtensorMap* m, const void* base, size_t rows, size_t cols, int box_rows) {
+static encode_tiled_fn tensor_map_encoder() {
     static encode_tiled_fn encode = nullptr;
     if (!encode) {
         cudaDriverEntryPointQueryResult qr;
         void* fn = nullptr;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qr) != cudaSuccess || !fn ||
-            qr != cudaDriverEntryPointSuccess)
-            return fail(LPP_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
-        encode = (encode_tiled_fn)fn;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qr) == cudaSuccess && fn &&
+            qr == cudaDriverEntryPointSuccess)
+            encode = (encode_tiled_fn)fn;
     }
-    const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-    const cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
-    const cuuint32_t box[2] = {64u, (cuuint32_t)box_rows};
-    const cuuint32_t estr[2] = {1, 1};
-    const CUresult r = encode(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+    return encode;
+}
+
+// Tensor maps over row-major FP16 matrices of THIS GPU's memory, cut into pieces of 64 inputs (128 bytes, stored with
+// the 128-byte swizzle: the K-major operand layout of the MMA descriptors).  cols must be a multiple of 64; elements
+// outside the matrix read as zero.
+//
+// Weights [rows][cols] seen as (64 inputs, rows, cols / 64): a box is 64 inputs x box_rows rows x 2 pieces, i.e. one
+// copy delivers both 64-input sub-tiles of a stage, sub-tile after sub-tile.
+static lpp_status make_weight_map(CUtensorMap* m, const void* base, size_t rows, size_t cols, int box_rows) {
+    encode_tiled_fn encode = tensor_map_encoder();
+    if (!encode) return fail(LPP_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+    const cuuint64_t dims[3] = {64, (cuuint64_t)rows, (cuuint64_t)(cols / 64)};
+    const cuuint64_t strides[2] = {(cuuint64_t)cols * 2, 128};
+    const cuuint32_t box[3] = {64u, (cuuint32_t)box_rows, 2u};
+    const cuuint32_t estr[3] = {1, 1, 1};
+    const CUresult r = encode(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
                               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return fail(LPP_ERR_CUDA, "cuTensorMapEncodeTiled failed (%d) for a %zu x %zu matrix", (int)r, rows, cols);
+    return LPP_OK;
+}
+// Activations: hi plane [tokens][cols] followed by the lo plane, seen as (64 inputs, tokens, 2 planes, cols / 64): a
+// box is 64 inputs x box_tokens x 2 planes x 2 pieces, i.e. one copy delivers, per 64-input piece, the hi rows
+// followed by the lo rows: one K-major operand tile of 2 x box_tokens rows (the MMA's N) per piece.
+static lpp_status make_activation_map(CUtensorMap* m, const void* base, size_t tokens, size_t cols, int box_tokens) {
+    encode_tiled_fn encode = tensor_map_encoder();
+    if (!encode) return fail(LPP_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+    const cuuint64_t dims[4] = {64, (cuuint64_t)tokens, 2, (cuuint64_t)(cols / 64)};
+    const cuuint64_t strides[3] = {(cuuint64_t)cols * 2, (cuuint64_t)tokens * cols * 2, 128};
+    const cuuint32_t box[4] = {64u, (cuuint32_t)box_tokens, 2u, 2u};
+    const cuuint32_t estr[4] = {1, 1, 1, 1};
+    const CUresult r = encode(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, const_cast<void*>(base), dims, strides, box, estr,
+                              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(LPP_ERR_CUDA, "cuTensorMapEncodeTiled failed (%d) for a %zu x %zu activation block", (int)r, tokens, cols);
     return LPP_OK;
 }
 
 // The tensor-core path takes FP16 weights, an FP16 cache and a single GPU; everything else is fed token by token.
 static bool prefill_batched(const lpp_engine* e) {
     return e->c.tp_size == 1 && e->c.weight_dtype == LPP_F16 && e->c.kv_dtype == LPP_F16 && e->hs <= 128 && e->gqa <= 8 &&
-           !(e->c.flags & LPP_FLAG_NO_PREFILL_GEMM);
+           e->c.dim % 64 == 0 && e->Dq % 64 == 0 && e->Fl % 64 == 0 && !(e->c.flags & LPP_FLAG_NO_PREFILL_GEMM);
 }
 
 static lpp_status prefill_setup(lpp_engine* e) {
@@ -1298,24 +1321,13 @@ static lpp_status prefill_setup(lpp_engine* e) {
     CU(cudaMemsetAsync(e->pf_att, 0, 2 * T * e->Dq * 2, e->stream));
     CU(cudaMemsetAsync(e->pf_hb, 0, 2 * T * e->Fl * 2, e->stream));
     CU(cudaMemsetAsync(e->pf_tokens, 0, T * sizeof(int), e->stream));
-#ifdef LPP_TIMING_AIDS
-    if (const char* v = aid_env("LPP_PF_UMMA")) {  // comparison kernel (warp-level MMA): bit 0 clear for the residual/SwiGLU GEMMs, bit 1 for QKV
-        const int m = atoi(v);
-        e->pf_rows = (m & 1) ? kUmmaM : 64;
-        e->pf_rows_qkv = (m & 2) ? kUmmaM : 32;
-    }
-#endif
-    TRY(make_map(&e->pf_map_wqkv, e->wqkv, L * qkv_rows, D, e->pf_rows_qkv));
-    TRY(make_map(&e->pf_map_wo, e->wo, L * D, e->Dq, e->pf_rows));
-    TRY(make_map(&e->pf_map_w13, e->w13, L * 2 * e->Fl, D, e->pf_rows));
-    TRY(make_map(&e->pf_map_w2, e->w2, L * D, e->Fl, e->pf_rows));
-    TRY(make_map(&e->pf_map_xn, e->pf_xn, 2 * T, D, kPrefillTokens));
-    TRY(make_map(&e->pf_map_att, e->pf_att, 2 * T, e->Dq, kPrefillTokens));
-    TRY(make_map(&e->pf_map_hb, e->pf_hb, 2 * T, e->Fl, kPrefillTokens));
-#ifdef LPP_TIMING_AIDS
-    CU(cudaFuncSetAttribute(prefill_gemm_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, kPfSmemBytes));
-    CU(cudaFuncSetAttribute(prefill_gemm_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, kPfSmemBytes));
-#endif
+    TRY(make_weight_map(&e->pf_map_wqkv, e->wqkv, L * qkv_rows, D, kUmmaM));
+    TRY(make_weight_map(&e->pf_map_wo, e->wo, L * D, e->Dq, kUmmaM));
+    TRY(make_weight_map(&e->pf_map_w13, e->w13, L * 2 * e->Fl, D, kUmmaM));
+    TRY(make_weight_map(&e->pf_map_w2, e->w2, L * D, e->Fl, kUmmaM));
+    TRY(make_activation_map(&e->pf_map_xn, e->pf_xn, T, D, kPrefillTokens));
+    TRY(make_activation_map(&e->pf_map_att, e->pf_att, T, e->Dq, kPrefillTokens));
+    TRY(make_activation_map(&e->pf_map_hb, e->pf_hb, T, e->Fl, kPrefillTokens));
     CU(cudaFuncSetAttribute(prefill_gemm_umma_kernel<kPfQkv>, cudaFuncAttributeMaxDynamicSharedMemorySize, kPfSmemBytes));
     CU(cudaFuncSetAttribute(prefill_gemm_umma_kernel<kPfResid>, cudaFuncAttributeMaxDynamicSharedMemorySize, kPfSmemBytes));
     CU(cudaFuncSetAttribute(prefill_gemm_umma_kernel<kPfSwiglu>, cudaFuncAttributeMaxDynamicSharedMemorySize, kPfSmemBytes));
@@ -1325,37 +1337,28 @@ static lpp_status prefill_setup(lpp_engine* e) {
     return LPP_OK;
 }
 
-// tile_rows must match the weight map's box: 128 for the tcgen05 kernel (32 or 64: the comparison kernel of the
-// timing-aids build).  A GEMM whose row tiles do not fill the GPU is also cut along K; its partial sums go to pf_part
-// and are added up by the next prefill_norm_kernel (residual projections) or by prefill_qkv_finish_kernel (QKV).
-static cudaError_t launch_prefill_gemm(lpp_engine* e, const CUtensorMap& wm, const CUtensorMap& xm, PrefillGemmArgs a, int tile_rows) {
-    const int tiles = (a.n_rows + tile_rows - 1) / tile_rows;
+// Work items are tiles of 128 weight rows (the weight maps' box).  A GEMM whose row tiles do not fill the GPU is also
+// cut along K; its partial sums go to pf_part and are added up by the next prefill_norm_kernel (residual projections)
+// or by prefill_qkv_finish_kernel (QKV).
+static cudaError_t launch_prefill_gemm(lpp_engine* e, const CUtensorMap& wm, const CUtensorMap& xm, PrefillGemmArgs a) {
+    const int tiles = (a.n_rows + kUmmaM - 1) / kUmmaM;
     const int n_kc = (a.K + kPfKc - 1) / kPfKc;
     a.st = e->st;
     a.splits = 1;
-    // the tcgen05 QKV GEMM is cut too: its partial sums are finished by prefill_qkv_finish_kernel
-    if ((a.epi == kPfResid || (a.epi == kPfQkv && tile_rows == kUmmaM)) && tiles < e->num_sms)
+    // QKV is cut too: its partial sums are finished by prefill_qkv_finish_kernel
+    if ((a.epi == kPfResid || a.epi == kPfQkv) && tiles < e->num_sms)
         a.splits = std::max(1, std::min({kPfMaxSplits, n_kc, (e->num_sms + tiles - 1) / tiles}));
     a.part = e->pf_part;
-    const int grid = std::min(tiles * a.splits, e->num_sms);
-    if (tile_rows == kUmmaM) {
-        const dim3 g(grid), b(kUmmaThreads);
-        if (a.epi == kPfResid) return launch_kernel(prefill_gemm_umma_kernel<kPfResid>, g, b, (size_t)kPfSmemBytes, e->stream, true, wm, xm, a);
-        if (a.epi == kPfSwiglu) return launch_kernel(prefill_gemm_umma_kernel<kPfSwiglu>, g, b, (size_t)kPfSmemBytes, e->stream, true, wm, xm, a);
-        const cudaError_t err = launch_kernel(prefill_gemm_umma_kernel<kPfQkv>, g, b, (size_t)kPfSmemBytes, e->stream, true, wm, xm, a);
-        if (err != cudaSuccess || a.splits == 1) return err;
-        return launch_kernel(prefill_qkv_finish_kernel, dim3(a.n_tokens, (a.n_rows / 2 + 255) / 256), dim3(256), 0, e->stream, true, a);
-    }
-#ifdef LPP_TIMING_AIDS
-    if (tile_rows == 32)
-        return launch_kernel(prefill_gemm_kernel<32>, dim3(grid), dim3(kPfThreads), (size_t)kPfSmemBytes, e->stream, true, wm, xm, a);
-    return launch_kernel(prefill_gemm_kernel<64>, dim3(grid), dim3(kPfThreads), (size_t)kPfSmemBytes, e->stream, true, wm, xm, a);
-#else
-    return cudaErrorInvalidValue;
-#endif
+    const dim3 g(std::min(tiles * a.splits, e->num_sms)), b(kUmmaThreads);
+    const size_t sm = (size_t)kPfSmemBytes;
+    if (a.epi == kPfResid) return launch_kernel(prefill_gemm_umma_kernel<kPfResid>, g, b, sm, e->stream, true, wm, xm, a);
+    if (a.epi == kPfSwiglu) return launch_kernel(prefill_gemm_umma_kernel<kPfSwiglu>, g, b, sm, e->stream, true, wm, xm, a);
+    const cudaError_t err = launch_kernel(prefill_gemm_umma_kernel<kPfQkv>, g, b, sm, e->stream, true, wm, xm, a);
+    if (err != cudaSuccess || a.splits == 1) return err;
+    return launch_kernel(prefill_qkv_finish_kernel, dim3(a.n_tokens, (a.n_rows / 2 + 255) / 256), dim3(256), 0, e->stream, true, a);
 }
 static int prefill_splits(const lpp_engine* e, int n_rows, int K) {  // what launch_prefill_gemm chooses for a residual GEMM
-    const int tiles = (n_rows + e->pf_rows - 1) / e->pf_rows, n_kc = (K + kPfKc - 1) / kPfKc;
+    const int tiles = (n_rows + kUmmaM - 1) / kUmmaM, n_kc = (K + kPfKc - 1) / kPfKc;
     return tiles < e->num_sms ? std::max(1, std::min({kPfMaxSplits, n_kc, (e->num_sms + tiles - 1) / tiles})) : 1;
 }
 
@@ -1388,7 +1391,7 @@ static lpp_status prefill_block(lpp_engine* e, const int* h_tokens, int n, int s
         g.rope = e->rope;
         g.k_cache = (__half*)e->kcache + lofs;
         g.v_cache = (__half*)e->vcache + lofs;
-        CU(launch_prefill_gemm(e, e->pf_map_wqkv, e->pf_map_xn, g, e->pf_rows_qkv));
+        CU(launch_prefill_gemm(e, e->pf_map_wqkv, e->pf_map_xn, g));
         if (l == L - 1) break;
         const dim3 agrid((n + kPfAttnRows - 1) / kPfAttnRows, e->KVHl);
         const bool pf_mma = !aid_env("LPP_ATTN_CUDA_CORES");
@@ -1413,7 +1416,7 @@ static lpp_status prefill_block(lpp_engine* e, const int* h_tokens, int n, int s
         o.row0 = l * D;
         o.epi = kPfResid;
         o.x = e->pf_x;
-        CU(launch_prefill_gemm(e, e->pf_map_wo, e->pf_map_att, o, e->pf_rows));
+        CU(launch_prefill_gemm(e, e->pf_map_wo, e->pf_map_att, o));
         CU(launch_kernel(prefill_norm_kernel, dim3(n), dim3(kPfNormThreads), 0, e->stream, true, e->pf_x, (const int*)e->pf_tokens,
                          (const __half*)nullptr, c.vocab_size, (const float*)(e->rms_ffn + (size_t)l * D), e->pf_xn, D, n,
                          (const float*)e->pf_part, s_o, e->st));
@@ -1425,7 +1428,7 @@ static lpp_status prefill_block(lpp_engine* e, const int* h_tokens, int n, int s
         u.row0 = l * 2 * e->Fl;
         u.epi = kPfSwiglu;
         u.hb = e->pf_hb;
-        CU(launch_prefill_gemm(e, e->pf_map_w13, e->pf_map_xn, u, e->pf_rows));
+        CU(launch_prefill_gemm(e, e->pf_map_w13, e->pf_map_xn, u));
         PrefillGemmArgs d = {};
         d.n_tokens = n;
         d.start_pos = start_pos;
@@ -1434,7 +1437,7 @@ static lpp_status prefill_block(lpp_engine* e, const int* h_tokens, int n, int s
         d.row0 = l * D;
         d.epi = kPfResid;
         d.x = e->pf_x;
-        CU(launch_prefill_gemm(e, e->pf_map_w2, e->pf_map_hb, d, e->pf_rows));
+        CU(launch_prefill_gemm(e, e->pf_map_w2, e->pf_map_hb, d));
     }
     return LPP_OK;
 }

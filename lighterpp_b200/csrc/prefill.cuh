@@ -7,13 +7,14 @@
 // the weight stream (2 FLOP per weight byte and token: far below the tensor cores' ridge for 64 tokens), so the
 // kernels are organised around that stream like the decode GEMV -- a producer thread, a ring of shared-memory
 // stages, mbarrier hand-over -- only that a stage is a set of 2-D tiles fetched by the tensor memory accelerator
-// (cp.async.bulk.tensor.2d with the 128-byte swizzle: 128 weight rows x 128 inputs and the matching 64 tokens x
-// 128 inputs of the activations, the weight tiles of the first ring pass requested before the dependency wait)
-// and the arithmetic runs on the tensor cores:
-//   * prefill_gemm_umma_kernel: tcgen05.mma reading both operands from shared memory through matrix descriptors,
-//     FP32 accumulators in tensor memory, epilogue warps that read them back with tcgen05.ld (the product path);
-//   * prefill_gemm_kernel: the same ring consumed by eight warps with ldmatrix + mma.sync.m16n8k16 (kept as the
-//     comparison kernel of the timing-aids build).
+// (cp.async.bulk.tensor with the 128-byte swizzle, one copy per operand and stage: 128 weight rows x 128 inputs
+// through a 3-D map, the matching 64 tokens x 128 inputs of the activations, hi and lo plane, through a 4-D map;
+// the weight tiles of the first ring pass are requested before the dependency wait) and the arithmetic runs on
+// the tensor cores:
+// prefill_gemm_umma_kernel issues tcgen05.mma reading both operands from shared memory through matrix descriptors,
+// FP32 accumulators in tensor memory, epilogue warps that read them back with tcgen05.ld.  (An earlier kernel that
+// consumed the same ring with ldmatrix + mma.sync.m16n8k16 in eight warps measured 1.17 ms against 0.83 ms for a
+// 64-token pass of the Llama-3.2-1B shape and was removed.)
 // Matrices whose row tiles do not fill the GPU (QKV, o_proj, down) are also cut along K so that every SM streams
 // a share; partial sums are added in a fixed order by the next kernel (the norm kernel for the residual
 // projections, prefill_qkv_finish_kernel for QKV).  Activations are rounded to FP16 as MMA operands; everything
@@ -30,22 +31,10 @@ namespace lpp {
 
 constexpr int kPrefillTokens = 64;   // tokens per pass (rows of the activation tiles)
 constexpr int kPfKc = 128;           // inputs per stage: two 64-wide (128-byte) swizzled sub-tiles per operand
-constexpr int kPfConsumerWarps = 8;
-constexpr int kPfThreads = (kPfConsumerWarps + 1) * 32;
 constexpr int kPfSubBytesX = kPrefillTokens * 128;  // one activation sub-tile: 64 tokens x 64 inputs
 constexpr int kPfMaxSplits = 8;
 constexpr int kPfRingBytes = 192 * 1024;
 constexpr int kPfSmemBytes = 1024 /*barriers*/ + 1024 /*alignment slack*/ + kPfRingBytes;
-template <int M>
-struct PfGeom {
-    static constexpr int kSubW = M * 128;                         // one weight sub-tile: M rows x 64 inputs
-    static constexpr int kStage = 2 * kSubW + 2 * kPfSubBytesX;   // 32 KiB (M = 64) / 24 KiB (M = 32)
-    static constexpr int kStages = kPfRingBytes / kStage;         // 6 / 8
-    static constexpr int kRowTiles = M / 16;                      // 16-row MMA tiles per CTA tile
-    static constexpr int kTokGroups = kPfConsumerWarps / kRowTiles;
-    static constexpr int kTokPerWarp = kPrefillTokens / kTokGroups;  // 32 / 16
-    static constexpr int kNT = kTokPerWarp / 8;                   // 8-token MMA tiles per warp
-};
 
 enum PfEpi : int { kPfQkv = 0, kPfResid = 1, kPfSwiglu = 2 };
 
@@ -80,10 +69,16 @@ struct PrefillGemmArgs {
     __half* v_cache;
 };
 
-__device__ __forceinline__ void tma_load_2d(uint32_t smem_dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
-    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
+__device__ __forceinline__ void tma_load_3d(uint32_t smem_dst, const CUtensorMap* map, int x, int y, int z, uint32_t bar_addr) {
+    asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];" ::"r"(
                      smem_dst),
-                 "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar))
+                 "l"(map), "r"(x), "r"(y), "r"(z), "r"(bar_addr)
+                 : "memory");
+}
+__device__ __forceinline__ void tma_load_4d(uint32_t smem_dst, const CUtensorMap* map, int x, int y, int z, int w, uint32_t bar_addr) {
+    asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];" ::"r"(
+                     smem_dst),
+                 "l"(map), "r"(x), "r"(y), "r"(z), "r"(w), "r"(bar_addr)
                  : "memory");
 }
 
@@ -95,12 +90,6 @@ __device__ __forceinline__ void mma_f16_16816(float (&d)[4], uint32_t a0, uint32
 __device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
 }
-// Address of 16-byte chunk `chunk` (0..7) of row `row` in a sub-tile written by the tensor memory accelerator with
-// the 128-byte swizzle (rows of 128 bytes, chunk index XOR row % 8; the sub-tile starts on a 1024-byte boundary).
-__device__ __forceinline__ uint32_t swz(uint32_t base, int row, int chunk) {
-    return base + (uint32_t)row * 128u + (uint32_t)((chunk ^ (row & 7)) << 4);
-}
-
 // One value of the finished tile: row `row` (and its pair partner `other`, the value of row ^ 1), token t.
 __device__ __forceinline__ void pf_epilogue(const PrefillGemmArgs& a, int split, int row, int t, float v, float other) {
     if (row >= a.n_rows || t >= a.n_tokens) return;
@@ -147,132 +136,6 @@ __device__ __forceinline__ void pf_epilogue(const PrefillGemmArgs& a, int split,
     }
 }
 
-#ifdef LPP_TIMING_AIDS
-// Comparison kernel of the timing-aids build (warp-level MMA); the product runs prefill_gemm_umma_kernel below.
-// C[t][row] = sum_k X[t][k] * W[row][k] for t < 64, fused with the epilogue.  A work item is (tile of M rows, K
-// range); CTA b takes items b, b + grid, ...; the ring runs across item boundaries.  M = 32 for the matrices with
-// few rows per SM and an epilogue that needs the whole sum (QKV), 64 otherwise.
-template <int M>
-static __global__ void __launch_bounds__(kPfThreads) prefill_gemm_kernel(const __grid_constant__ CUtensorMap w_map,
-                                                                          const __grid_constant__ CUtensorMap x_map,
-                                                                          const PrefillGemmArgs a) {
-    using G = PfGeom<M>;
-    extern __shared__ __align__(128) unsigned char smem[];
-    uint64_t* full = reinterpret_cast<uint64_t*>(smem);  // [kStages]
-    uint64_t* empty = full + G::kStages;                 // [kStages]
-    const uint32_t ring = (smem_u32(smem) + 1024u + 1023u) & ~1023u;  // swizzled sub-tiles start on 1024-byte boundaries
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int n_tiles = (a.n_rows + M - 1) / M;
-    const int n_kc = (a.K + kPfKc - 1) / kPfKc;
-    const int S = a.splits;
-    const int n_items = n_tiles * S;
-    pdl_launch_dependents();
-    if (tid < G::kStages) {
-        mbar_init(&full[tid], 1);
-        mbar_init(&empty[tid], kPfConsumerWarps);
-        mbar_fence_init();
-    }
-    __syncthreads();
-
-    if (warp == kPfConsumerWarps) {
-        // ---------------- producer: one lane issues the four sub-tile copies of every stage
-        if (lane == 0) {
-            // the weight sub-tiles of the first ring pass are requested before the dependency wait (they do not depend
-            // on the previous kernel), the activation sub-tiles of the same stages right after it
-            int slot = 0, pass = 0, early = 0;
-            bool waited = false;
-            for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
-                const int tile = item / S, split = item - tile * S;
-                const int kc0 = (split * n_kc) / S, kc1 = ((split + 1) * n_kc) / S;
-                if (!waited) {
-                    early = min(kc1 - kc0, G::kStages);
-                    for (int i = 0; i < early; ++i) {
-                        const uint32_t dst = ring + (uint32_t)i * G::kStage;
-                        mbar_arrive_expect_tx(&full[i], G::kStage);
-                        tma_load_2d(dst, &w_map, (kc0 + i) * kPfKc, a.row0 + tile * M, &full[i]);
-                        tma_load_2d(dst + G::kSubW, &w_map, (kc0 + i) * kPfKc + 64, a.row0 + tile * M, &full[i]);
-                    }
-                    pdl_wait();
-                    waited = true;
-                }
-                for (int kc = kc0; kc < kc1; ++kc) {
-                    const uint32_t dst = ring + (uint32_t)slot * G::kStage;
-                    if (early > 0) {
-                        --early;
-                    } else {
-                        if (pass > 0 && !mbar_wait_bounded(&empty[slot], (uint32_t)(pass - 1) & 1u, a.st)) return;
-                        mbar_arrive_expect_tx(&full[slot], G::kStage);
-                        tma_load_2d(dst, &w_map, kc * kPfKc, a.row0 + tile * M, &full[slot]);
-                        tma_load_2d(dst + G::kSubW, &w_map, kc * kPfKc + 64, a.row0 + tile * M, &full[slot]);
-                    }
-                    tma_load_2d(dst + 2 * G::kSubW, &x_map, kc * kPfKc, 0, &full[slot]);
-                    tma_load_2d(dst + 2 * G::kSubW + kPfSubBytesX, &x_map, kc * kPfKc + 64, 0, &full[slot]);
-                    if (++slot == G::kStages) {
-                        slot = 0;
-                        ++pass;
-                    }
-                }
-            }
-        }
-        return;
-    }
-
-    // ---------------- consumers: warp = (16-row tile rt of the CTA tile, token group tg)
-    const int rt = warp % G::kRowTiles, tg = warp / G::kRowTiles;
-    const int g = lane >> 2, j = lane & 3;
-    // ldmatrix source rows of this lane.  A (x4): matrices (rows 0-7, k 0-7), (rows 8-15, k 0-7), (rows 0-7, k 8-15),
-    // (rows 8-15, k 8-15) = a0..a3.  B (x4): (tokens 0-7, k 0-7), (tokens 0-7, k 8-15), (tokens 8-15, k 0-7),
-    // (tokens 8-15, k 8-15) = b0, b1 of two 8-token tiles.
-    const int a_row = rt * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, a_chunk = lane >> 4;
-    const int b_row = tg * G::kTokPerWarp + (lane & 7) + ((lane >> 4) & 1) * 8, b_chunk = (lane >> 3) & 1;
-    int slot = 0;
-    uint32_t par = 0;
-    for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
-        const int tile = item / S, split = item - tile * S;
-        const int kc0 = (split * n_kc) / S, kc1 = ((split + 1) * n_kc) / S;
-        float acc[G::kNT][4];
-#pragma unroll
-        for (int nt = 0; nt < G::kNT; ++nt) acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f;
-        for (int kc = kc0; kc < kc1; ++kc) {
-            if (!__all_sync(0xffffffffu, mbar_wait_bounded(&full[slot], par, a.st))) return;
-            const uint32_t st = ring + (uint32_t)slot * G::kStage;
-#pragma unroll
-            for (int sub = 0; sub < 2; ++sub) {
-                const uint32_t wt = st + sub * G::kSubW, xt = st + 2 * G::kSubW + sub * kPfSubBytesX;
-#pragma unroll
-                for (int ks = 0; ks < 4; ++ks) {  // four 16-input steps per 64-wide sub-tile
-                    uint32_t a0, a1, a2, a3;
-                    ldmatrix_x4(swz(wt, a_row, 2 * ks + a_chunk), a0, a1, a2, a3);
-#pragma unroll
-                    for (int np = 0; np < G::kNT / 2; ++np) {
-                        uint32_t b0, b1, b2, b3;
-                        ldmatrix_x4(swz(xt, b_row + np * 16, 2 * ks + b_chunk), b0, b1, b2, b3);
-                        mma_f16_16816(acc[2 * np], a0, a1, a2, a3, b0, b1);
-                        mma_f16_16816(acc[2 * np + 1], a0, a1, a2, a3, b2, b3);
-                    }
-                }
-            }
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&empty[slot]);
-            if (++slot == G::kStages) {
-                slot = 0;
-                par ^= 1u;
-            }
-        }
-        // acc[nt]: rows g (c0, c1) and g + 8 (c2, c3), tokens tg*kTokPerWarp + nt*8 + 2j (c0, c2) and + 1 (c1, c3)
-        const int row_lo = tile * M + rt * 16 + g;
-#pragma unroll
-        for (int nt = 0; nt < G::kNT; ++nt)
-#pragma unroll
-            for (int c = 0; c < 4; ++c) {
-                const float v = acc[nt][c];
-                const float other = __shfl_xor_sync(0xffffffffu, v, 4);  // the same token, row g ^ 1
-                pf_epilogue(a, split, row_lo + (c >> 1) * 8, tg * G::kTokPerWarp + nt * 8 + 2 * j + (c & 1), v, other);
-            }
-    }
-}
-#endif  // LPP_TIMING_AIDS
-
 // ---- the GEMM on the fifth-generation tensor cores (tcgen05), accumulators in tensor memory
 //
 // A work item is (tile of 128 weight rows, K range).  Per stage the tensor memory accelerator delivers two
@@ -293,11 +156,12 @@ constexpr int kUmmaStage = 2 * kUmmaSubW + 4 * kPfSubBytesX;       // 64 KiB: we
 constexpr int kUmmaStages = kPfRingBytes / kUmmaStage;             // 3
 constexpr int kUmmaEpiWarps = 8;                                   // two per tensor-memory lane quarter: 32 tokens each
 constexpr int kUmmaThreads = (2 + kUmmaEpiWarps) * 32;
-constexpr int kUmmaAccCols = kPrefillTokens;                       // FP32 columns of one accumulator
+constexpr int kUmmaN = 2 * kPrefillTokens;                         // MMA N: the 64 hi rows and the 64 lo rows of the activation tile
+constexpr int kUmmaAccCols = kUmmaN;                               // FP32 columns of one accumulator: W.hi | W.lo
 constexpr int kUmmaTmemCols = 2 * kUmmaAccCols;                    // power of two >= 32
 // Instruction descriptor: D = F32 (bits 4-5 = 1), A = B = F16 (0), both K-major (bits 15, 16 = 0),
 // N / 8 in bits 17-22, M / 16 in bits 24-28.
-constexpr uint32_t kUmmaIdesc = (1u << 4) | ((uint32_t)(kPrefillTokens >> 3) << 17) | ((uint32_t)(kUmmaM >> 4) << 24);
+constexpr uint32_t kUmmaIdesc = (1u << 4) | ((uint32_t)(kUmmaN >> 3) << 17) | ((uint32_t)(kUmmaM >> 4) << 24);
 
 // Shared-memory matrix descriptor of a K-major operand tile with the 128-byte swizzle: start address / 16 in bits
 // 0-13, leading byte offset (unused for swizzled K-major, set to 1) in bits 16-29, stride between 8-row groups
@@ -446,21 +310,23 @@ template <int EPI>
 static __global__ void __launch_bounds__(kUmmaThreads, 1) prefill_gemm_umma_kernel(const __grid_constant__ CUtensorMap w_map,
                                                                                    const __grid_constant__ CUtensorMap x_map,
                                                                                    const PrefillGemmArgs a) {
+    constexpr int kStages = kUmmaStages, kStage = kUmmaStage, kSubX = kPfSubBytesX;
     extern __shared__ __align__(128) unsigned char smem[];
-    uint64_t* full = reinterpret_cast<uint64_t*>(smem);  // [kUmmaStages]
-    uint64_t* empty = full + kUmmaStages;                // [kUmmaStages]
-    uint64_t* acc_full = empty + kUmmaStages;            // [2]
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem);  // [kStages]
+    uint64_t* empty = full + kStages;                    // [kStages]
+    uint64_t* acc_full = empty + kStages;                // [2]
     uint64_t* acc_empty = acc_full + 2;                  // [2]
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
     const uint32_t ring = (smem_u32(smem) + 1024u + 1023u) & ~1023u;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int n_tiles = (a.n_rows + kUmmaM - 1) / kUmmaM;
+    const int unit = blockIdx.x, n_units = gridDim.x;
+    const int n_tiles = (a.n_rows + kUmmaM - 1) / kUmmaM;  // items along the rows
     const int n_kc = (a.K + kPfKc - 1) / kPfKc;
     const int S = a.splits;
     const int n_items = n_tiles * S;
     pdl_launch_dependents();
     if (tid == 0) {
-        for (int i = 0; i < kUmmaStages; ++i) {
+        for (int i = 0; i < kStages; ++i) {
             mbar_init(&full[i], 1);
             mbar_init(&empty[i], 1);
         }
@@ -488,23 +354,27 @@ static __global__ void __launch_bounds__(kUmmaThreads, 1) prefill_gemm_umma_kern
             int slot = 0, pass = 0;
             bool ok = true, waited = false;
             int early = 0;  // stages whose weights are already in flight
-            for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
+            // one copy per operand and stage: both 64-input weight sub-tiles / the four activation sub-tiles (hi, lo)
+            auto load_w = [&](uint32_t dst, int kc, int wrow, int sl) { tma_load_3d(dst, &w_map, 0, wrow, 2 * kc, smem_u32(&full[sl])); };
+            auto load_x = [&](uint32_t dst, int kc, int sl) { tma_load_4d(dst, &x_map, 0, 0, 0, 2 * kc, smem_u32(&full[sl])); };
+            auto expect = [&](int sl) { mbar_arrive_expect_tx(&full[sl], kStage); };
+            for (int item = unit; item < n_items && ok; item += n_units) {
                 const int tile = item / S, split = item - tile * S;
                 const int kc0 = (split * n_kc) / S, kc1 = ((split + 1) * n_kc) / S;
+                const int wrow = a.row0 + tile * kUmmaM;
                 if (!waited) {
-                    early = min(kc1 - kc0, kUmmaStages);
+                    early = min(kc1 - kc0, kStages);
                     for (int i = 0; i < early; ++i) {
-                        const uint32_t dst = ring + (uint32_t)i * kUmmaStage;
-                        mbar_arrive_expect_tx(&full[i], kUmmaStage);
-                        tma_load_2d(dst, &w_map, (kc0 + i) * kPfKc, a.row0 + tile * kUmmaM, &full[i]);
-                        tma_load_2d(dst + kUmmaSubW, &w_map, (kc0 + i) * kPfKc + 64, a.row0 + tile * kUmmaM, &full[i]);
+                        const uint32_t dst = ring + (uint32_t)i * kStage;
+                        expect(i);
+                        load_w(dst, kc0 + i, wrow, i);
                     }
                     pdl_wait();
                     PF_STAMP(1);
                     waited = true;
                 }
                 for (int kc = kc0; kc < kc1; ++kc) {
-                    const uint32_t dst = ring + (uint32_t)slot * kUmmaStage;
+                    const uint32_t dst = ring + (uint32_t)slot * kStage;
                     if (early > 0) {
                         --early;  // first pass of the first item: only the activations are missing
                     } else {
@@ -512,16 +382,12 @@ static __global__ void __launch_bounds__(kUmmaThreads, 1) prefill_gemm_umma_kern
                             ok = false;
                             break;
                         }
-                        mbar_arrive_expect_tx(&full[slot], kUmmaStage);
-                        tma_load_2d(dst, &w_map, kc * kPfKc, a.row0 + tile * kUmmaM, &full[slot]);
-                        tma_load_2d(dst + kUmmaSubW, &w_map, kc * kPfKc + 64, a.row0 + tile * kUmmaM, &full[slot]);
+                        expect(slot);
+                        load_w(dst, kc, wrow, slot);
                     }
                     PF_STAMP(2 + kc - kc0);
-                    tma_load_2d(dst + 2 * kUmmaSubW, &x_map, kc * kPfKc, 0, &full[slot]);
-                    tma_load_2d(dst + 2 * kUmmaSubW + kPfSubBytesX, &x_map, kc * kPfKc + 64, 0, &full[slot]);
-                    tma_load_2d(dst + 2 * kUmmaSubW + 2 * kPfSubBytesX, &x_map, kc * kPfKc, kPrefillTokens, &full[slot]);
-                    tma_load_2d(dst + 2 * kUmmaSubW + 3 * kPfSubBytesX, &x_map, kc * kPfKc + 64, kPrefillTokens, &full[slot]);
-                    if (++slot == kUmmaStages) {
+                    load_x(dst + 2 * kUmmaSubW, kc, slot);
+                    if (++slot == kStages) {
                         slot = 0;
                         ++pass;
                     }
@@ -536,7 +402,7 @@ static __global__ void __launch_bounds__(kUmmaThreads, 1) prefill_gemm_umma_kern
             uint32_t par = 0;
             bool ok = true;
             int it = 0;
-            for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x, ++it) {
+            for (int item = unit; item < n_items && ok; item += n_units, ++it) {
                 const int tile = item / S, split = item - tile * S;
                 const int kc0 = (split * n_kc) / S, kc1 = ((split + 1) * n_kc) / S;
                 const int b = it & 1, use = it >> 1;
@@ -551,19 +417,19 @@ static __global__ void __launch_bounds__(kUmmaThreads, 1) prefill_gemm_umma_kern
                     }
                     tc_fence_after();
                     PF_STAMP(18 + kc - kc0);
-                    const uint32_t st = ring + (uint32_t)slot * kUmmaStage;
+                    const uint32_t st = ring + (uint32_t)slot * kStage;
 #pragma unroll
                     for (int sub = 0; sub < 2; ++sub) {
-                        const uint32_t wt = st + sub * kUmmaSubW, xt = st + 2 * kUmmaSubW + sub * kPfSubBytesX;
+                        // the activation sub-tile holds the hi rows followed by the lo rows: one MMA covers both (N = 128)
+                        const uint32_t wt = st + sub * kUmmaSubW, xt = st + 2 * kUmmaSubW + sub * 2 * kSubX;
 #pragma unroll
                         for (int ks = 0; ks < 4; ++ks) {  // 16 inputs = 32 bytes along the swizzled row per step
-                            const uint64_t wd = umma_desc(wt + ks * 32);
-                            tc_mma_f16(d_tmem, wd, umma_desc(xt + ks * 32), kUmmaIdesc, (kc > kc0 || sub > 0 || ks > 0) ? 1u : 0u);
-                            tc_mma_f16(d_tmem, wd, umma_desc(xt + 2 * kPfSubBytesX + ks * 32), kUmmaIdesc, 1u);  // lo plane
+                            const uint32_t acc = (kc > kc0 || sub > 0 || ks > 0) ? 1u : 0u;
+                            tc_mma_f16(d_tmem, umma_desc(wt + ks * 32), umma_desc(xt + ks * 32), kUmmaIdesc, acc);
                         }
                     }
                     tc_commit(&empty[slot]);  // arrives once the MMAs issued so far have read this stage
-                    if (++slot == kUmmaStages) {
+                    if (++slot == kStages) {
                         slot = 0;
                         par ^= 1u;
                     }
@@ -576,14 +442,18 @@ static __global__ void __launch_bounds__(kUmmaThreads, 1) prefill_gemm_umma_kern
         // and the first or second 32 columns (tokens) of the accumulator
         const int quarter = warp & 3, half = (warp - 2) >> 2;
         int it = 0;
-        for (int item = blockIdx.x; item < n_items; item += gridDim.x, ++it) {
+        for (int item = unit; item < n_items; item += n_units, ++it) {
             const int tile = item / S, split = item - tile * S;
             const int b = it & 1, use = it >> 1;
             if (!__all_sync(0xffffffffu, mbar_wait_bounded(&acc_full[b], (uint32_t)use & 1u, a.st))) break;
             tc_fence_after();
             if (tid == 64) PF_STAMP(34);
-            float v[32];
-            tc_ld32(tmem + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(b * kUmmaAccCols + half * 32), v);
+            float v[32], vlo[32];
+            const uint32_t taddr = tmem + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(b * kUmmaAccCols);
+            tc_ld32(taddr + half * 32, v);                     // W.hi of this warp's 32 tokens
+            tc_ld32(taddr + kPrefillTokens + half * 32, vlo);  // W.lo
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] += vlo[i];
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&acc_empty[b]);

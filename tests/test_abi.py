@@ -79,5 +79,5 @@ def test_library_is_the_product_build():
     made with -DLPP_TIMING_AIDS; the library that ships must not contain them."""
     with open(E.LIB_PATH, "rb") as f:
         blob = f.read()
-    for name in (b"LPP_DEBUG_SKIP", b"LPP_DEBUG_GEMV", b"LPP_STAGE_KB", b"LPP_ATTN_CHUNK", b"LPP_PF_UMMA"):
+    for name in (b"LPP_DEBUG_SKIP", b"LPP_DEBUG_GEMV", b"LPP_STAGE_KB", b"LPP_ATTN_CHUNK", b"LPP_ATTN_CUDA_CORES"):
         assert name not in blob, name
