@@ -149,7 +149,8 @@ __device__ __forceinline__ void pf_epilogue(const PrefillGemmArgs& a, int split,
 // 2..9 epilogue (a warp may only read the tensor-memory lanes of its quarter, warp index modulo 4; two warps
 // share a quarter and take 32 tokens each).  An epilogue thread owns one weight row and walks its tokens, so
 // everything that depends on the row alone (which of q/k/v, head, rotation-table column) is computed once.
-// Every wait is bounded; every path, also a failed one, reaches the common exit that frees the tensor memory.
+// Every wait is bounded; every path, also a failed one, reaches the common exit, which lets copies in flight land
+// (bounded) and frees the tensor memory.
 constexpr int kUmmaM = 128;
 constexpr int kUmmaSubW = kUmmaM * 128;                            // 16 KiB
 constexpr int kUmmaStage = 2 * kUmmaSubW + 4 * kPfSubBytesX;       // 64 KiB: weights, activations hi, activations lo
@@ -317,6 +318,7 @@ static __global__ void __launch_bounds__(kUmmaThreads, 1) prefill_gemm_umma_kern
     uint64_t* acc_full = empty + kStages;                // [2]
     uint64_t* acc_empty = acc_full + 2;                  // [2]
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+    int* s_fail = reinterpret_cast<int*>(tmem_slot + 1);  // set by a role whose wait ran out
     const uint32_t ring = (smem_u32(smem) + 1024u + 1023u) & ~1023u;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int unit = blockIdx.x, n_units = gridDim.x;
@@ -326,6 +328,7 @@ static __global__ void __launch_bounds__(kUmmaThreads, 1) prefill_gemm_umma_kern
     const int n_items = n_tiles * S;
     pdl_launch_dependents();
     if (tid == 0) {
+        *s_fail = 0;
         for (int i = 0; i < kStages; ++i) {
             mbar_init(&full[i], 1);
             mbar_init(&empty[i], 1);
@@ -379,6 +382,7 @@ static __global__ void __launch_bounds__(kUmmaThreads, 1) prefill_gemm_umma_kern
                         --early;  // first pass of the first item: only the activations are missing
                     } else {
                         if (pass > 0 && !mbar_wait_bounded(&empty[slot], (uint32_t)(pass - 1) & 1u, a.st)) {
+                            *s_fail = 1;
                             ok = false;
                             break;
                         }
@@ -407,11 +411,15 @@ static __global__ void __launch_bounds__(kUmmaThreads, 1) prefill_gemm_umma_kern
                 const int kc0 = (split * n_kc) / S, kc1 = ((split + 1) * n_kc) / S;
                 const int b = it & 1, use = it >> 1;
                 (void)tile;
-                if (use > 0 && !mbar_wait_bounded(&acc_empty[b], (uint32_t)(use - 1) & 1u, a.st)) break;
+                if (use > 0 && !mbar_wait_bounded(&acc_empty[b], (uint32_t)(use - 1) & 1u, a.st)) {
+                    *s_fail = 1;
+                    break;
+                }
                 tc_fence_after();
                 const uint32_t d_tmem = tmem + (uint32_t)(b * kUmmaAccCols);
                 for (int kc = kc0; kc < kc1; ++kc) {
                     if (!mbar_wait_bounded(&full[slot], par, a.st)) {
+                        *s_fail = 1;
                         ok = false;
                         break;
                     }
@@ -445,7 +453,10 @@ static __global__ void __launch_bounds__(kUmmaThreads, 1) prefill_gemm_umma_kern
         for (int item = unit; item < n_items; item += n_units, ++it) {
             const int tile = item / S, split = item - tile * S;
             const int b = it & 1, use = it >> 1;
-            if (!__all_sync(0xffffffffu, mbar_wait_bounded(&acc_full[b], (uint32_t)use & 1u, a.st))) break;
+            if (!__all_sync(0xffffffffu, mbar_wait_bounded(&acc_full[b], (uint32_t)use & 1u, a.st))) {
+                *s_fail = 1;
+                break;
+            }
             tc_fence_after();
             if (tid == 64) PF_STAMP(34);
             float v[32], vlo[32];
@@ -465,6 +476,14 @@ static __global__ void __launch_bounds__(kUmmaThreads, 1) prefill_gemm_umma_kern
     // ---------------- common exit
     __syncwarp();
     tc_fence_before();
+    __syncthreads();
+    // A wait that ran out has set the status word (mbar_wait_bounded) and this CTA's flag.  Copies may then still be in
+    // flight towards its shared memory: give them a bounded time to land before the CTA leaves (a tile copy takes a
+    // few microseconds; nobody reads the tiles any more).
+    if (tid == 0 && *reinterpret_cast<volatile int*>(s_fail) != 0) {
+        const long long t0 = clock64();
+        while (clock64() - t0 < (1 << 17)) __nanosleep(1000);
+    }
     __syncthreads();
     if (warp == 1) tc_dealloc(tmem, kUmmaTmemCols);
 }

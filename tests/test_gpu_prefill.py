@@ -102,6 +102,23 @@ def test_prefill_token_loop_for_fp32_models(E, oracle):
     b.close()
 
 
+def test_prefill_token_loop_for_widths_off_the_tile_grid(E):
+    """FP16 weights whose widths are not multiples of 64 inputs (the tensor maps cut rows into 128-byte pieces) stay
+    on the token loop: same bits as lpp_step_logits token by token."""
+    c = ModelConfig(dim=96, hidden_dim=160, n_layers=2, n_heads=3, n_kv_heads=3, vocab_size=512, seq_len=32, rope_base=10000.0)
+    T = synth.gen_model(c, 21, "f16", True)
+    toks = synth.prompt_tokens(c.vocab_size, 12, 21)
+    a, b = E.Engine(c, "f16", "f16"), E.Engine(c, "f16", "f16")
+    for eng in (a, b):
+        eng.load_weights(T)
+    a.prefill(toks[:-1])
+    for pos, t in enumerate(toks[:-1]):
+        b.step_logits(int(t), pos)
+    assert np.array_equal(a.step_logits(int(toks[-1]), 11), b.step_logits(int(toks[-1]), 11))
+    a.close()
+    b.close()
+
+
 def test_prefill_llama32_1b_shape(E, oracle):
     """Config 3's 32-token prompt at the real shape: last-position logits of the batched pass against the oracle and
     against the token loop, and how much faster the batched pass is."""
