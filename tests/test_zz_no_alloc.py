@@ -60,6 +60,44 @@ def test_static_scratch_sampler_matches_allocating_one(env, V):
         assert np.array_equal(lg_a, lg_b)          # and the same in-place effect on the logits
 
 
+def test_static_scratch_sampler_leaves_device_memory_alone(env):
+    """After its first call on the device the entry point allocates nothing: free device memory and the default
+    memory pool's reservation are the same before and after a run of calls on pre-allocated buffers."""
+    torch, lib = env
+    V = 32000
+    rng = np.random.default_rng(5)
+    d_logits = torch.from_numpy(rng.standard_normal(V).astype(np.float32)).cuda()
+    keep = d_logits.clone()
+    d_hist = torch.from_numpy(rng.integers(0, V, 64).astype(np.int32)).cuda()
+    out = torch.zeros(1, dtype=torch.int32, device="cuda")
+    stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+    def call(r):
+        d_logits.copy_(keep)
+        return lib.lpp_op_sample_static(C.c_void_p(d_logits.data_ptr()), V, 0.8, 1.1, C.c_void_p(d_hist.data_ptr()), 64, r,
+                                        C.c_void_p(out.data_ptr()), stream)
+
+    assert call(0.5) == 0  # the first call per device resolves the scratch address
+    torch.cuda.synchronize()
+    rt = C.CDLL("libcudart.so.12")
+    pool = C.c_void_p()
+    assert rt.cudaDeviceGetDefaultMemPool(C.byref(pool), torch.cuda.current_device()) == 0
+
+    def reserved():
+        v = C.c_uint64(0)
+        assert rt.cudaMemPoolGetAttribute(pool, 5, C.byref(v)) == 0  # cudaMemPoolAttrReservedMemCurrent
+        return v.value
+
+    free0, res0 = torch.cuda.mem_get_info()[0], reserved()
+    toks = []
+    for r in (0.1, 0.37, 0.93):
+        assert call(r) == 0
+        torch.cuda.synchronize()
+        toks.append(int(out.item()))
+    assert torch.cuda.mem_get_info()[0] == free0 and reserved() == res0
+    assert all(0 <= t < V for t in toks)
+
+
 def test_static_scratch_sampler_rejects_oversize(env):
     torch, lib = env
     lib.lpp_last_error.restype = C.c_char_p
