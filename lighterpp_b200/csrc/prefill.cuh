@@ -6,20 +6,20 @@
 // four projections become small GEMMs  C[tokens][rows] = X[tokens][K] . W[rows][K]^T  that are still bound by
 // the weight stream (2 FLOP per weight byte and token: far below the tensor cores' ridge for 64 tokens), so the
 // kernels are organised around that stream like the decode GEMV -- a producer thread, a ring of shared-memory
-// stages, mbarrier hand-over -- only that a stage is a set of 2-D tiles fetched by the tensor memory accelerator
+// stages, mbarrier hand-over -- only that a stage is a pair of tiles fetched by the tensor memory accelerator
 // (cp.async.bulk.tensor with the 128-byte swizzle, one copy per operand and stage: 128 weight rows x 128 inputs
 // through a 3-D map, the matching 64 tokens x 128 inputs of the activations, hi and lo plane, through a 4-D map;
 // the weight tiles of the first ring pass are requested before the dependency wait) and the arithmetic runs on
-// the tensor cores:
-// prefill_gemm_umma_kernel issues tcgen05.mma reading both operands from shared memory through matrix descriptors,
-// FP32 accumulators in tensor memory, epilogue warps that read them back with tcgen05.ld.  (An earlier kernel that
-// consumed the same ring with ldmatrix + mma.sync.m16n8k16 in eight warps measured 1.17 ms against 0.83 ms for a
-// 64-token pass of the Llama-3.2-1B shape and was removed.)
+// the tensor cores: prefill_gemm_umma_kernel issues tcgen05.mma reading both operands from shared memory through
+// matrix descriptors, FP32 accumulators in tensor memory, epilogue warps that read them back with tcgen05.ld.
+// (An earlier kernel that consumed the same ring with ldmatrix + mma.sync.m16n8k16 in eight warps measured 1.17 ms
+// against 0.83 ms for a 64-token pass of the Llama-3.2-1B shape and was removed.)
 // Matrices whose row tiles do not fill the GPU (QKV, o_proj, down) are also cut along K so that every SM streams
 // a share; partial sums are added in a fixed order by the next kernel (the norm kernel for the residual
-// projections, prefill_qkv_finish_kernel for QKV).  Activations are rounded to FP16 as MMA operands; everything
-// between the GEMMs (residual stream, RMSNorm, RoPE, softmax) stays FP32, following src/ops.cpp like the decode path.
-// The causal attention of the block (prefill_attention_mma_kernel) is a tensor-core flash attention over the cache.
+// projections, prefill_qkv_finish_kernel for QKV).  Activations reach the MMAs as hi + lo FP16 pairs (see
+// split_half); everything between the GEMMs (residual stream, RMSNorm, RoPE, softmax) stays FP32, following
+// src/ops.cpp like the decode path.  The causal attention of the block (prefill_attention_mma_kernel) is a
+// tensor-core flash attention over the cache.
 //
 // Tensor maps cover this GPU's own memory only; no cluster multicast is used anywhere.
 #pragma once
@@ -41,7 +41,7 @@ enum PfEpi : int { kPfQkv = 0, kPfResid = 1, kPfSwiglu = 2 };
 // An activation x is handed to the tensor cores as two FP16 numbers, hi = fp16(x) and lo = fp16(x - hi): the MMA
 // accumulates W.hi + W.lo in FP32, which keeps about 22 bits of x, so the batched pass carries FP32 activations
 // through FP16-operand MMAs like the token loop carries them through its FP32 arithmetic.  Every activation buffer
-// holds the hi plane [kPrefillTokens][cols] followed by the lo plane; one tensor map covers both (lo tile at row 64).
+// holds the hi plane [kPrefillTokens][cols] followed by the lo plane; one 4-D tensor map covers both.
 __device__ __forceinline__ void split_half(float x, __half& hi, __half& lo) {
     hi = __float2half_rn(x);
     lo = __float2half_rn(x - __half2float(hi));
@@ -53,7 +53,7 @@ struct PrefillGemmArgs {
     int n_tokens;         // valid tokens (<= kPrefillTokens)
     int start_pos;        // position of token 0
     int epi;
-    int splits;           // K is cut into this many ranges (kPfResid only when > 1): work item = (row tile, range)
+    int splits;           // K is cut into this many ranges (kPfResid and kPfQkv): work item = (row tile, range)
     StepState* st;
     // kPfResid: x[t][row] += c (x: [kPrefillTokens][n_rows] FP32) when splits == 1; else the partial sums go to
     // part[split][t][row] and the next kernel (prefill_norm_kernel) adds them to x in split order
@@ -90,26 +90,11 @@ __device__ __forceinline__ void mma_f16_16816(float (&d)[4], uint32_t a0, uint32
 __device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
 }
-// One value of the finished tile: row `row` (and its pair partner `other`, the value of row ^ 1), token t.
-__device__ __forceinline__ void pf_epilogue(const PrefillGemmArgs& a, int split, int row, int t, float v, float other) {
+// QKV epilogue of one value: row `row` (and its pair partner `other`, the value of row ^ 1), token t: rotation of
+// q and k pairs, q -> FP32 rows, k / v -> cache rows at the reference index.
+__device__ __forceinline__ void pf_qkv_store(const PrefillGemmArgs& a, int row, int t, float v, float other) {
     if (row >= a.n_rows || t >= a.n_tokens) return;
-    if (a.epi == kPfResid) {
-        if (a.splits > 1) {
-            a.part[((size_t)split * kPrefillTokens + t) * a.n_rows + row] = v;
-        } else {
-            float* p = a.x + (size_t)t * a.n_rows + row;
-            *p = *p + v;  // x += W.xb (src/model.cpp:232, 239)
-        }
-    } else if (a.epi == kPfSwiglu) {
-        // rows are interleaved (gate_i, up_i); hb = (h1*sigmoid(h1))*h3 (src/ops.cpp:78-87): the even row writes
-        if ((row & 1) == 0) {
-            const float sig = __fdiv_rn(1.0f, 1.0f + expf(-v));
-            __half hi, lo;
-            split_half(__fmul_rn(__fmul_rn(v, sig), other), hi, lo);
-            a.hb[(size_t)t * (a.n_rows >> 1) + (row >> 1)] = hi;
-            a.hb[(size_t)(kPrefillTokens + t) * (a.n_rows >> 1) + (row >> 1)] = lo;
-        }
-    } else {  // kPfQkv
+    {  // (one scope: the body reads like the decode epilogue it mirrors, gemv.cuh)
         const int pos = a.start_pos + t;
         if (pos < 0 || pos >= a.seq_len) {
             atomicOr(&a.st->status, kStatusBadPos);
@@ -138,17 +123,18 @@ __device__ __forceinline__ void pf_epilogue(const PrefillGemmArgs& a, int split,
 
 // ---- the GEMM on the fifth-generation tensor cores (tcgen05), accumulators in tensor memory
 //
-// A work item is (tile of 128 weight rows, K range).  Per stage the tensor memory accelerator delivers two
-// 128-row x 64-input weight sub-tiles and the two matching 64-token activation sub-tiles, all in the 128-byte
-// swizzled K-major layout that the MMA reads straight from shared memory through matrix descriptors: one elected
-// thread issues eight 128 x 64 x 16 MMAs per stage (D[128 rows][64 tokens] += W . X^T) into one of two 64-column
-// accumulators in tensor memory, commits the stage back to the producer, and after the last stage of the item
-// commits the accumulator to the four epilogue warps; these read their 32 lanes (rows) x 64 columns (tokens) with
-// tcgen05.ld, release the accumulator and run the same epilogues as above from registers while the next item's
-// MMAs already fill the other accumulator.  Warp roles: 0 producer, 1 MMA issue and tensor-memory allocation,
-// 2..9 epilogue (a warp may only read the tensor-memory lanes of its quarter, warp index modulo 4; two warps
-// share a quarter and take 32 tokens each).  An epilogue thread owns one weight row and walks its tokens, so
-// everything that depends on the row alone (which of q/k/v, head, rotation-table column) is computed once.
+// A work item is (tile of 128 weight rows, K range).  Per stage the tensor memory accelerator delivers the two
+// 128-row x 64-input weight sub-tiles and, per 64-input piece, the 64 hi rows followed by the 64 lo rows of the
+// activations, all in the 128-byte swizzled K-major layout that the MMA reads straight from shared memory through
+// matrix descriptors: one elected thread issues eight 128 x 128 x 16 MMAs per stage (D[128 rows][hi tokens | lo
+// tokens] += W . X^T) into one of two 128-column accumulators in tensor memory, commits the stage back to the
+// producer, and after the last stage of the item commits the accumulator to the eight epilogue warps; these read
+// their 32 lanes (rows) x 32 token columns of both halves with tcgen05.ld, add them, release the accumulator and
+// run the epilogue from registers while the next item's MMAs already fill the other accumulator.  Warp roles: 0
+// producer, 1 MMA issue and tensor-memory allocation, 2..9 epilogue (a warp may only read the tensor-memory lanes
+// of its quarter, warp index modulo 4; two warps share a quarter and take 32 tokens each).  An epilogue thread owns
+// one weight row and walks its tokens, so everything that depends on the row alone (which of q/k/v, head,
+// rotation-table column) is computed once.
 // Every wait is bounded; every path, also a failed one, reaches the common exit, which lets copies in flight land
 // (bounded) and frees the tensor memory.
 constexpr int kUmmaM = 128;
@@ -211,7 +197,7 @@ __device__ __forceinline__ void tc_ld32(uint32_t taddr, float (&v)[32]) {
 
 // Epilogue of one thread: weight row `row`, tokens t0 .. t0+31 with the sums v[0..31].  Lanes are consecutive rows,
 // so for a fixed token a warp's stores are contiguous; the partner row (row ^ 1) of the rotation and SwiGLU pairs
-// is the neighbouring lane.  Arithmetic and rounding are those of pf_epilogue.
+// is the neighbouring lane.  The rotation rounds like pf_qkv_store.
 template <int EPI>
 __device__ __forceinline__ void umma_epilogue(const PrefillGemmArgs& a, int split, int row, int t0, const float (&v)[32],
                                               int lane) {
@@ -508,8 +494,8 @@ static __global__ void __launch_bounds__(256) prefill_qkv_finish_kernel(const Pr
             v.x += p[s0].x;
             v.y += p[s0].y;
         }
-    pf_epilogue(a, 0, row, t, v.x, v.y);
-    pf_epilogue(a, 0, row + 1, t, v.y, v.x);
+    pf_qkv_store(a, row, t, v.x, v.y);
+    pf_qkv_store(a, row + 1, t, v.y, v.x);
 }
 
 // Rows of the residual stream -> RMS-normalised FP16 rows (MMA operands).  Layer 0 takes the embedding rows of
