@@ -46,19 +46,49 @@ def measured_peak():
 
 
 class ClockSampler:
-    """nvidia-smi clocks / throttle reasons while the timed region runs."""
+    """SM clock, power and throttle reasons of one GPU while the timed region runs.
+
+    Read through NVML in a thread of this process (the same counters nvidia-smi prints; a sample every 5 ms from the
+    first millisecond on, which matters on an 8-GPU box where an nvidia-smi child needs longer to start than a 90 ms
+    timed region lasts); falls back to an nvidia-smi child when the NVML binding is missing.  Nothing is set."""
     Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
          "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
          "clocks_event_reasons.sw_power_cap")
+    REASONS = {0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown", 0x4: "sw_power_cap"}
 
     def __init__(self, index):
-        self.rows, self.proc, self.index = [], None, index
+        self.rows, self.proc, self.index, self.nvml, self.stop, self.source = [], None, index, None, False, None
+
+    def _nvml_loop(self):
+        n = self.nvml
+        try:
+            h = n.nvmlDeviceGetHandleByIndex(self.index)
+            mx = float(n.nvmlDeviceGetMaxClockInfo(h, n.NVML_CLOCK_SM))
+            get_reasons = getattr(n, "nvmlDeviceGetCurrentClocksEventReasons", None) or n.nvmlDeviceGetCurrentClocksThrottleReasons
+            while not self.stop:
+                mask = int(get_reasons(h))
+                self.rows.append([str(float(n.nvmlDeviceGetClockInfo(h, n.NVML_CLOCK_SM))), str(mx),
+                                  str(n.nvmlDeviceGetPowerUsage(h) / 1000.0)] +
+                                 ["Active" if mask & bit else "Not Active" for bit in (0x8, 0x40, 0x20, 0x4)])
+                time.sleep(0.005)
+        except Exception:
+            pass
 
     def __enter__(self):
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nvml, self.source = pynvml, "nvml"
+            self.t = threading.Thread(target=self._nvml_loop, daemon=True)
+            self.t.start()
+            return self
+        except Exception:
+            self.nvml = None
         try:
             self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.Q}",
                                           "--format=csv,noheader,nounits", "-lms", os.environ.get("LPP_BENCH_LMS", "25")],
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.source = "nvidia-smi"
             self.t = threading.Thread(target=self._read, daemon=True)
             self.t.start()
         except Exception:
@@ -70,7 +100,10 @@ class ClockSampler:
             self.rows.append([x.strip() for x in line.split(",")])
 
     def __exit__(self, *a):
-        if self.proc:
+        if self.nvml:
+            self.stop = True
+            self.t.join(timeout=2)
+        elif self.proc:
             time.sleep(0.15)
             self.proc.terminate()
             self.t.join(timeout=2)
@@ -83,7 +116,7 @@ class ClockSampler:
         reasons = sorted({n for r in self.rows if len(r) >= 7 for n, v in zip(names, r[3:7]) if v.lower().startswith("active")})
         busy = [x for x in sm if x > 0.5 * max(sm)]
         return {"sm_mhz": statistics.median(busy), "sm_max_mhz": float(self.rows[0][1]), "reasons": reasons,
-                "samples": len(sm), "power_w_max": max(float(r[2]) for r in self.rows if len(r) >= 7)}
+                "samples": len(sm), "power_w_max": max(float(r[2]) for r in self.rows if len(r) >= 7), "source": self.source}
 
 
 def gen_device_weights(cfg, dtype, tied, seed, layers=None):
