@@ -146,11 +146,12 @@ def test_prefill_llama32_1b_shape(E, oracle):
     loop.close()
 
 
-@pytest.mark.parametrize("name,n", [("tinyllama-1.1b", 150), ("llama-3-8b", 70)])
+@pytest.mark.parametrize("name,n", [("tinyllama-1.1b", 150), ("llama-3.2-1b", 700), ("llama-3-8b", 70)])
 def test_prefill_real_shapes_against_token_loop(E, name, n):
     """The remaining benchmark shapes through the batched pass: eight query heads per KV head at head size 64
     (TinyLlama: the attention kernel's widest CTA) and head size 128 with K = 14336 rows cut into 224 row tiles
-    (Llama-3-8B), three / two blocks of tokens; last-position logits against the token loop on the same GPU
+    (Llama-3-8B), three / two blocks of tokens, and eleven blocks at the Llama-3.2-1B shape (attention over up to
+    eleven 64-position tiles); last-position logits against the token loop on the same GPU
     (which meets the oracle in test_gpu_shapes.py) and K/V rows bit-comparable within FP16 rounding."""
     import torch
     c, dt, tied, seed = synth.SHAPES[name]
@@ -158,7 +159,7 @@ def test_prefill_real_shapes_against_token_loop(E, name, n):
                                                      (2 * c.vocab_size, c.dim)))
     if torch.cuda.mem_get_info()[0] < need + (8 << 30):
         pytest.skip("not enough device memory for two engines of this shape")
-    c = ModelConfig(**{**c.asdict(), "seq_len": 256})
+    c = ModelConfig(**{**c.asdict(), "seq_len": max(256, n + 8)})
     T = synth.gen_model(c, seed, dt, tied, threads=8)
     toks = synth.prompt_tokens(c.vocab_size, n, seed)
     batched, loop = E.Engine(c, dt, "f16"), E.Engine(c, dt, "f16", flags=E.FLAG_NO_PREFILL_GEMM)
